@@ -1,0 +1,79 @@
+"""ctypes binding of include/b200mk.h (the library's only entry points)."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200mk.so")
+
+MK_BF16, MK_F32, MK_I32, MK_I64, MK_U64, MK_F16 = range(6)
+MK_MODE_OFFLINE, MK_MODE_ONEPASS = 0, 1
+MK_NUMERICS_MPK, MK_NUMERICS_TORCH = 0, 1
+MK_CAT_CUDA, MK_CAT_SYMMETRIC = 0, 1
+MK_E_INVALID, MK_E_STATE, MK_E_CUDA, MK_E_UNSUPPORTED, MK_E_DEVICE, MK_E_NOMEM = -1, -2, -3, -4, -5, -6
+
+
+class MkConfig(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int32), ("world_size", C.c_int32), ("rank", C.c_int32), ("num_workers", C.c_int32),
+        ("max_seq_length", C.c_int32), ("max_num_batched_requests", C.c_int32),
+        ("max_num_batched_tokens", C.c_int32), ("max_num_pages", C.c_int32), ("page_size", C.c_int32),
+        ("numerics", C.c_int32), ("eos_token_id", C.c_int64), ("fuse", C.c_int32),
+        ("max_iterations", C.c_int32), ("timeout_ms", C.c_int64), ("device", C.c_int32),
+        ("reserved", C.c_int32 * 7),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "mk_create": (C.c_void_p, [C.POINTER(MkConfig)]),
+    "mk_tensor_attach": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "mk_tensor_new": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int]),
+    "mk_tensor_shuffle": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]),
+    "mk_tensor_fuse": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]),
+    "mk_op": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "mk_set_meta": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int64, C.c_void_p]),
+    "mk_compile": (C.c_int, [C.c_void_p]),
+    "mk_init_requests": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mk_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mk_launch_async": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mk_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mk_get_event_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int]),
+    "mk_finalize": (C.c_int, [C.c_void_p]),
+    "mk_last_error": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "mk_plan": (C.c_int, [C.c_void_p]),
+    "mk_num_device_ops": (C.c_int, [C.c_void_p]),
+    "mk_describe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "mk_grid_size": (C.c_int, [C.c_void_p]),
+    "mk_weight_bytes_per_step": (C.c_int64, [C.c_void_p]),
+    "mk_debug_partition": (C.c_int, [C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int)]),
+    "mk_tensor_ptr": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "mk_tensor_read": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the native library; there is no Python or CPU fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m fleet_chiplet_megakernel_b200._build` "
+            "(nvcc, sm_100a). The decode path has no fallback without it.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def i64_array(values):
+    return (C.c_int64 * len(values))(*[int(v) for v in values])
+
+
+def int_array(values):
+    return (C.c_int * len(values))(*[int(v) for v in values])

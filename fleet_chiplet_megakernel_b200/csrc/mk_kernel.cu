@@ -1,0 +1,1190 @@
+// The persistent decode megakernel for sm_100a.
+//
+// One cooperative launch runs a whole generation.  Every SM hosts one CTA of
+// nine warps: warp 8 is a TMA producer that streams this CTA's share of every
+// linear layer's weights (128x64 bf16 tiles, 128-byte swizzle) into a ring of
+// shared-memory stages, running ahead of the eight consumer warps across op
+// boundaries (weights have no dependencies).  The consumer warps walk the
+// program: wait at a grid barrier where an op reads what other CTAs wrote, do
+// the op's share of work, go on.  Every wait in the kernel is bounded: on
+// expiry the waiter records a status and raises a sticky abort flag that all
+// other waits poll, and the kernel returns with an error code.
+//
+// Replaces the worker/scheduler loops of the reference runtime
+// (include/mirage/persistent_kernel/persistent_kernel.cuh:693-1854) and its
+// task kernels (tasks/blackwell/*.cuh, tasks/ampere/*.cuh, tasks/hopper/rmsnorm_hopper.cuh).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mk_types.h"
+
+namespace mk {
+
+// ------------------------------------------------------------------------------------
+// PTX helpers
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// 2-D tiled TMA load, no multicast: box {64 k-elements, 128 rows} at (x = k, y = row).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+  f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+}
+__device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ------------------------------------------------------------------------------------
+// per-thread context
+// ------------------------------------------------------------------------------------
+struct Ctx {
+  const KParams& p;
+  uint8_t* smem;
+  uint32_t smem_addr;
+  unsigned epoch;     // grid barriers passed
+  unsigned cons_idx;  // weight stages consumed
+  int tid, lane, warp;
+  int iter, cur_op;
+  __device__ Ctx(const KParams& p_) : p(p_) {}
+  __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
+  __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
+  __device__ volatile int* flags() const { return (volatile int*)(smem + p.bar_off + 16 * p.num_stages); }
+  __device__ float* red() const { return (float*)(smem + p.red_off); }
+};
+// flags(): [0] go word written by consumers, read by the producer
+//          [1] stages issued by the producer   [2] broadcast slot   [3] dead flag of the op
+
+__device__ __noinline__ void raise_abort(const Ctx& c, int code, int d0, int d1) {
+  if (atomicCAS(c.p.abort_flag, 0, 1) == 0) {
+    c.p.status[0] = code;
+    c.p.status[1] = blockIdx.x;
+    c.p.status[2] = c.cur_op;
+    c.p.status[3] = c.iter;
+    c.p.status[4] = d0;
+    c.p.status[5] = d1;
+    c.p.status[6] = threadIdx.x;
+    __threadfence();
+  }
+}
+__device__ __forceinline__ bool aborted(const Ctx& c) { return *(volatile int*)c.p.abort_flag != 0; }
+
+// Bounded wait on an mbarrier phase.  Returns false after raising the abort flag.
+__device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
+  unsigned long long t0 = globaltimer();
+  while (true) {
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (aborted(c)) return false;
+    if (globaltimer() - t0 > c.p.timeout_ns) {
+      raise_abort(c, code, (int)bar, (int)parity);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
+  for (int i = 0; i < 16; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(c, bar, parity, code);
+}
+
+// Grid-wide barrier of the consumer warps.  The counter only grows within a
+// launch: barrier number e is passed when it reaches e * gridDim.x.
+__device__ __noinline__ void grid_sync(Ctx& c) {
+  consumer_sync();
+  if (c.tid == 0) {
+    c.epoch += 1;
+    __threadfence();
+    atomicAdd(c.p.grid_bar, 1u);
+    const unsigned target = c.epoch * gridDim.x;
+    if (ld_acquire_u32(c.p.grid_bar) < target) {
+      unsigned long long t0 = globaltimer();
+      int spins = 0;
+      while (ld_acquire_u32(c.p.grid_bar) < target) {
+        if (((++spins) & 63) == 0) {
+          if (aborted(c)) break;
+          if (globaltimer() - t0 > c.p.timeout_ns) {
+            raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+            break;
+          }
+        }
+      }
+    }
+    __threadfence();
+  } else {
+    c.epoch += 1;
+  }
+  consumer_sync();
+}
+
+// Sum over the 256 consumer threads; every thread gets the result.
+__device__ __forceinline__ float block_sum(Ctx& c, float v) {
+  float* r = c.red() + 1024;  // scratch behind the 128x4 accumulator block
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (c.lane == 0) r[c.warp] = v;
+  consumer_sync();
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNumConsumerWarps; ++i) s += r[i];
+  consumer_sync();
+  return s;
+}
+
+// ------------------------------------------------------------------------------------
+// activations -> shared memory, with the optional fused RMSNorm
+// ------------------------------------------------------------------------------------
+// Stages rows tok0 .. tok0+TB-1 of op.in as bf16 [TB][kp] in the x region, zero padded.
+template <int TB>
+__device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0, int T) {
+  const KParams& p = c.p;
+  uint4* xs = reinterpret_cast<uint4*>(c.smem + p.x_off);
+  const int nvec = kp >> 3;
+  const int kvec = K >> 3;
+  for (int tb = 0; tb < TB; ++tb) {
+    const int tok = tok0 + tb;
+    const bool valid = tok < T;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)tok * ld_in);
+    float ss = 0.f;
+    for (int v = c.tid; v < nvec; v += kNumConsumers) {
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (valid && v < kvec) val = __ldcg(src + v);
+      xs[tb * nvec + v] = val;
+      if (norm_w != nullptr) {
+        float f[8];
+        unpack8(val, f);
+        if (p.numerics == NUM_TORCH) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += rbf(f[i] * f[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        }
+      }
+    }
+    if (norm_w != nullptr) {
+      const float tot = block_sum(c, ss);
+      const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
+      if (p.numerics == NUM_TORCH) {
+        // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
+        const float var = rbf(tot / (float)K);
+        const float r = rbf(rsqrtf(var));
+        for (int v = c.tid; v < kvec; v += kNumConsumers) {
+          float f[8], w[8];
+          unpack8(xs[tb * nvec + v], f);
+          unpack8(__ldg(wv + v), w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = w[i] * rbf(f[i] * r);
+          xs[tb * nvec + v] = pack8(f);
+        }
+      } else {
+        const float r = rsqrtf(tot / (float)K + 1e-6f);
+        for (int v = c.tid; v < kvec; v += kNumConsumers) {
+          float f[8], w[8];
+          unpack8(xs[tb * nvec + v], f);
+          unpack8(__ldg(wv + v), w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = f[i] * (r * w[i]);
+          xs[tb * nvec + v] = pack8(f);
+        }
+      }
+    }
+  }
+  consumer_sync();
+}
+
+// ------------------------------------------------------------------------------------
+// linear layer on the CUDA cores (up to 4 tokens per pass)
+// ------------------------------------------------------------------------------------
+struct ArgBest {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgBest arg_better(ArgBest a, ArgBest b) {
+  // larger value wins; ties go to the lower index
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ ArgBest warp_argmax(ArgBest a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = arg_better(a, b);
+  }
+  return a;
+}
+
+template <int TB>
+__device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int T) {
+  const KParams& p = c.p;
+  const float* red = c.red();
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  if (op.flags & F_SILU_MUL) {
+    // rows 0..63 of the tile are gate columns, rows 64..127 the matching up columns
+    const int half = op.n >> 1;
+    for (int e = c.tid; e < 64 * TB; e += kNumConsumers) {
+      const int row = e & 63, tb = e >> 6;
+      const int tok = tok0 + tb, col = blk * 64 + row;
+      if (tok < T && col < half) {
+        const float g = rbf(red[row * TB + tb]);       // linear output is bf16 before the activation
+        const float u = rbf(red[(row + 64) * TB + tb]);
+        const float s = rbf(g / (1.0f + expf(-g)));
+        out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(s * u);
+      }
+    }
+    return;
+  }
+  const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
+  const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
+  for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) {
+    const int row = e & 127, tb = e >> 7;
+    const int tok = tok0 + tb, col = blk * kTileRows + row;
+    if (tok < T && col < op.n) {
+      float v = red[row * TB + tb];
+      if (with_res) {
+        const float r = __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
+        v = (p.numerics == NUM_TORCH) ? rbf(v) + r : v + r;
+      }
+      out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(v);
+    }
+  }
+  if (op.flags & F_ARGMAX) {
+    float* scratch = c.red() + 1024 + 32;
+    for (int tb = 0; tb < TB; ++tb) {
+      ArgBest b;
+      b.v = -INFINITY;
+      b.i = 0x7fffffff;
+      if (c.tid < kTileRows) {
+        const int col = blk * kTileRows + c.tid;
+        if (col < op.n) {
+          b.v = rbf(red[c.tid * TB + tb]);
+          b.i = col;
+        }
+      }
+      b = warp_argmax(b);
+      if (c.lane == 0 && c.warp < 4) {
+        scratch[c.warp * 2] = b.v;
+        scratch[c.warp * 2 + 1] = __int_as_float(b.i);
+      }
+      consumer_sync();
+      if (c.tid == 0 && tok0 + tb < T) {
+        ArgBest a;
+        a.v = scratch[0];
+        a.i = __float_as_int(scratch[1]);
+        for (int w = 1; w < 4; ++w) {
+          ArgBest x;
+          x.v = scratch[w * 2];
+          x.i = __float_as_int(scratch[w * 2 + 1]);
+          a = arg_better(a, x);
+        }
+        op.amax_val[(size_t)(tok0 + tb) * op.amax_n + blk] = a.v;
+        op.amax_idx[(size_t)(tok0 + tb) * op.amax_n + blk] = a.i;
+      }
+      consumer_sync();
+    }
+  }
+}
+
+// Called by all consumers at the end of a run of tiles of one row block, after the
+// per-row sums of the run were left in red[row * TB + token].
+template <int TB>
+__device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int blk, int kt_first, int kt_last,
+                                                 bool first_of_cta, int tok0, int T, int group) {
+  const KParams& p = c.p;
+  float* red = c.red();
+  consumer_sync();
+  const bool whole = (kt_first == 0) && (kt_last == op.nkt - 1);
+  if (!whole) {
+    // this CTA holds one of several k-ranges of the row block: publish the partial
+    // sums; the CTA that arrives last adds them in CTA order and runs the epilogue
+    const int G = gridDim.x;
+    const size_t slot_elems = (size_t)kTileRows * kMaxTokGroup;
+    float* mine = p.partial + (((size_t)group * G + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems;
+    for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) mine[e] = red[e];
+    __threadfence();
+    consumer_sync();
+    volatile int* fl = c.flags();
+    const long long total = (long long)op.nblk * op.nkt;
+    const int c_first = tile_owner((long long)blk * op.nkt, total, G);
+    const int c_last = tile_owner((long long)blk * op.nkt + op.nkt - 1, total, G);
+    unsigned* cnt = p.piece_count + (size_t)group * p.piece_stride + blk;
+    if (c.tid == 0) {
+      const unsigned old = atomicAdd(cnt, 1u);
+      fl[2] = (old == (unsigned)(c_last - c_first)) ? 1 : 0;
+    }
+    consumer_sync();
+    const bool last = fl[2] != 0;
+    if (!last) {
+      consumer_sync();
+      return;
+    }
+    __threadfence();
+    for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) {
+      float s = 0.f;
+      for (int cc = c_first; cc <= c_last; ++cc) {
+        const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
+        const float* src = p.partial + (((size_t)group * G + cc) * 2 + (first ? 0 : 1)) * slot_elems;
+        s += __ldcg(src + e);
+      }
+      red[e] = s;
+    }
+    if (c.tid == 0) *cnt = 0u;
+    consumer_sync();
+  }
+  linear_epilogue<TB>(c, op, blk, tok0, T);
+  consumer_sync();
+}
+
+template <int TB>
+__device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int T, int group) {
+  const KParams& p = c.p;
+  const int kp = op.nkt * kTileK;
+  stage_x<TB>(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, T);
+
+  const int G = gridDim.x;
+  const long long total = (long long)op.nblk * op.nkt;
+  const long long t0 = tile_begin(blockIdx.x, total, G);
+  const long long t1 = tile_begin(blockIdx.x + 1, total, G);
+  if (t0 >= t1) return;
+  const int S = p.num_stages;
+  const int c8 = c.tid & 7, rg = c.tid >> 3;
+  const uint32_t w_off = (uint32_t)(rg * 128 + ((c8 ^ (rg & 7)) << 4));
+  const uint32_t xs_addr = c.smem_addr + p.x_off + c8 * 16;
+  float acc[4][TB];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int tb = 0; tb < TB; ++tb) acc[i][tb] = 0.f;
+
+  int blk = (int)(t0 / op.nkt);
+  int kt = (int)(t0 - (long long)blk * op.nkt);
+  int kt_first = kt;
+  bool first_of_cta = true;
+  for (long long tile = t0; tile < t1; ++tile) {
+    const int s = c.cons_idx % S;
+    const uint32_t parity = (c.cons_idx / S) & 1;
+    mbar_wait(c, c.full_bar(s), parity, ST_TIMEOUT_FULL);
+    const uint32_t st = c.smem_addr + s * kStageBytes + w_off;
+    uint4 w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = lds128(st + i * 32 * 128);
+#pragma unroll
+    for (int tb = 0; tb < TB; ++tb) {
+      float xf[8];
+      unpack8(lds128(xs_addr + (uint32_t)(tb * kp + kt * kTileK) * 2), xf);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float wf[8];
+        unpack8(w[i], wf);
+        float a = acc[i][tb];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a = fmaf(wf[j], xf[j], a);
+        acc[i][tb] = a;
+      }
+    }
+    __syncwarp();
+    if (c.lane == 0) mbar_arrive(c.empty_bar(s));
+    c.cons_idx += 1;
+    const bool end_blk = (kt == op.nkt - 1);
+    if (end_blk || tile == t1 - 1) {
+      // add up the 8 lanes that share a row group, leave the sums in shared memory
+      float* red = c.red();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int tb = 0; tb < TB; ++tb) {
+          float v = acc[i][tb];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          if (c8 == 0) red[(rg + 32 * i) * TB + tb] = v;
+          acc[i][tb] = 0.f;
+        }
+      }
+      linear_finish_piece<TB>(c, op, blk, kt_first, kt, first_of_cta, tok0, T, group);
+      first_of_cta = false;
+      kt_first = 0;
+    }
+    if (end_blk) {
+      kt = 0;
+      blk += 1;
+    } else {
+      kt += 1;
+    }
+  }
+}
+
+// Number of passes the weight stream of a linear op makes for T active tokens.
+__device__ __forceinline__ int linear_passes(int T) { return (T + kMaxTokGroup - 1) / kMaxTokGroup; }
+
+__device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
+  const int passes = linear_passes(T);
+  for (int g = 0; g < passes; ++g) {
+    const int tok0 = g * kMaxTokGroup;
+    const int n = min(kMaxTokGroup, T - tok0);
+    if (n == 1) linear_pass<1>(c, op, tok0, T, g);
+    else if (n == 2) linear_pass<2>(c, op, tok0, T, g);
+    else linear_pass<4>(c, op, tok0, T, g);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// attention: QK-norm + RoPE + KV append + paged split-KV GQA decode + merge
+// ------------------------------------------------------------------------------------
+// One head vector is spread over 16 lanes, 8 dims each.  Both halves of a warp run
+// this with full-mask shuffles (xor < 16 stays inside a half-warp).
+__device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, const void* cos_row, const void* sin_row,
+                                               int l16, int flags, int numerics) {
+  if (flags & F_QK_NORM) {
+    float w[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(norm_w) + l16), w);
+    float ss = 0.f;
+    if (numerics == NUM_TORCH) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += rbf(x[i] * x[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (numerics == NUM_TORCH) {
+      const float r = rbf(rsqrtf(rbf(ss / (float)kHeadDim)));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = rbf(w[i] * rbf(x[i] * r));
+    } else {
+      const float r = rsqrtf(ss / (float)kHeadDim + 1e-6f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = rbf(x[i] * (r * w[i]));
+    }
+  }
+  if (flags & F_ROPE) {
+    float cs[8], sn[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(cos_row) + l16), cs);
+    unpack8(__ldg(reinterpret_cast<const uint4*>(sin_row) + l16), sn);
+    const float sign = (l16 < 8) ? -1.f : 1.f;  // first half: x*cos - partner*sin
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], 8);
+      if (numerics == NUM_TORCH) x[i] = rbf(rbf(x[i] * cs[i]) + rbf(sign * other * sn[i]));
+      else x[i] = rbf(x[i] * cs[i] + sign * other * sn[i]);
+    }
+  }
+}
+
+// aux0 = kv heads, aux1 = q heads.  Tokens: one per request, token t == request slot t.
+template <int QPK>
+__device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
+  const KParams& p = c.p;
+  const int HKV = op.aux0;
+  const int PS = p.page_size;
+  const int G = gridDim.x;
+  int* lens = reinterpret_cast<int*>(c.red() + 1024 + 64);  // [<=64] sequence lengths incl. the new token
+  for (int r = c.tid; r < T; r += kNumConsumers) {
+    const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
+    lens[r] = (last - first - 1) * PS + __ldcg(p.kv_last_page_len + r);
+  }
+  consumer_sync();
+  int Lmax = 1;
+  for (int r = 0; r < T; ++r) Lmax = max(Lmax, lens[r]);
+  const int nb_max = (Lmax + 63) >> 6;
+  int bpc = (T * HKV * nb_max + G - 1) / G;  // 64-position blocks per chunk: one round of tasks
+  bpc = max(bpc, (nb_max + p.attn_max_chunks - 1) / p.attn_max_chunks);
+  bpc = max(bpc, 1);
+  const int CS = bpc * 64;
+  const int nch_max = (nb_max + bpc - 1) / bpc;
+  const int ntasks = T * HKV * nch_max;
+  const int hw = c.tid >> 4, l16 = c.tid & 15;
+  constexpr int PART = QPK * (kHeadDim + 2);
+  const float sc = 1.4426950408889634f / sqrtf((float)kHeadDim);  // softmax scale in the exp2 domain
+  float* sm_o = reinterpret_cast<float*>(c.smem + p.x_off);       // [16][QPK][128]
+  float* sm_m = sm_o + 16 * QPK * kHeadDim;                       // [16][QPK]
+  float* sm_l = sm_m + 16 * QPK;
+
+  for (int task = blockIdx.x; task < ntasks; task += G) {
+    const int ch = task % nch_max;
+    const int h = (task / nch_max) % HKV;
+    const int t = task / (nch_max * HKV);
+    const int L = lens[t];
+    const int p0 = ch * CS;
+    if (p0 >= L || L <= 0) continue;
+    const int p1 = min(L, p0 + CS);
+    const int nch = (L + CS - 1) / CS;
+    const int kv_base = __ldcg(p.kv_indptr + t);
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)t * op.ld_in +
+                               (size_t)h * (QPK + 2) * kHeadDim;
+    const int pos = min(L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
+    const __nv_bfloat16* cos_row = reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim;
+    const __nv_bfloat16* sin_row = reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim;
+
+    float q[QPK][8];
+#pragma unroll
+    for (int qh = 0; qh < QPK; ++qh) {
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + qh * kHeadDim) + l16), q[qh]);
+      head_norm_rope(q[qh], op.q_norm_w, cos_row, sin_row, l16, op.flags, p.numerics);
+    }
+    // the new token's K (normalised, rotated) and V; the last chunk appends them to the cache
+    uint4 knew, vnew;
+    {
+      float kf[8];
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + QPK * kHeadDim) + l16), kf);
+      head_norm_rope(kf, op.k_norm_w, cos_row, sin_row, l16, op.flags, p.numerics);
+      knew = pack8(kf);
+      vnew = __ldcg(reinterpret_cast<const uint4*>(row + (QPK + 1) * kHeadDim) + l16);
+    }
+    if (p1 == L && hw == 0) {
+      const int pg = __ldcg(p.kv_indices + kv_base + (L - 1) / PS);
+      const size_t dst = (((size_t)pg * PS + (L - 1) % PS) * HKV + h) * kHeadDim;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = knew;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+    }
+
+    float m[QPK], l[QPK], o[QPK][8];
+#pragma unroll
+    for (int qh = 0; qh < QPK; ++qh) {
+      m[qh] = -INFINITY;
+      l[qh] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[qh][i] = 0.f;
+    }
+    const int niter = (p1 - p0 + 15) >> 4;
+    for (int it = 0; it < niter; it += 4) {
+      uint4 kr[4], vr[4];
+      bool ok[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = p0 + (it + u) * 16 + hw;
+        ok[u] = (it + u < niter) && (j < p1);
+        kr[u] = make_uint4(0, 0, 0, 0);
+        vr[u] = make_uint4(0, 0, 0, 0);
+        if (ok[u] && j == L - 1) {
+          kr[u] = knew;
+          vr[u] = vnew;
+        } else if (ok[u]) {
+          const int pg = __ldcg(p.kv_indices + kv_base + j / PS);
+          const size_t src = (((size_t)pg * PS + j % PS) * HKV + h) * kHeadDim;
+          kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src) + l16);
+          vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src) + l16);
+        }
+      }
+      float s[4][QPK];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float kf[8];
+        unpack8(kr[u], kf);
+#pragma unroll
+        for (int qh = 0; qh < QPK; ++qh) {
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d = fmaf(q[qh][i], kf[i], d);
+#pragma unroll
+          for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+          s[u][qh] = ok[u] ? d * sc : -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int qh = 0; qh < QPK; ++qh) {
+        float mn = m[qh];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mn = fmaxf(mn, s[u][qh]);
+        if (mn == -INFINITY) continue;
+        const float alpha = exp2f(m[qh] - mn);
+        float pr[4];
+        float ls = 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          pr[u] = exp2f(s[u][qh] - mn);
+          ls += pr[u];
+        }
+        l[qh] = l[qh] * alpha + ls;
+        m[qh] = mn;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[qh][i] *= alpha;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float vf[8];
+          unpack8(vr[u], vf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[qh][i] = fmaf(pr[u], vf[i], o[qh][i]);
+        }
+      }
+    }
+    // combine the 16 half-warps
+#pragma unroll
+    for (int qh = 0; qh < QPK; ++qh) {
+      float* dst = sm_o + ((size_t)hw * QPK + qh) * kHeadDim + l16 * 8;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(o[qh][0], o[qh][1], o[qh][2], o[qh][3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(o[qh][4], o[qh][5], o[qh][6], o[qh][7]);
+      if (l16 == 0) {
+        sm_m[hw * QPK + qh] = m[qh];
+        sm_l[hw * QPK + qh] = l[qh];
+      }
+    }
+    consumer_sync();
+    float* part = p.attn_part + (((size_t)t * HKV + h) * p.attn_max_chunks + ch) * PART;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)t * op.ld_out + (size_t)h * QPK * kHeadDim;
+    for (int e = c.tid; e < QPK * kHeadDim; e += kNumConsumers) {
+      const int qh = e >> 7, d = e & 127;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 16; ++w) M = fmaxf(M, sm_m[w * QPK + qh]);
+      float Ls = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < 16; ++w) {
+        const float mw = sm_m[w * QPK + qh];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += f * sm_l[w * QPK + qh];
+        O += f * sm_o[((size_t)w * QPK + qh) * kHeadDim + d];
+      }
+      if (nch == 1) {
+        out[e] = __float2bfloat16_rn(O / Ls);
+      } else {
+        part[e] = O;
+        if (d == 0) {
+          part[QPK * kHeadDim + qh] = M;
+          part[QPK * kHeadDim + QPK + qh] = Ls;
+        }
+      }
+    }
+    if (nch > 1) {
+      __threadfence();
+      consumer_sync();
+      volatile int* fl = c.flags();
+      unsigned* cnt = p.attn_count + (size_t)t * HKV + h;
+      if (c.tid == 0) {
+        const unsigned old = atomicAdd(cnt, 1u);
+        fl[2] = (old == (unsigned)(nch - 1)) ? 1 : 0;
+      }
+      consumer_sync();
+      if (fl[2] != 0) {
+        __threadfence();
+        const float* base = p.attn_part + (((size_t)t * HKV + h) * p.attn_max_chunks) * PART;
+        for (int e = c.tid; e < QPK * kHeadDim; e += kNumConsumers) {
+          const int qh = e >> 7;
+          float M = -INFINITY;
+          for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, __ldcg(base + (size_t)cc * PART + QPK * kHeadDim + qh));
+          float Ls = 0.f, O = 0.f;
+          for (int cc = 0; cc < nch; ++cc) {
+            const float f = exp2f(__ldcg(base + (size_t)cc * PART + QPK * kHeadDim + qh) - M);
+            Ls += f * __ldcg(base + (size_t)cc * PART + QPK * kHeadDim + QPK + qh);
+            O += f * __ldcg(base + (size_t)cc * PART + e);
+          }
+          out[e] = __float2bfloat16_rn(O / Ls);
+        }
+        if (c.tid == 0) *cnt = 0u;
+      }
+    }
+    consumer_sync();
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// small ops
+// ------------------------------------------------------------------------------------
+// aux0 = embedding rows
+__device__ void op_embed(Ctx& c, const OpDesc& op, int T) {
+  const int nseg = (op.n + 2047) / 2048;
+  const long long* ids = reinterpret_cast<const long long*>(op.in);
+  for (int u = blockIdx.x; u < T * nseg; u += gridDim.x) {
+    const int tok = u / nseg, seg = u % nseg;
+    long long id = __ldcg(ids + (size_t)tok * op.ld_in);
+    if (id < 0 || id >= op.aux0) {
+      if (c.tid == 0) raise_abort(c, ST_BAD_TOKEN, tok, (int)id);
+      id = 0;
+    }
+    const int col = seg * 2048 + c.tid * 8;
+    if (col < op.n) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.w) + (size_t)id * op.ld_res + col));
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out + col) = v;
+    }
+  }
+}
+
+__device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
+  const int kp = ((op.n + 63) / 64) * 64;
+  for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
+    stage_x<1>(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1);
+    const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out);
+    for (int v = c.tid; v < (op.n >> 3); v += kNumConsumers) dst[v] = xs[v];
+    consumer_sync();
+  }
+}
+
+// aux0 = columns per [gate | up] block of the input
+__device__ void op_silu_mul(Ctx& c, const OpDesc& op, int T) {
+  const int bk = op.aux0;
+  const int nvec = op.n >> 3;
+  const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  for (long long e = (long long)blockIdx.x * kNumConsumers + c.tid; e < (long long)T * nvec;
+       e += (long long)gridDim.x * kNumConsumers) {
+    const int tok = (int)(e / nvec), col = (int)(e % nvec) * 8;
+    const size_t src = (size_t)tok * op.ld_in + (size_t)(col / bk) * 2 * bk + col % bk;
+    float g[8], u[8], r[8];
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(in + src)), g);
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(in + src + bk)), u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = rbf(g[i] / (1.0f + expf(-g[i]))) * u[i];
+    *reinterpret_cast<uint4*>(out + (size_t)tok * op.ld_out + col) = pack8(r);
+  }
+}
+
+__device__ ArgBest block_argmax(Ctx& c, ArgBest b) {
+  float* scratch = c.red() + 1024 + 32;
+  b = warp_argmax(b);
+  if (c.lane == 0) {
+    scratch[c.warp * 2] = b.v;
+    scratch[c.warp * 2 + 1] = __int_as_float(b.i);
+  }
+  consumer_sync();
+  ArgBest a;
+  a.v = scratch[0];
+  a.i = __float_as_int(scratch[1]);
+  for (int w = 1; w < kNumConsumerWarps; ++w) {
+    ArgBest x;
+    x.v = scratch[w * 2];
+    x.i = __float_as_int(scratch[w * 2 + 1]);
+    a = arg_better(a, x);
+  }
+  consumer_sync();
+  return a;
+}
+
+// logits [T][n] -> amax_n partial (value, index) pairs per token
+__device__ void op_argmax_partial(Ctx& c, const OpDesc& op, int T) {
+  const int np = op.amax_n;
+  const int chunk = (op.n + np - 1) / np;
+  const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
+  for (int u = blockIdx.x; u < T * np; u += gridDim.x) {
+    const int tok = u / np, ck = u % np;
+    const int lo = ck * chunk, hi = min(op.n, lo + chunk);
+    ArgBest b;
+    b.v = -INFINITY;
+    b.i = 0x7fffffff;
+    for (int i = lo + c.tid; i < hi; i += kNumConsumers) {
+      ArgBest x;
+      x.v = __bfloat162float(__ldcg(in + (size_t)tok * op.ld_in + i));
+      x.i = i;
+      b = arg_better(b, x);
+    }
+    b = block_argmax(c, b);
+    if (c.tid == 0) {
+      op.amax_val[(size_t)tok * np + ck] = b.v;
+      op.amax_idx[(size_t)tok * np + ck] = b.i;
+    }
+  }
+}
+
+// partial pairs -> int64 token per row; CTA 0 only
+__device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
+  long long* out = reinterpret_cast<long long*>(op.out);
+  for (int tok = 0; tok < T; ++tok) {
+    ArgBest b;
+    b.v = -INFINITY;
+    b.i = 0x7fffffff;
+    for (int i = c.tid; i < op.amax_n; i += kNumConsumers) {
+      ArgBest x;
+      x.v = __ldcg(op.amax_val + (size_t)tok * op.amax_n + i);
+      x.i = __ldcg(op.amax_idx + (size_t)tok * op.amax_n + i);
+      b = arg_better(b, x);
+    }
+    b = block_argmax(c, b);
+    if (c.tid == 0) out[(size_t)tok * op.ld_out] = (b.i == 0x7fffffff) ? -1 : (long long)b.i;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// continuous-batching bookkeeping between iterations (CTA 0, one thread)
+// ------------------------------------------------------------------------------------
+// Same protocol as the reference's offline mode (persistent_kernel.cuh:380-536):
+// append the sampled tokens, retire finished requests and free their pages,
+// compact the survivors, give each one more token, admit new requests, and
+// leave the number of active tokens in qo_indptr[max_reqs].  It is split in two so
+// that a launch bounded by max_iters still appends its last tokens before it ends.
+// Part 1, after an iteration: append the sampled tokens, advance step[], retire
+// finished requests and return their pages.
+__device__ __noinline__ void bookkeep_finish(Ctx& c) {
+  const KParams& p = c.p;
+  const int R = p.max_reqs;
+  int tail = p.sched[1];
+  for (int i = 0; i < R; ++i) {
+    const int rid = p.request_ids[i];
+    if (rid < 0) continue;
+    int st = p.step[rid];
+    const int q0 = p.qo_indptr[i];
+    const int n = p.qo_indptr[i + 1] - q0;
+    const int pl = p.prompt_lengths[rid];
+    for (int j = 0; j < n; ++j) {
+      const int pos = st + j + 1;
+      if (pos >= pl && pos < p.max_seq_len) p.tokens[(size_t)rid * p.max_seq_len + pos] = p.output_tokens[q0 + j];
+    }
+    st += n;
+    p.step[rid] = st;
+    const bool done = (st + 1 >= p.max_seq_len) ||
+                      (st >= pl && p.tokens[(size_t)rid * p.max_seq_len + st] == p.eos);
+    if (done) {
+      p.request_ids[i] = -1;
+      const int k0 = p.kv_indptr[i], k1 = p.kv_indptr[i + 1];
+      for (int j = k0; j < k1; ++j) {
+        p.page_queue[tail % p.max_pages] = p.kv_indices[j];
+        ++tail;
+      }
+    }
+  }
+  p.sched[1] = tail;
+}
+
+// Part 2, before an iteration: compact the surviving requests, give each one more
+// token and the page it needs, admit new requests.  Returns the active tokens.
+__device__ __noinline__ int bookkeep_prepare(Ctx& c) {
+  const KParams& p = c.p;
+  const int R = p.max_reqs;
+  int head = p.sched[0], tail = p.sched[1];
+  int* old_idx = reinterpret_cast<int*>(c.smem + p.x_off);
+  const int n_old = p.kv_indptr[R];
+  for (int i = 0; i < n_old; ++i) old_idx[i] = p.kv_indices[i];
+  int nreq = 0, ntok = 0, npages = 0;
+  for (int i = 0; i < R; ++i) {
+    const int rid = p.request_ids[i];
+    if (rid < 0) continue;
+    const int k0 = p.kv_indptr[i];
+    const int have = p.kv_indptr[i + 1] - k0;
+    p.request_ids[nreq] = rid;
+    p.qo_indptr[nreq] = ntok;
+    p.kv_indptr[nreq] = npages;
+    const int st = p.step[rid];
+    const int nnew = min(1, p.max_tokens - ntok);
+    for (int j = 0; j < nnew; ++j) p.input_tokens[ntok + j] = p.tokens[(size_t)rid * p.max_seq_len + st + j];
+    const int need = (st + nnew + p.page_size - 1) / p.page_size;
+    const int last = (st + nnew) % p.page_size;
+    p.kv_last_page_len[nreq] = last == 0 ? p.page_size : last;
+    for (int j = 0; j < have; ++j) p.kv_indices[npages + j] = old_idx[k0 + j];
+    for (int j = have; j < need; ++j) {
+      if (tail - head <= 0) {
+        raise_abort(c, ST_OUT_OF_PAGES, rid, need);
+        return 0;
+      }
+      p.kv_indices[npages + j] = p.page_queue[head % p.max_pages];
+      ++head;
+    }
+    npages += need > have ? need : have;
+    ntok += nnew;
+    ++nreq;
+  }
+  while (nreq < R && ntok < p.max_tokens) {
+    const int rid = p.sched[2];
+    if (rid >= p.total_requests) break;
+    if (tail - head <= 0) break;  // no page for a new request yet: admit it later
+    p.request_ids[nreq] = rid;
+    p.qo_indptr[nreq] = ntok;
+    p.kv_indptr[nreq] = npages;
+    p.input_tokens[ntok] = p.tokens[(size_t)rid * p.max_seq_len];
+    p.kv_last_page_len[nreq] = 1;
+    p.kv_indices[npages] = p.page_queue[head % p.max_pages];
+    ++head;
+    npages += 1;
+    ntok += 1;
+    ++nreq;
+    p.sched[2] = rid + 1;
+  }
+  for (int i = nreq; i < R; ++i) p.request_ids[i] = -1;
+  for (int i = nreq; i <= R; ++i) {
+    p.qo_indptr[i] = ntok;
+    p.kv_indptr[i] = npages;
+  }
+  p.sched[0] = head;
+  p.sched[1] = tail;
+  return ntok;
+}
+
+// ------------------------------------------------------------------------------------
+// the TMA producer
+// ------------------------------------------------------------------------------------
+__device__ __noinline__ void producer_loop(Ctx& c) {
+  const KParams& p = c.p;
+  const int S = p.num_stages;
+  const int G = gridDim.x;
+  volatile int* fl = c.flags();
+  unsigned issued = 0;
+  for (int iter = 1;; ++iter) {
+    // wait for the consumers to publish this iteration's token count (or the end)
+    int go;
+    {
+      unsigned long long t0 = globaltimer();
+      int spins = 0;
+      while (true) {
+        go = fl[0];
+        if (go < 0 || (go >> 8) >= iter) break;
+        __nanosleep(40);
+        if (((++spins) & 255) == 0) {
+          if (aborted(c)) { go = -1; break; }
+          if (globaltimer() - t0 > c.p.timeout_ns) {
+            raise_abort(c, ST_TIMEOUT_GO, iter, go);
+            go = -1;
+            break;
+          }
+        }
+      }
+    }
+    if (go < 0) break;
+    const int T = go & 255;
+    const int passes = linear_passes(T);
+    bool dead = false;
+    for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
+      const OpDesc& op = p.ops[oi];
+      if (op.type != OP_LINEAR) continue;
+      const long long total = (long long)op.nblk * op.nkt;
+      const long long t0 = tile_begin(blockIdx.x, total, G);
+      const long long t1 = tile_begin(blockIdx.x + 1, total, G);
+      for (int g = 0; g < passes && !dead; ++g) {
+        int blk = (int)(t0 / op.nkt);
+        int kt = (int)(t0 - (long long)blk * op.nkt);
+        for (long long tile = t0; tile < t1; ++tile) {
+          const int s = issued % S;
+          if (!mbar_wait(c, c.empty_bar(s), ((issued / S) & 1) ^ 1, ST_TIMEOUT_EMPTY)) {
+            dead = true;
+            break;
+          }
+          mbar_arrive_expect_tx(c.full_bar(s), kStageBytes);
+          tma_load_2d(c.smem_addr + s * kStageBytes, op.tmap_w, c.full_bar(s), kt * kTileK, blk * kTileRows);
+          issued += 1;
+          fl[1] = (int)issued;
+          if (++kt == op.nkt) {
+            kt = 0;
+            ++blk;
+          }
+        }
+      }
+    }
+    if (dead || p.mode == MODE_ONEPASS) break;
+  }
+  fl[1] = (int)issued;
+}
+
+// ------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_constant__ KParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Ctx c(p);
+  // 128-byte-swizzled TMA stages need a 1024-byte-aligned base; the host budgets the slack
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  c.smem = smem_raw + pad;
+  c.smem_addr = raw_addr + pad;
+  c.epoch = 0;
+  c.cons_idx = 0;
+  c.tid = threadIdx.x;
+  c.lane = threadIdx.x & 31;
+  c.warp = threadIdx.x >> 5;
+  c.iter = 0;
+  c.cur_op = -1;
+  volatile int* fl = c.flags();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.num_stages; ++s) {
+      mbar_init(c.full_bar(s), 1);
+      mbar_init(c.empty_bar(s), kNumConsumerWarps);
+    }
+    fl[0] = 0;
+    fl[1] = 0;
+    fl[2] = 0;
+    fl[3] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (c.warp == kNumConsumerWarps) {
+    if (c.lane == 0) producer_loop(c);
+    __syncwarp();
+  } else {
+    for (int iter = 1;; ++iter) {
+      c.iter = iter;
+      c.cur_op = -1;
+      int T;
+      if (p.mode == MODE_OFFLINE) {
+        if (blockIdx.x == 0) {
+          consumer_sync();
+          if (c.tid == 0) {
+            int n = 0;
+            if (!aborted(c)) {
+              // sched[4] != 0: the last iteration's outputs have not been appended yet
+              if (p.sched[4] != 0) bookkeep_finish(c);
+              p.sched[4] = 0;
+              if (p.max_iters == 0 || iter <= p.max_iters) {
+                n = bookkeep_prepare(c);
+                if (n > 0) p.sched[4] = 1;
+              }
+            }
+            if (iter - 1 < p.max_step_times) {
+              p.step_times[2 * (iter - 1)] = globaltimer();
+              p.step_times[2 * (iter - 1) + 1] = (unsigned long long)n;
+            }
+            p.sched[3] = iter - 1;
+            p.ctrl[0] = n > 0 ? n : -1;
+            __threadfence();
+          }
+        }
+        grid_sync(c);
+        T = __ldcg(p.ctrl);
+      } else {
+        T = (iter == 1) ? __ldcg(p.qo_indptr + p.max_reqs) : -1;
+        if (T == 0) T = -1;
+      }
+      if (aborted(c)) T = -1;
+      // the whole CTA must agree: take thread 0's view
+      if (c.tid == 0) fl[3] = T;
+      consumer_sync();
+      T = fl[3];
+      consumer_sync();
+      if (T <= 0) break;
+      if (T > 255) T = 255;
+      if (c.tid == 0) fl[0] = (iter << 8) | T;
+
+      for (int oi = 0; oi < p.num_ops; ++oi) {
+        const OpDesc& op = p.ops[oi];
+        c.cur_op = oi;
+        if (op.flags & F_SYNC_BEFORE) grid_sync(c);
+        // once the abort flag is up the op bodies are skipped; the decision is CTA-uniform
+        if (c.tid == 0) fl[3] = aborted(c) ? 1 : 0;
+        consumer_sync();
+        const bool dead = fl[3] != 0;
+        consumer_sync();
+        if (dead) break;
+        if ((op.flags & F_CTA0_ONLY) && blockIdx.x != 0) continue;
+        switch (op.type) {
+          case OP_EMBED: op_embed(c, op, T); break;
+          case OP_RMSNORM: op_rmsnorm(c, op, T); break;
+          case OP_LINEAR: op_linear(c, op, T); break;
+          case OP_ATTN:
+            if (op.aux1 / op.aux0 == 4) op_attention<4>(c, op, T);
+            else if (op.aux1 / op.aux0 == 2) op_attention<2>(c, op, T);
+            else op_attention<8>(c, op, T);
+            break;
+          case OP_SILU_MUL: op_silu_mul(c, op, T); break;
+          case OP_ARGMAX_PARTIAL: op_argmax_partial(c, op, T); break;
+          case OP_ARGMAX_REDUCE: op_argmax_reduce(c, op, T); break;
+          default: break;
+        }
+      }
+      if (p.mode == MODE_ONEPASS) break;
+      if (aborted(c)) {
+        // fall through to the next iteration's uniform abort check
+      }
+    }
+    // the producer may be waiting for the next iteration
+    consumer_sync();
+    if (c.tid == 0) fl[0] = -1;
+  }
+  __syncthreads();
+  // no CTA may exit with a bulk copy still writing its shared memory
+  if (threadIdx.x == 0) {
+    const unsigned issued = (unsigned)fl[1];
+    for (unsigned i = c.cons_idx; i < issued; ++i)
+      mbar_wait(c, c.full_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
+    if (p.mode == MODE_OFFLINE && blockIdx.x == 0 && c.iter - 1 < p.max_step_times) {
+      // closing timestamp
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void init_state_kernel(KParams p) {
+  const int tid = threadIdx.x + blockIdx.x * blockDim.x;
+  const int nth = blockDim.x * gridDim.x;
+  for (int i = tid; i < p.total_requests; i += nth) p.step[i] = 0;
+  for (int i = tid; i < p.max_reqs; i += nth) p.request_ids[i] = -1;
+  for (int i = tid; i <= p.max_reqs; i += nth) {
+    p.qo_indptr[i] = 0;
+    p.kv_indptr[i] = 0;
+  }
+  for (int i = tid; i < p.max_pages; i += nth) p.page_queue[i] = i;
+  if (tid == 0) {
+    p.sched[0] = 0;
+    p.sched[1] = p.max_pages;
+    p.sched[2] = 0;
+    p.sched[3] = 0;
+    p.sched[4] = 0;
+  }
+}
+
+}  // namespace mk
+
+// ------------------------------------------------------------------------------------
+// host-side launch helpers (called by the runtime in mk_runtime.cpp)
+// ------------------------------------------------------------------------------------
+extern "C" int mk_kernel_max_ctas_per_sm(int smem_bytes) {
+  int n = 0;
+  if (cudaFuncSetAttribute(mk::megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mk::megakernel, mk::kNumThreads, smem_bytes) != cudaSuccess) return -1;
+  return n;
+}
+
+extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream) {
+  cudaError_t e = cudaFuncSetAttribute(mk::megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return (int)e;
+  void* args[] = {(void*)p};
+  e = cudaLaunchCooperativeKernel((void*)mk::megakernel, dim3(grid), dim3(mk::kNumThreads), args, (size_t)smem_bytes,
+                                  (cudaStream_t)stream);
+  return (int)e;
+}
+
+extern "C" int mk_kernel_init_state(const mk::KParams* p, void* stream) {
+  mk::init_state_kernel<<<4, 256, 0, (cudaStream_t)stream>>>(*p);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,924 @@
+// Host runtime behind the C ABI: records the operator list, lowers it to the
+// device program (fusing RMSNorm, SiLU*up and the argmax partials into the
+// linear tasks where the intermediate is runtime-owned and has one reader),
+// materialises shuffled weights, encodes TMA descriptors, owns scratch and
+// launches the persistent kernel.
+//
+// Stands in for the reference's Cython binding + task-graph compiler + JIT
+// (python/mirage/_cython/core.pyx:944-1013, src/kernel/graph.cc:338-848,
+// src/kernel/runtime.cc:53-1685, python/mirage/mpk/persistent_kernel.py:2404-2618)
+// and its host launcher (include/mirage/persistent_kernel/persistent_kernel.cuh:1960-2429).
+// There is no code generation: the kernel is compiled ahead of time and reads
+// shapes from the program.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/b200mk.h"
+#include "mk_types.h"
+
+extern "C" int mk_kernel_max_ctas_per_sm(int smem_bytes);
+extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream);
+extern "C" int mk_kernel_init_state(const mk::KParams* p, void* stream);
+
+namespace {
+
+constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
+constexpr int kRedBytes = 8192;
+constexpr int kAttnMaxChunks = 32;
+constexpr int kMaxStepTimes = 16384;
+
+size_t dtype_size(int dt) {
+  switch (dt) {
+    case MK_BF16: case MK_F16: return 2;
+    case MK_F32: case MK_I32: return 4;
+    default: return 8;
+  }
+}
+
+struct Tensor {
+  std::string name;
+  int dtype = MK_BF16;
+  int ndim = 0;
+  int64_t dims[4] = {1, 1, 1, 1};
+  int64_t strides[4] = {1, 1, 1, 1};
+  void* ptr = nullptr;
+  bool owned = false;       // allocated by the runtime
+  bool user = false;        // attached by the caller: contents are observable
+  std::vector<int> src;     // shuffle/fuse sources
+  int groups = 0;
+  bool interleave64 = false;  // two sources laid out as [64 rows of src0 | 64 rows of src1] per tile
+  int readers = 0;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < ndim; ++i) n *= dims[i];
+    return n;
+  }
+  size_t alloc_bytes() const {
+    int64_t m = 1;
+    for (int i = 0; i < ndim; ++i) m = std::max<int64_t>(m, dims[i] * strides[i]);
+    return (size_t)m * dtype_size(dtype);
+  }
+};
+
+struct RecOp {
+  std::string name;
+  std::vector<int> t;
+  std::vector<int64_t> params;
+  int grid[3] = {1, 1, 1};
+  int block[3] = {1, 1, 1};
+};
+
+// A device op before addresses are known: tensor ids instead of pointers.
+struct PlanOp {
+  int type = 0, flags = 0;
+  int in = -1, w = -1, norm_w = -1, res = -1, out = -1;
+  int kc = -1, vc = -1, qn = -1, kn = -1, cos = -1, sin = -1;
+  int n = 0, k = 0, aux0 = 0, aux1 = 0, aux2 = 0, aux3 = 0;
+  int amax_n = 0;
+  std::string note;
+};
+
+bool starts_with(const std::string& s, const char* p) { return s.rfind(p, 0) == 0; }
+
+}  // namespace
+
+struct mk_handle {
+  mk_config cfg{};
+  std::vector<Tensor> tensors;
+  std::vector<RecOp> ops;
+  std::vector<PlanOp> plan;
+  bool planned = false, compiled = false, meta_set = false;
+  std::string err;
+  void* meta[10] = {};
+  int64_t total_requests = 0;
+  int num_sms = 0;
+  int grid = 0, smem_bytes = 0;
+  mk::KParams kp{};
+  std::vector<void*> allocs;
+  int max_nblk = 1;
+  int64_t weight_bytes = 0;
+  bool launched = false;
+
+  int fail(int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    err = buf;
+    return code;
+  }
+  int cuda_fail(cudaError_t e, const char* what) {
+    return fail(MK_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  }
+  int dmalloc(void** p, size_t bytes, bool zero = true) {
+    cudaError_t e = cudaMalloc(p, std::max<size_t>(bytes, 256));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+    allocs.push_back(*p);
+    if (zero) {
+      e = cudaMemset(*p, 0, std::max<size_t>(bytes, 256));
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMemset");
+    }
+    return 0;
+  }
+};
+
+namespace {
+
+bool valid_tensor(mk_handle* h, int id) { return id >= 0 && id < (int)h->tensors.size(); }
+
+int add_tensor(mk_handle* h, const char* name, int dtype, int ndim, const int64_t* dims, const int64_t* strides) {
+  if (!name || ndim < 1 || ndim > 4 || !dims) return h->fail(MK_E_INVALID, "tensor needs a name and 1..4 dims");
+  if (dtype < MK_BF16 || dtype > MK_F16) return h->fail(MK_E_INVALID, "tensor %s: unknown dtype %d", name, dtype);
+  Tensor t;
+  t.name = name;
+  t.dtype = dtype;
+  t.ndim = ndim;
+  int64_t s = 1;
+  for (int i = ndim - 1; i >= 0; --i) {
+    if (dims[i] <= 0) return h->fail(MK_E_INVALID, "tensor %s: dim %d is %lld", name, i, (long long)dims[i]);
+    t.dims[i] = dims[i];
+    t.strides[i] = strides ? strides[i] : s;
+    s *= dims[i];
+  }
+  h->tensors.push_back(t);
+  return (int)h->tensors.size() - 1;
+}
+
+// ------------------------------------------------------------------------------------
+// lowering: recorded layers -> device ops (host only, no CUDA calls)
+// ------------------------------------------------------------------------------------
+bool is_linear(const std::string& n) {
+  return n == "linear" || starts_with(n, "linear_sm100") || n == "linear_with_residual" ||
+         starts_with(n, "linear_with_residual_sm100") || starts_with(n, "linear_swapAB") || n == "rmsnorm_linear";
+}
+
+int check_2d_bf16(mk_handle* h, int id, const char* what) {
+  const Tensor& t = h->tensors[id];
+  if (t.ndim != 2 || t.dtype != MK_BF16)
+    return h->fail(MK_E_INVALID, "%s: tensor %s must be 2-D bf16", what, t.name.c_str());
+  if (t.strides[1] != 1) return h->fail(MK_E_INVALID, "%s: tensor %s must be row-major", what, t.name.c_str());
+  return 0;
+}
+
+int plan_graph(mk_handle* h) {
+  h->plan.clear();
+  h->planned = false;
+  const mk_config& cfg = h->cfg;
+  for (auto& t : h->tensors) {
+    t.readers = 0;
+    t.interleave64 = false;
+  }
+  // operand positions that are read (everything except each layer's outputs)
+  auto n_outputs = [](const RecOp& op) {
+    if (starts_with(op.name, "argmax_partial")) return 2;
+    if (op.name == "paged_attention_split_kv" || starts_with(op.name, "paged_attention_split_kv_sm100")) return 2;
+    return 1;
+  };
+  for (auto& op : h->ops) {
+    const int nout = n_outputs(op);
+    for (int i = 0; i + nout < (int)op.t.size(); ++i)
+      if (valid_tensor(h, op.t[i])) h->tensors[op.t[i]].readers++;
+  }
+  const bool fuse = cfg.fuse != 0;
+  const int nops_all = (int)h->ops.size();
+  // True when the value layer `i` writes into tensor `tid` is read by layer i+1 only:
+  // walk the layers in execution order (wrapping into the next iteration) until the
+  // tensor is written again.
+  auto only_next_reads = [&](int i, int tid) {
+    if (!h->tensors[tid].owned) return false;  // caller-visible tensors are always written
+    for (int step = 1; step < nops_all; ++step) {
+      const RecOp& o = h->ops[(i + step) % nops_all];
+      const int nout = n_outputs(o);
+      const int nin = (int)o.t.size() - nout;
+      bool reads = false, writes = false;
+      for (int a = 0; a < (int)o.t.size(); ++a) {
+        if (o.t[a] != tid) continue;
+        if (a < nin) reads = true; else writes = true;
+      }
+      if (reads && step != 1) return false;
+      if (writes) return true;
+    }
+    return true;
+  };
+  int pending_norm_in = -1, pending_norm_w = -1, pending_norm_out = -1;
+  const int nops = (int)h->ops.size();
+  for (int i = 0; i < nops; ++i) {
+    const RecOp& op = h->ops[i];
+    const std::string& nm = op.name;
+    for (int id : op.t)
+      if (!valid_tensor(h, id)) return h->fail(MK_E_INVALID, "layer %d (%s): bad tensor id %d", i, nm.c_str(), id);
+    PlanOp po;
+    if (nm == "embedding") {
+      if (op.t.size() != 3) return h->fail(MK_E_INVALID, "embedding takes (input, weight, output)");
+      const Tensor &ids = h->tensors[op.t[0]], &w = h->tensors[op.t[1]], &out = h->tensors[op.t[2]];
+      if (ids.dtype != MK_I64) return h->fail(MK_E_INVALID, "embedding: token ids must be int64");
+      if (int e = check_2d_bf16(h, op.t[1], "embedding")) return e;
+      if (int e = check_2d_bf16(h, op.t[2], "embedding")) return e;
+      if (w.dims[1] != out.dims[1] || w.dims[1] % 8) return h->fail(MK_E_INVALID, "embedding: hidden size mismatch");
+      po.type = mk::OP_EMBED;
+      po.in = op.t[0]; po.w = op.t[1]; po.out = op.t[2];
+      po.n = (int)w.dims[1];
+      po.aux0 = (int)w.dims[0];
+    } else if (nm == "rmsnorm" || nm == "rmsnorm_hopper") {
+      if (op.t.size() != 3) return h->fail(MK_E_INVALID, "rmsnorm takes (input, weight, output)");
+      if (int e = check_2d_bf16(h, op.t[0], "rmsnorm")) return e;
+      if (int e = check_2d_bf16(h, op.t[2], "rmsnorm")) return e;
+      const Tensor &in = h->tensors[op.t[0]], &w = h->tensors[op.t[1]], &out = h->tensors[op.t[2]];
+      if (w.numel() != in.dims[1] || out.dims[1] != in.dims[1] || in.dims[1] % 8)
+        return h->fail(MK_E_INVALID, "rmsnorm: shape mismatch on %s", in.name.c_str());
+      // fuse into the next linear when the normalised rows are only an intermediate
+      if (fuse && i + 1 < nops && is_linear(h->ops[i + 1].name) && h->ops[i + 1].name != "rmsnorm_linear" &&
+          h->ops[i + 1].t[0] == op.t[2] && only_next_reads(i, op.t[2])) {
+        pending_norm_in = op.t[0];
+        pending_norm_w = op.t[1];
+        pending_norm_out = op.t[2];
+        continue;
+      }
+      po.type = mk::OP_RMSNORM;
+      po.in = op.t[0]; po.w = op.t[1]; po.out = op.t[2];
+      po.n = (int)in.dims[1];
+    } else if (is_linear(nm)) {
+      const bool rl = nm == "rmsnorm_linear";
+      const bool with_res = nm.find("with_residual") != std::string::npos;
+      const size_t want = rl ? 4 : (with_res ? 4 : 3);
+      if (op.t.size() != want) return h->fail(MK_E_INVALID, "%s: expected %zu tensors", nm.c_str(), want);
+      int in = op.t[0], w = rl ? op.t[2] : op.t[1], res = with_res ? op.t[2] : -1, out = op.t.back();
+      if (int e = check_2d_bf16(h, in, nm.c_str())) return e;
+      if (int e = check_2d_bf16(h, w, nm.c_str())) return e;
+      if (int e = check_2d_bf16(h, out, nm.c_str())) return e;
+      const Tensor &tw = h->tensors[w], &tin = h->tensors[in], &tout = h->tensors[out];
+      if (tw.dims[1] != tin.dims[1]) return h->fail(MK_E_INVALID, "%s: K mismatch (%s vs %s)", nm.c_str(), tw.name.c_str(), tin.name.c_str());
+      if (tw.dims[0] != tout.dims[1]) return h->fail(MK_E_INVALID, "%s: N mismatch (%s vs %s)", nm.c_str(), tw.name.c_str(), tout.name.c_str());
+      if (tw.dims[1] % 8 || tw.strides[0] % 8) return h->fail(MK_E_INVALID, "%s: K and the weight pitch must be multiples of 8", nm.c_str());
+      po.type = mk::OP_LINEAR;
+      po.in = in; po.w = w; po.out = out; po.res = res;
+      po.n = (int)tw.dims[0];
+      po.k = (int)tw.dims[1];
+      if (with_res) {
+        if (int e = check_2d_bf16(h, res, nm.c_str())) return e;
+        po.flags |= mk::F_RESIDUAL;
+        if (cfg.world_size > 1) po.flags |= mk::F_RES_RANK0;  // row-parallel partial sums: add the residual once
+      }
+      if (rl) {
+        po.flags |= mk::F_NORM_IN;
+        po.norm_w = op.t[1];
+      } else if (pending_norm_out == in) {
+        po.flags |= mk::F_NORM_IN;
+        po.norm_w = pending_norm_w;
+        po.in = pending_norm_in;
+        po.note = "rmsnorm fused";
+      }
+      pending_norm_in = pending_norm_w = pending_norm_out = -1;
+      // SiLU*up fused into the epilogue of a gate/up linear
+      if (fuse && !with_res && i + 1 < nops && h->ops[i + 1].name == "silu_mul" && h->ops[i + 1].t.size() == 2 &&
+          h->ops[i + 1].t[0] == out && only_next_reads(i, out) && tw.src.size() == 2 && tw.owned) {
+        const RecOp& sm = h->ops[i + 1];
+        const Tensor& so = h->tensors[sm.t[1]];
+        const int64_t inter = so.dims[1];
+        const int64_t blk = inter / std::max(1, sm.grid[0]);
+        const Tensor &g = h->tensors[tw.src[0]], &u = h->tensors[tw.src[1]];
+        if (g.dims[0] == inter && u.dims[0] == inter && inter % 64 == 0 && tw.groups > 0 && inter / tw.groups == blk &&
+            inter % std::max(1, sm.grid[0]) == 0) {
+          po.flags |= mk::F_SILU_MUL;
+          po.out = sm.t[1];
+          po.note += po.note.empty() ? "silu_mul fused" : ", silu_mul fused";
+          h->tensors[w].interleave64 = true;
+          ++i;
+        }
+      }
+      // per-tile argmax partials fused into the LM-head epilogue
+      if (fuse && !(po.flags & mk::F_SILU_MUL) && i + 2 < nops && starts_with(h->ops[i + 1].name, "argmax_partial") &&
+          starts_with(h->ops[i + 2].name, "argmax_reduce") && h->ops[i + 1].t[0] == out) {
+        po.flags |= mk::F_ARGMAX;
+        po.amax_n = (po.n + mk::kTileRows - 1) / mk::kTileRows;
+        po.note += po.note.empty() ? "argmax partials fused" : ", argmax partials fused";
+        h->plan.push_back(po);
+        PlanOp rd;
+        rd.type = mk::OP_ARGMAX_REDUCE;
+        rd.flags = mk::F_CTA0_ONLY;
+        rd.out = h->ops[i + 2].t.back();
+        rd.amax_n = po.amax_n;
+        rd.in = -2;  // reads the previous op's partials
+        if (h->tensors[rd.out].dtype != MK_I64) return h->fail(MK_E_INVALID, "argmax output must be int64");
+        h->plan.push_back(rd);
+        i += 2;
+        continue;
+      }
+    } else if (nm == "paged_attention" || starts_with(nm, "paged_attention_sm100") ||
+               nm == "paged_attention_split_kv" || starts_with(nm, "paged_attention_split_kv_sm100")) {
+      const bool split = nm.find("split_kv") != std::string::npos;
+      if (op.t.size() != (split ? 9u : 8u)) return h->fail(MK_E_INVALID, "%s: wrong operand count", nm.c_str());
+      int out = op.t[7];
+      if (split) {
+        if (i + 1 >= nops || !starts_with(h->ops[i + 1].name, "paged_attention_split_kv_merge"))
+          return h->fail(MK_E_UNSUPPORTED, "paged_attention_split_kv must be followed by its merge layer");
+        const RecOp& mg = h->ops[i + 1];
+        if (mg.t.size() != 3) return h->fail(MK_E_INVALID, "split_kv merge takes (lse, output_tmp, output)");
+        out = mg.t[2];
+      }
+      if (op.params.size() < 4) return h->fail(MK_E_INVALID, "%s: params (q heads, kv heads, qk_norm, rope) missing", nm.c_str());
+      po.type = mk::OP_ATTN;
+      po.in = op.t[0]; po.kc = op.t[1]; po.vc = op.t[2]; po.qn = op.t[3]; po.kn = op.t[4];
+      po.cos = op.t[5]; po.sin = op.t[6]; po.out = out;
+      po.aux1 = (int)op.params[0];
+      po.aux0 = (int)op.params[1];
+      if (op.params[2]) po.flags |= mk::F_QK_NORM;
+      if (op.params[3]) po.flags |= mk::F_ROPE;
+      const Tensor &kc = h->tensors[po.kc], &qkv = h->tensors[po.in], &to = h->tensors[out];
+      if (kc.ndim != 4 || kc.dims[3] != mk::kHeadDim) return h->fail(MK_E_UNSUPPORTED, "attention: head_dim must be 128");
+      if (kc.dims[0] != cfg.max_num_pages || kc.dims[1] != cfg.page_size || kc.dims[2] != po.aux0)
+        return h->fail(MK_E_INVALID, "attention: KV cache must be [max_num_pages, page_size, kv_heads, 128]");
+      const int qpk = po.aux0 > 0 ? po.aux1 / po.aux0 : 0;
+      if (po.aux0 <= 0 || po.aux1 % po.aux0 || (qpk != 2 && qpk != 4 && qpk != 8))
+        return h->fail(MK_E_UNSUPPORTED, "attention: q heads per kv head must be 2, 4 or 8");
+      if (qkv.dims[1] != (int64_t)(po.aux1 + 2 * po.aux0) * mk::kHeadDim || to.dims[1] != (int64_t)po.aux1 * mk::kHeadDim)
+        return h->fail(MK_E_INVALID, "attention: qkv/output widths do not match the head counts");
+      po.aux2 = (int)h->tensors[po.cos].dims[0];
+      if (split) { po.note = "split-kv + merge"; ++i; }
+    } else if (starts_with(nm, "paged_attention_split_kv_merge")) {
+      return h->fail(MK_E_UNSUPPORTED, "split_kv merge without a preceding split_kv layer");
+    } else if (nm == "silu_mul") {
+      if (op.t.size() != 2) return h->fail(MK_E_INVALID, "silu_mul takes (input, output)");
+      if (int e = check_2d_bf16(h, op.t[0], "silu_mul")) return e;
+      if (int e = check_2d_bf16(h, op.t[1], "silu_mul")) return e;
+      const Tensor &in = h->tensors[op.t[0]], &out = h->tensors[op.t[1]];
+      const int64_t blk = out.dims[1] / std::max(1, op.grid[0]);
+      if (in.dims[1] != 2 * out.dims[1] || blk * op.grid[0] != out.dims[1] || blk % 8)
+        return h->fail(MK_E_INVALID, "silu_mul: input must be [gate|up] blocks of a multiple of 8 columns");
+      po.type = mk::OP_SILU_MUL;
+      po.in = op.t[0]; po.out = op.t[1];
+      po.n = (int)out.dims[1];
+      po.aux0 = (int)blk;
+    } else if (starts_with(nm, "argmax_partial") || nm == "argmax") {
+      const bool single = nm == "argmax";
+      if (!single && (i + 1 >= nops || !starts_with(h->ops[i + 1].name, "argmax_reduce")))
+        return h->fail(MK_E_UNSUPPORTED, "argmax_partial must be followed by argmax_reduce");
+      if (int e = check_2d_bf16(h, op.t[0], "argmax")) return e;
+      const int out = single ? op.t[1] : h->ops[i + 1].t.back();
+      if (h->tensors[out].dtype != MK_I64) return h->fail(MK_E_INVALID, "argmax output must be int64");
+      po.type = mk::OP_ARGMAX_PARTIAL;
+      po.in = op.t[0];
+      po.n = (int)h->tensors[op.t[0]].dims[1];
+      po.amax_n = std::max(1, std::min(po.n / 256, 1024));
+      h->plan.push_back(po);
+      PlanOp rd;
+      rd.type = mk::OP_ARGMAX_REDUCE;
+      rd.flags = mk::F_CTA0_ONLY;
+      rd.out = out;
+      rd.amax_n = po.amax_n;
+      rd.in = -2;
+      h->plan.push_back(rd);
+      if (!single) ++i;
+      continue;
+    } else if (starts_with(nm, "argmax_reduce")) {
+      return h->fail(MK_E_UNSUPPORTED, "argmax_reduce without a preceding argmax_partial");
+    } else if (nm == "allreduce") {
+      return h->fail(MK_E_UNSUPPORTED, "allreduce: tensor-parallel exchange is not built in this library version");
+    } else {
+      return h->fail(MK_E_UNSUPPORTED, "unknown layer '%s'", nm.c_str());
+    }
+    if (pending_norm_out >= 0 && po.type != 0) {
+      return h->fail(MK_E_STATE, "internal: a fused rmsnorm lost its linear");
+    }
+    h->plan.push_back(po);
+  }
+  // every op waits for its producers; CTA-0-only ops that follow each other need no grid barrier
+  for (size_t i = 0; i < h->plan.size(); ++i) h->plan[i].flags |= mk::F_SYNC_BEFORE;
+  if (h->plan.empty()) return h->fail(MK_E_INVALID, "no layers recorded");
+  // the first op follows the iteration's own barrier (offline) or the launch (onepass)
+  h->plan[0].flags &= ~mk::F_SYNC_BEFORE;
+  h->planned = true;
+  return 0;
+}
+
+const char* op_type_name(int t) {
+  switch (t) {
+    case mk::OP_EMBED: return "embed";
+    case mk::OP_RMSNORM: return "rmsnorm";
+    case mk::OP_LINEAR: return "linear";
+    case mk::OP_ATTN: return "attention";
+    case mk::OP_SILU_MUL: return "silu_mul";
+    case mk::OP_ARGMAX_PARTIAL: return "argmax_partial";
+    case mk::OP_ARGMAX_REDUCE: return "argmax_reduce";
+    case mk::OP_ALLREDUCE: return "allreduce";
+  }
+  return "?";
+}
+
+// ------------------------------------------------------------------------------------
+// device side of compile
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int materialise_shuffle(mk_handle* h, Tensor& t) {
+  // rows of the sources, interleaved per group; every source is a full-row 2-D bf16 tensor
+  const size_t row_bytes = (size_t)t.dims[1] * dtype_size(t.dtype);
+  size_t dst_row = 0;
+  auto copy_rows = [&](const Tensor& s, int64_t r0, int64_t nr) -> int {
+    const char* sp = (const char*)s.ptr + (size_t)r0 * s.strides[0] * dtype_size(s.dtype);
+    cudaError_t e;
+    if (s.strides[0] == s.dims[1])
+      e = cudaMemcpyAsync((char*)t.ptr + dst_row * row_bytes, sp, (size_t)nr * row_bytes, cudaMemcpyDeviceToDevice, 0);
+    else
+      e = cudaMemcpy2DAsync((char*)t.ptr + dst_row * row_bytes, row_bytes, sp, (size_t)s.strides[0] * dtype_size(s.dtype),
+                            row_bytes, (size_t)nr, cudaMemcpyDeviceToDevice, 0);
+    dst_row += nr;
+    return e == cudaSuccess ? 0 : h->cuda_fail(e, "shuffle copy");
+  };
+  if (t.interleave64) {
+    const Tensor &a = h->tensors[t.src[0]], &b = h->tensors[t.src[1]];
+    for (int64_t r = 0; r < a.dims[0]; r += 64) {
+      if (int e = copy_rows(a, r, 64)) return e;
+      if (int e = copy_rows(b, r, 64)) return e;
+    }
+  } else {
+    for (int g = 0; g < t.groups; ++g)
+      for (int sid : t.src) {
+        const Tensor& s = h->tensors[sid];
+        const int64_t per = s.dims[0] / t.groups;
+        if (int e = copy_rows(s, g * per, per)) return e;
+      }
+  }
+  return 0;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------
+extern "C" {
+
+mk_handle* mk_create(const mk_config* cfg) {
+  if (!cfg) return nullptr;
+  mk_handle* h = new mk_handle();
+  h->cfg = *cfg;
+  if (h->cfg.timeout_ms <= 0) h->cfg.timeout_ms = 4000;
+  return h;
+}
+
+int mk_last_error(mk_handle* h, char* buf, int n) {
+  if (!h || !buf || n <= 0) return MK_E_INVALID;
+  snprintf(buf, n, "%s", h->err.c_str());
+  return 0;
+}
+
+int mk_tensor_attach(mk_handle* h, const char* name, void* ptr, int dtype, int ndim, const int64_t* dims,
+                     const int64_t* strides) {
+  if (!h) return MK_E_INVALID;
+  if (h->planned) return h->fail(MK_E_STATE, "graph already compiled");
+  if (!ptr) return h->fail(MK_E_INVALID, "attach_input %s: null pointer", name ? name : "?");
+  if (((uintptr_t)ptr) & 15) return h->fail(MK_E_INVALID, "attach_input %s: pointer must be 16-byte aligned", name);
+  if (strides)
+    for (int d = 0; d + 1 < ndim; ++d)
+      if (strides[d] != strides[d + 1] * dims[d + 1])
+        return h->fail(MK_E_INVALID, "attach_input %s: tensor must be row-major contiguous", name);
+  int id = add_tensor(h, name, dtype, ndim, dims, strides);
+  if (id < 0) return id;
+  h->tensors[id].ptr = ptr;
+  h->tensors[id].user = true;
+  return id;
+}
+
+int mk_tensor_new(mk_handle* h, const char* name, int dtype, int ndim, const int64_t* dims, const int64_t* strides,
+                  int category) {
+  if (!h) return MK_E_INVALID;
+  if (h->planned) return h->fail(MK_E_STATE, "graph already compiled");
+  if (category != MK_CAT_CUDA && category != MK_CAT_SYMMETRIC) return h->fail(MK_E_INVALID, "Invalid io_category");
+  int id = add_tensor(h, name, dtype, ndim, dims, strides);
+  if (id < 0) return id;
+  h->tensors[id].owned = true;
+  return id;
+}
+
+static int shuffle_impl(mk_handle* h, const char* name, const int* ids, int n, int dim, int groups) {
+  if (!h) return MK_E_INVALID;
+  if (h->planned) return h->fail(MK_E_STATE, "graph already compiled");
+  if (dim != 0) return h->fail(MK_E_UNSUPPORTED, "only dimension 0 can be shuffled");
+  if (n < 1 || groups < 1 || !ids) return h->fail(MK_E_INVALID, "shuffle_tensors: need inputs and num_groups >= 1");
+  int64_t rows = 0, cols = -1;
+  for (int i = 0; i < n; ++i) {
+    if (!valid_tensor(h, ids[i])) return h->fail(MK_E_INVALID, "shuffle_tensors: bad tensor id");
+    const Tensor& s = h->tensors[ids[i]];
+    if (s.ndim != 2) return h->fail(MK_E_INVALID, "shuffle_tensors: inputs must be 2-D");
+    if (cols >= 0 && s.dims[1] != cols) return h->fail(MK_E_INVALID, "shuffle_tensors: column counts differ");
+    if (s.dims[0] % groups) return h->fail(MK_E_INVALID, "shuffle_tensors: rows of %s not divisible by num_groups", s.name.c_str());
+    if (s.dtype != h->tensors[ids[0]].dtype) return h->fail(MK_E_INVALID, "shuffle_tensors: dtypes differ");
+    cols = s.dims[1];
+    rows += s.dims[0];
+  }
+  int64_t dims[2] = {rows, cols};
+  int id = add_tensor(h, name ? name : "shuffled", h->tensors[ids[0]].dtype, 2, dims, nullptr);
+  if (id < 0) return id;
+  Tensor& t = h->tensors[id];
+  t.owned = true;
+  t.src.assign(ids, ids + n);
+  t.groups = groups;
+  return id;
+}
+
+int mk_tensor_shuffle(mk_handle* h, const char* name, const int* ids, int n, int dim, int groups) {
+  return shuffle_impl(h, name, ids, n, dim, groups);
+}
+int mk_tensor_fuse(mk_handle* h, const char* name, const int* ids, int n, int dim, int groups) {
+  return shuffle_impl(h, name, ids, n, dim, groups);
+}
+
+int mk_op(mk_handle* h, const char* op_name, const int* ids, int n, const int64_t* params, int np, const int* grid,
+          const int* block) {
+  if (!h) return MK_E_INVALID;
+  if (h->planned) return h->fail(MK_E_STATE, "graph already compiled");
+  if (!op_name || n < 1 || !ids) return h->fail(MK_E_INVALID, "mk_op: name and tensors required");
+  RecOp op;
+  op.name = op_name;
+  op.t.assign(ids, ids + n);
+  if (params && np > 0) op.params.assign(params, params + np);
+  for (int i = 0; i < 3; ++i) {
+    op.grid[i] = grid ? std::max(1, grid[i]) : 1;
+    op.block[i] = block ? std::max(1, block[i]) : 1;
+  }
+  h->ops.push_back(op);
+  return (int)h->ops.size() - 1;
+}
+
+int mk_set_meta(mk_handle* h, void* const meta[10], int64_t total_num_requests, void* profiler) {
+  (void)profiler;
+  if (!h || !meta) return MK_E_INVALID;
+  for (int i = 0; i < 10; ++i) {
+    if (!meta[i]) return h->fail(MK_E_INVALID, "meta tensor %d is null", i);
+    h->meta[i] = meta[i];
+  }
+  if (total_num_requests < 1) return h->fail(MK_E_INVALID, "total_num_requests must be >= 1");
+  h->total_requests = total_num_requests;
+  h->meta_set = true;
+  return 0;
+}
+
+int mk_plan(mk_handle* h) {
+  if (!h) return MK_E_INVALID;
+  const mk_config& c = h->cfg;
+  if (c.mode != MK_MODE_OFFLINE && c.mode != MK_MODE_ONEPASS) return h->fail(MK_E_INVALID, "Invalid persistent kernel mode");
+  if (c.max_num_batched_requests < 1 || c.max_num_batched_tokens < c.max_num_batched_requests)
+    return h->fail(MK_E_INVALID, "max_num_batched_tokens must be >= max_num_batched_requests >= 1");
+  if (c.max_num_batched_tokens > 128) return h->fail(MK_E_UNSUPPORTED, "at most 128 batched tokens");
+  if (c.page_size < 1 || c.max_num_pages < 1 || c.max_seq_length < 2) return h->fail(MK_E_INVALID, "bad paging/sequence limits");
+  if (c.world_size < 1 || c.rank < 0 || c.rank >= c.world_size) return h->fail(MK_E_INVALID, "bad rank/world_size");
+  return plan_graph(h);
+}
+
+int mk_num_device_ops(mk_handle* h) { return h && h->planned ? (int)h->plan.size() : MK_E_STATE; }
+
+int mk_describe(mk_handle* h, char* buf, int n) {
+  if (!h || !buf || n <= 0) return MK_E_INVALID;
+  if (!h->planned) return h->fail(MK_E_STATE, "not planned");
+  std::string s;
+  char line[512];
+  for (size_t i = 0; i < h->plan.size(); ++i) {
+    const PlanOp& p = h->plan[i];
+    snprintf(line, sizeof(line), "%zu %s n=%d k=%d flags=0x%x in=%s out=%s%s%s\n", i, op_type_name(p.type), p.n, p.k,
+             p.flags, p.in >= 0 ? h->tensors[p.in].name.c_str() : "-", p.out >= 0 ? h->tensors[p.out].name.c_str() : "-",
+             p.note.empty() ? "" : " # ", p.note.c_str());
+    s += line;
+  }
+  snprintf(buf, n, "%s", s.c_str());
+  return (int)h->plan.size();
+}
+
+int mk_grid_size(mk_handle* h) { return h && h->compiled ? h->grid : MK_E_STATE; }
+int64_t mk_weight_bytes_per_step(mk_handle* h) { return h && h->compiled ? h->weight_bytes : MK_E_STATE; }
+
+void* mk_tensor_ptr(mk_handle* h, int id) {
+  if (!h || !valid_tensor(h, id)) return nullptr;
+  return h->tensors[id].ptr;
+}
+
+int mk_tensor_read(mk_handle* h, int id, void* host_buf, int64_t bytes) {
+  if (!h || !host_buf || !valid_tensor(h, id)) return MK_E_INVALID;
+  const Tensor& t = h->tensors[id];
+  if (!t.ptr) return h->fail(MK_E_STATE, "tensor %s has no storage before compile", t.name.c_str());
+  if (bytes < 0 || (size_t)bytes > t.alloc_bytes()) return h->fail(MK_E_INVALID, "tensor %s holds %zu bytes", t.name.c_str(), t.alloc_bytes());
+  cudaError_t ce = cudaMemcpy(host_buf, t.ptr, (size_t)bytes, cudaMemcpyDeviceToHost);
+  return ce == cudaSuccess ? 0 : h->cuda_fail(ce, "tensor readback");
+}
+
+int mk_debug_partition(int64_t nblk, int64_t nkt, int grid, int64_t* begin_out, int* owner_check) {
+  if (nblk < 1 || nkt < 1 || grid < 1 || !begin_out) return MK_E_INVALID;
+  const long long total = nblk * nkt;
+  for (int c = 0; c <= grid; ++c) begin_out[c] = mk::tile_begin(c, total, grid);
+  int bad = 0;
+  for (long long t = 0; t < total; ++t) {
+    const int o = mk::tile_owner(t, total, grid);
+    if (o < 0 || o >= grid || t < begin_out[o] || t >= begin_out[o + 1]) ++bad;
+  }
+  if (owner_check) *owner_check = bad;
+  return 0;
+}
+
+int mk_compile(mk_handle* h) {
+  if (!h) return MK_E_INVALID;
+  if (h->compiled) return h->fail(MK_E_STATE, "already compiled");
+  if (!h->meta_set) return h->fail(MK_E_STATE, "mk_set_meta must be called before mk_compile");
+  if (int e = mk_plan(h)) return e;
+  const mk_config& cfg = h->cfg;
+  cudaError_t ce;
+  int dev = cfg.device;
+  if (dev < 0) {
+    if ((ce = cudaGetDevice(&dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDevice (is a CUDA device present?)");
+  } else if ((ce = cudaSetDevice(dev)) != cudaSuccess) {
+    return h->cuda_fail(ce, "cudaSetDevice");
+  }
+  cudaDeviceProp prop;
+  if ((ce = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDeviceProperties");
+  if (prop.major != 10) return h->fail(MK_E_UNSUPPORTED, "this library only runs on sm_100 (found sm_%d%d)", prop.major, prop.minor);
+  if (!prop.cooperativeLaunch) return h->fail(MK_E_UNSUPPORTED, "device lacks cooperative launch");
+  h->num_sms = prop.multiProcessorCount;
+
+  // 1. runtime-owned tensors (shuffles are filled below)
+  for (auto& t : h->tensors)
+    if (t.owned && !t.ptr)
+      if (int e = h->dmalloc(&t.ptr, t.alloc_bytes())) return e;
+  for (auto& t : h->tensors)
+    if (!t.src.empty())
+      if (int e = materialise_shuffle(h, t)) return e;
+  if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return h->cuda_fail(ce, "shuffle copies");
+
+  // 2. shared-memory carve-up
+  const int tb_max = std::min(mk::kMaxTokGroup, cfg.max_num_batched_tokens);
+  int x_bytes = cfg.max_num_pages * 4;
+  int max_nblk = 1, n_linear = 0;
+  for (const PlanOp& p : h->plan) {
+    if (p.type == mk::OP_LINEAR) {
+      const int kp = (p.k + mk::kTileK - 1) / mk::kTileK * mk::kTileK;
+      x_bytes = std::max(x_bytes, tb_max * kp * 2);
+      max_nblk = std::max(max_nblk, (p.n + mk::kTileRows - 1) / mk::kTileRows);
+      ++n_linear;
+    } else if (p.type == mk::OP_RMSNORM) {
+      x_bytes = std::max(x_bytes, (p.n + 63) / 64 * 64 * 2);
+    } else if (p.type == mk::OP_ATTN) {
+      const int qpk = p.aux1 / p.aux0;
+      x_bytes = std::max(x_bytes, 16 * qpk * (mk::kHeadDim + 2) * 4);
+    }
+  }
+  x_bytes = (x_bytes + 1023) / 1024 * 1024;
+  const int fixed = 1024 /*alignment slack*/ + x_bytes + kRedBytes + 1024 /*barriers, flags*/;
+  int stages = (kMaxSmem - fixed) / mk::kStageBytes;
+  stages = std::min(stages, 24);
+  if (stages < 2) return h->fail(MK_E_UNSUPPORTED, "activations need %d bytes of shared memory; too large for the CUDA-core path", x_bytes);
+  mk::KParams& kp = h->kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.num_stages = stages;
+  kp.x_off = stages * mk::kStageBytes;
+  kp.x_bytes = x_bytes;
+  kp.red_off = kp.x_off + x_bytes;
+  kp.bar_off = kp.red_off + kRedBytes;
+  h->smem_bytes = kp.bar_off + 1024 + 1024;
+  const int per_sm = mk_kernel_max_ctas_per_sm(h->smem_bytes);
+  if (per_sm < 1) return h->fail(MK_E_CUDA, "the megakernel does not fit on an SM with %d bytes of shared memory", h->smem_bytes);
+  h->grid = h->num_sms;
+  if (cfg.num_workers > 0) h->grid = std::min(h->grid, cfg.num_workers);
+  h->max_nblk = max_nblk;
+
+  // 3. scratch and state
+  const int G = h->grid;
+  const int groups = (cfg.max_num_batched_tokens + mk::kMaxTokGroup - 1) / mk::kMaxTokGroup;
+  void* p = nullptr;
+  if (int e = h->dmalloc(&p, (size_t)groups * G * 2 * mk::kTileRows * mk::kMaxTokGroup * 4)) return e;
+  kp.partial = (float*)p;
+  if (int e = h->dmalloc(&p, (size_t)groups * max_nblk * 4)) return e;
+  kp.piece_count = (unsigned*)p;
+  kp.piece_stride = max_nblk;
+  int max_hkv = 1, max_qpk = 2;
+  for (const PlanOp& po : h->plan)
+    if (po.type == mk::OP_ATTN) {
+      max_hkv = std::max(max_hkv, po.aux0);
+      max_qpk = std::max(max_qpk, po.aux1 / po.aux0);
+    }
+  kp.attn_max_chunks = kAttnMaxChunks;
+  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_tokens * max_hkv * kAttnMaxChunks * max_qpk * (mk::kHeadDim + 2) * 4)) return e;
+  kp.attn_part = (float*)p;
+  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_tokens * max_hkv * 4)) return e;
+  kp.attn_count = (unsigned*)p;
+  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_requests * 4)) return e;
+  kp.request_ids = (int*)p;
+  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_pages * 4)) return e;
+  kp.page_queue = (int*)p;
+  if (int e = h->dmalloc(&p, 256)) return e;
+  kp.sched = (int*)p;
+  kp.grid_bar = (unsigned*)p + 16;
+  kp.ctrl = (int*)p + 20;
+  kp.abort_flag = (int*)p + 24;
+  kp.status = (int*)p + 32;
+  if (int e = h->dmalloc(&p, (size_t)kMaxStepTimes * 16)) return e;
+  kp.step_times = (unsigned long long*)p;
+  kp.max_step_times = kMaxStepTimes;
+
+  // 4. the program
+  std::vector<mk::OpDesc> descs(h->plan.size());
+  std::vector<CUtensorMap> maps;
+  std::vector<int> map_of(h->plan.size(), -1);
+  EncodeTiledFn encode = get_encode_fn();
+  if (n_linear && !encode) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  auto tp = [&](int id) -> void* { return id >= 0 ? h->tensors[id].ptr : nullptr; };
+  auto ld = [&](int id) -> int { return id >= 0 ? (int)h->tensors[id].strides[0] : 0; };
+  h->weight_bytes = 0;
+  float* last_amax_val = nullptr;
+  int* last_amax_idx = nullptr;
+  for (size_t i = 0; i < h->plan.size(); ++i) {
+    const PlanOp& po = h->plan[i];
+    mk::OpDesc& d = descs[i];
+    memset(&d, 0, sizeof(d));
+    d.type = po.type;
+    d.flags = po.flags;
+    d.n = po.n;
+    d.k = po.k;
+    d.aux0 = po.aux0; d.aux1 = po.aux1; d.aux2 = po.aux2; d.aux3 = po.aux3;
+    d.in = tp(po.in);
+    d.w = tp(po.w);
+    d.norm_w = tp(po.norm_w);
+    d.res = tp(po.res);
+    d.out = tp(po.out);
+    d.ld_in = ld(po.in);
+    d.ld_out = ld(po.out);
+    d.ld_res = ld(po.res);
+    d.amax_n = po.amax_n;
+    if (po.type == mk::OP_EMBED) {
+      d.ld_res = ld(po.w);
+      d.ld_in = (int)h->tensors[po.in].strides[0];
+    } else if (po.type == mk::OP_LINEAR) {
+      const Tensor& w = h->tensors[po.w];
+      d.nblk = (po.n + mk::kTileRows - 1) / mk::kTileRows;
+      d.nkt = (po.k + mk::kTileK - 1) / mk::kTileK;
+      CUtensorMap m;
+      cuuint64_t gdim[2] = {(cuuint64_t)po.k, (cuuint64_t)po.n};
+      cuuint64_t gstr[1] = {(cuuint64_t)w.strides[0] * 2};
+      cuuint32_t box[2] = {(cuuint32_t)mk::kTileK, (cuuint32_t)mk::kTileRows};
+      cuuint32_t estr[2] = {1, 1};
+      if (((uintptr_t)w.ptr) & 15) return h->fail(MK_E_INVALID, "weight %s is not 16-byte aligned", w.name.c_str());
+      CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w.ptr, gdim, gstr, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %s [%d x %d]", (int)r, w.name.c_str(), po.n, po.k);
+      map_of[i] = (int)maps.size();
+      maps.push_back(m);
+      h->weight_bytes += (int64_t)d.nblk * d.nkt * mk::kStageBytes;
+      if (po.flags & mk::F_ARGMAX) {
+        void* q = nullptr;
+        if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+        d.amax_val = last_amax_val = (float*)q;
+        if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+        d.amax_idx = last_amax_idx = (int*)q;
+      }
+    } else if (po.type == mk::OP_ATTN) {
+      d.k_cache = tp(po.kc);
+      d.v_cache = tp(po.vc);
+      d.q_norm_w = tp(po.qn);
+      d.k_norm_w = tp(po.kn);
+      d.cos = tp(po.cos);
+      d.sin = tp(po.sin);
+    } else if (po.type == mk::OP_ARGMAX_PARTIAL) {
+      void* q = nullptr;
+      if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+      d.amax_val = last_amax_val = (float*)q;
+      if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+      d.amax_idx = last_amax_idx = (int*)q;
+    } else if (po.type == mk::OP_ARGMAX_REDUCE) {
+      d.amax_val = last_amax_val;
+      d.amax_idx = last_amax_idx;
+      d.ld_out = (int)h->tensors[po.out].strides[0];
+    }
+  }
+  if (!maps.empty()) {
+    if (int e = h->dmalloc(&p, maps.size() * sizeof(CUtensorMap), false)) return e;
+    if ((ce = cudaMemcpy(p, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice)) != cudaSuccess)
+      return h->cuda_fail(ce, "tensor map upload");
+    for (size_t i = 0; i < descs.size(); ++i)
+      if (map_of[i] >= 0) descs[i].tmap_w = (const char*)p + (size_t)map_of[i] * sizeof(CUtensorMap);
+  }
+  if (int e = h->dmalloc(&p, descs.size() * sizeof(mk::OpDesc), false)) return e;
+  if ((ce = cudaMemcpy(p, descs.data(), descs.size() * sizeof(mk::OpDesc), cudaMemcpyHostToDevice)) != cudaSuccess)
+    return h->cuda_fail(ce, "program upload");
+  kp.ops = (const mk::OpDesc*)p;
+  kp.num_ops = (int)descs.size();
+
+  kp.mode = cfg.mode;
+  kp.numerics = cfg.numerics;
+  kp.rank = cfg.rank;
+  kp.world = cfg.world_size;
+  kp.step = (int*)h->meta[0];
+  kp.tokens = (long long*)h->meta[1];
+  kp.input_tokens = (long long*)h->meta[2];
+  kp.output_tokens = (long long*)h->meta[3];
+  kp.num_new_tokens = (int*)h->meta[4];
+  kp.prompt_lengths = (int*)h->meta[5];
+  kp.qo_indptr = (int*)h->meta[6];
+  kp.kv_indptr = (int*)h->meta[7];
+  kp.kv_indices = (int*)h->meta[8];
+  kp.kv_last_page_len = (int*)h->meta[9];
+  kp.max_seq_len = cfg.max_seq_length;
+  kp.max_reqs = cfg.max_num_batched_requests;
+  kp.max_tokens = cfg.max_num_batched_tokens;
+  kp.max_pages = cfg.max_num_pages;
+  kp.page_size = cfg.page_size;
+  kp.total_requests = (int)h->total_requests;
+  kp.eos = cfg.eos_token_id;
+  kp.max_iters = cfg.max_iterations;
+  kp.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+  h->compiled = true;
+  if (cfg.mode == MK_MODE_OFFLINE) return mk_init_requests(h, nullptr);
+  return 0;
+}
+
+int mk_init_requests(mk_handle* h, void* stream) {
+  if (!h) return MK_E_INVALID;
+  if (!h->compiled) return h->fail(MK_E_STATE, "not compiled");
+  if (h->cfg.mode != MK_MODE_OFFLINE) return 0;
+  int e = mk_kernel_init_state(&h->kp, stream);
+  if (e) return h->cuda_fail((cudaError_t)e, "init_state");
+  cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "init_state sync");
+  return 0;
+}
+
+int mk_launch_async(mk_handle* h, void* stream) {
+  if (!h) return MK_E_INVALID;
+  if (!h->compiled) return h->fail(MK_E_STATE, "not compiled");
+  cudaStream_t s = (cudaStream_t)stream;
+  // grid barrier, control word, abort flag and status live in one 256-byte block behind sched[0..15]
+  cudaError_t ce = cudaMemsetAsync((char*)h->kp.sched + 64, 0, 192, s);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  int e = mk_kernel_launch(&h->kp, h->grid, h->smem_bytes, stream);
+  if (e) return h->cuda_fail((cudaError_t)e, "cooperative launch");
+  h->launched = true;
+  return 0;
+}
+
+int mk_wait(mk_handle* h, void* stream) {
+  if (!h) return MK_E_INVALID;
+  if (!h->launched) return h->fail(MK_E_STATE, "nothing launched");
+  cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "megakernel");
+  int st[16];
+  ce = cudaMemcpy(st, h->kp.abort_flag, sizeof(int) * 16, cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "status readback");
+  if (st[0] != 0) {
+    static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
+                                  "producer never got the next iteration", "peer never arrived", "token id out of range",
+                                  "out of KV pages"};
+    const int* s = st + 8;
+    const int code = s[0];
+    return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
+                   (code >= 0 && code < 8) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
+  }
+  return 0;
+}
+
+int mk_launch(mk_handle* h, void* stream) {
+  if (int e = mk_launch_async(h, stream)) return e;
+  return mk_wait(h, stream);
+}
+
+int mk_get_event_timing(mk_handle* h, uint64_t* buf, int max_entries) {
+  if (!h || !buf || max_entries < 0) return MK_E_INVALID;
+  if (!h->compiled) return h->fail(MK_E_STATE, "not compiled");
+  int iters = 0;
+  cudaError_t ce = cudaMemcpy(&iters, h->kp.sched + 3, 4, cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "timing readback");
+  int n = std::min(std::min(iters + 1, max_entries), h->kp.max_step_times);
+  if (n > 0) {
+    ce = cudaMemcpy(buf, h->kp.step_times, (size_t)n * 16, cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return h->cuda_fail(ce, "timing readback");
+  }
+  return n;
+}
+
+int mk_finalize(mk_handle* h) {
+  if (!h) return MK_E_INVALID;
+  for (void* p : h->allocs) cudaFree(p);
+  delete h;
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// Shared host/device definitions of the B200 decode megakernel.
+//
+// The host runtime lowers the recorded operator list into a flat array of
+// OpDesc (the "program").  One persistent cooperative kernel walks that array
+// once per decode iteration on every SM.
+#pragma once
+#include <stdint.h>
+
+namespace mk {
+
+// ---- geometry of the weight stream -------------------------------------------------
+// A weight tile is 128 output rows x 64 k-elements of bf16 (16 KB), fetched by one
+// 2-D TMA copy into a 128-byte-swizzled shared-memory stage.
+constexpr int kTileRows = 128;
+constexpr int kTileK = 64;
+constexpr int kStageBytes = kTileRows * kTileK * 2;
+constexpr int kNumConsumerWarps = 8;
+constexpr int kNumConsumers = kNumConsumerWarps * 32;
+constexpr int kNumThreads = kNumConsumers + 32;  // + one TMA producer warp
+constexpr int kMaxTokGroup = 4;                  // tokens per CUDA-core pass
+constexpr int kHeadDim = 128;
+
+enum OpType : int {
+  OP_EMBED = 1,
+  OP_RMSNORM = 2,
+  OP_LINEAR = 3,
+  OP_ATTN = 4,
+  OP_SILU_MUL = 5,
+  OP_ARGMAX_PARTIAL = 6,
+  OP_ARGMAX_REDUCE = 7,
+  OP_ALLREDUCE = 8,
+};
+
+enum OpFlags : int {
+  F_SYNC_BEFORE = 1 << 0,   // grid barrier before the op
+  F_CTA0_ONLY = 1 << 1,     // only CTA 0 executes the body
+  F_NORM_IN = 1 << 2,       // linear: RMSNorm fused on the input rows
+  F_RESIDUAL = 1 << 3,      // linear: + residual
+  F_SILU_MUL = 1 << 4,      // linear: rows are [64 gate | 64 up] per tile, epilogue SiLU(gate)*up
+  F_ARGMAX = 1 << 5,        // linear: per-tile (max, index) of the bf16 logits
+  F_QK_NORM = 1 << 6,       // attention
+  F_ROPE = 1 << 7,          // attention
+  F_WRITE_NORM = 1 << 8,    // linear with F_NORM_IN: CTA 0 also stores the normalised rows
+  F_RES_RANK0 = 1 << 9,     // residual only contributed when rank == 0 (row-parallel TP)
+};
+
+enum Numerics : int {
+  NUM_MPK = 0,    // fp32 task arithmetic of the reference megakernel, one bf16 rounding per task
+  NUM_TORCH = 1,  // bf16 roundings of the reference PyTorch model (no-eps bf16 RMSNorm, ...)
+};
+
+enum Mode : int { MODE_OFFLINE = 0, MODE_ONEPASS = 1 };
+
+enum Status : int {
+  ST_OK = 0,
+  ST_TIMEOUT_GRID = 1,
+  ST_TIMEOUT_FULL = 2,
+  ST_TIMEOUT_EMPTY = 3,
+  ST_TIMEOUT_GO = 4,
+  ST_TIMEOUT_PEER = 5,
+  ST_BAD_TOKEN = 6,
+  ST_OUT_OF_PAGES = 7,
+};
+
+struct OpDesc {
+  int type;
+  int flags;
+  // generic shapes
+  int n;        // linear: output features; rmsnorm/silu: columns; argmax: vocab
+  int k;        // linear: input features
+  int ld_in, ld_out, ld_res, ld_out2;  // row pitches in elements
+  int nblk, nkt;                       // linear: row tiles, k tiles
+  int aux0, aux1, aux2, aux3;          // per-type small ints (see mk_kernel.cu)
+  const void* in;
+  const void* w;       // linear weight / embedding table / rmsnorm weight
+  const void* norm_w;  // fused input norm weight
+  const void* res;
+  void* out;
+  void* out2;
+  const void* tmap_w;  // device address of the CUtensorMap of w
+  // attention
+  const void* k_cache_c;  // unused alias kept for alignment
+  void* k_cache;
+  void* v_cache;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  const void* cos;
+  const void* sin;
+  // argmax partials
+  float* amax_val;
+  int* amax_idx;
+  int amax_n;   // number of partials per token
+  int pad_;
+};
+
+struct KParams {
+  const OpDesc* ops;
+  int num_ops;
+  int mode;
+  int numerics;
+  int rank, world;
+  // meta tensors of the operator API (caller-owned)
+  int* step;
+  long long* tokens;
+  long long* input_tokens;
+  long long* output_tokens;
+  int* num_new_tokens;
+  int* prompt_lengths;
+  int* qo_indptr;
+  int* kv_indptr;
+  int* kv_indices;
+  int* kv_last_page_len;
+  int max_seq_len, max_reqs, max_tokens, max_pages, page_size, total_requests;
+  long long eos;
+  int vocab_limit;  // embedding rows, to refuse out-of-range token ids
+  // runtime-owned state
+  int* request_ids;   // [max_reqs]
+  int* page_queue;    // ring of free pages [max_pages]
+  int* sched;         // [0]=page head [1]=page tail [2]=next request id [3]=iterations done
+  unsigned* grid_bar;
+  int* ctrl;          // [0] = active tokens of the iteration, -1 = terminate
+  int* abort_flag;
+  int* status;        // [0]=code [1]=cta [2]=op [3]=iter [4..7]=detail
+  unsigned long long* step_times;
+  int max_step_times;
+  int max_iters;      // 0 = unlimited
+  unsigned long long timeout_ns;
+  // split-k scratch shared by all linear ops
+  float* partial;         // [groups][grid][2][128*kMaxTokGroup]
+  unsigned* piece_count;  // [groups][max nblk]
+  int piece_stride;       // max nblk
+  // attention scratch
+  float* attn_part;       // [tokens][kv heads][max chunks][qpk*(128+2)]
+  unsigned* attn_count;   // [tokens][kv heads]
+  int attn_max_chunks;
+  // shared-memory carve-up (bytes from the 1024-aligned base)
+  int num_stages;
+  int x_off, x_bytes;
+  int red_off;
+  int bar_off;
+};
+
+// The CTA that owns weight tile `tile` when `total` tiles are dealt to `grid`
+// CTAs as contiguous ranges [c*total/grid, (c+1)*total/grid).
+__host__ __device__ inline long long tile_begin(long long c, long long total, long long grid) {
+  return c * total / grid;
+}
+__host__ __device__ inline int tile_owner(long long tile, long long total, long long grid) {
+  return (int)(((tile + 1) * grid - 1) / total);
+}
+
+}  // namespace mk

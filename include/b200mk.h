@@ -1,0 +1,136 @@
+/* b200mk.h - C ABI of the B200 persistent decode megakernel.
+ *
+ * Plain C, no torch or C++ types: every pointer is a raw device or host
+ * address, every size an integer.  The entry points are what a binding of the
+ * reference's MPK operator API needs for the decode path; each one names the
+ * reference interface it stands in for (paths relative to the reference tree).
+ *
+ * All functions return 0 (or a non-negative id) on success and a negative
+ * MK_E_* code on failure; mk_last_error() gives the message.  Nothing here
+ * calls exit().  A handle is not thread-safe; use one handle per GPU.
+ */
+#ifndef B200MK_H
+#define B200MK_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mk_handle mk_handle;
+
+enum { MK_BF16 = 0, MK_F32 = 1, MK_I32 = 2, MK_I64 = 3, MK_U64 = 4, MK_F16 = 5 };
+enum { MK_MODE_OFFLINE = 0, MK_MODE_ONEPASS = 1 };
+enum { MK_NUMERICS_MPK = 0, MK_NUMERICS_TORCH = 1 };
+enum { MK_CAT_CUDA = 0, MK_CAT_SYMMETRIC = 1 };
+enum {
+  MK_E_INVALID = -1,   /* bad argument, shape or dtype */
+  MK_E_STATE = -2,     /* call out of order (e.g. launch before compile) */
+  MK_E_CUDA = -3,      /* a CUDA runtime/driver call failed */
+  MK_E_UNSUPPORTED = -4,
+  MK_E_DEVICE = -5,    /* the kernel reported a timeout or bad data; see mk_last_error */
+  MK_E_NOMEM = -6
+};
+
+/* Constructor arguments of PersistentKernel
+ * (python/mirage/mpk/persistent_kernel.py:368-387). */
+typedef struct mk_config {
+  int32_t mode;                     /* MK_MODE_* ("offline" / "online_notoken") */
+  int32_t world_size;
+  int32_t rank;                     /* mpi_rank */
+  int32_t num_workers;              /* hint; 0 = one CTA per SM */
+  int32_t max_seq_length;
+  int32_t max_num_batched_requests;
+  int32_t max_num_batched_tokens;
+  int32_t max_num_pages;
+  int32_t page_size;
+  int32_t numerics;                 /* MK_NUMERICS_* */
+  int64_t eos_token_id;
+  int32_t fuse;                     /* 1 = fuse norm/SiLU/argmax into the linear tasks */
+  int32_t max_iterations;           /* 0 = run until every request has finished */
+  int64_t timeout_ms;               /* bound of every in-kernel wait; 0 = default (4000) */
+  int32_t device;                   /* CUDA device ordinal, -1 = current */
+  int32_t reserved[7];
+} mk_config;
+
+/* PersistentKernel.__init__ -> KNGraph(CyKNGraph(...)) (persistent_kernel.py:404). */
+mk_handle* mk_create(const mk_config* cfg);
+
+/* attach_input (persistent_kernel.py:469-480; core.pyx attach_torch_tensor):
+ * borrow a caller-owned, row-major device tensor.  Returns the tensor id. */
+int mk_tensor_attach(mk_handle* h, const char* name, void* device_ptr, int dtype, int ndim, const int64_t* dims,
+                     const int64_t* strides);
+
+/* new_tensor (persistent_kernel.py:482-503; attach_cuda_tensor / attach_nvshmem_tensor):
+ * a runtime-owned intermediate.  strides may be NULL (row-major). */
+int mk_tensor_new(mk_handle* h, const char* name, int dtype, int ndim, const int64_t* dims, const int64_t* strides,
+                  int category);
+
+/* shuffle_tensors (persistent_kernel.py:513-519; python/mirage/mpk/models/utils.py:40-118):
+ * rows of the inputs interleaved in num_groups groups, materialised at compile time. */
+int mk_tensor_shuffle(mk_handle* h, const char* name, const int* tensor_ids, int n, int shuffled_dim, int num_groups);
+
+/* fuse_tensors (persistent_kernel.py:505-511): same as shuffle with the inputs concatenated per group. */
+int mk_tensor_fuse(mk_handle* h, const char* name, const int* tensor_ids, int n, int fused_dim, int num_groups);
+
+/* kn_graph.customized + register_task (core.pyx:944-1013; src/kernel/graph.cc:439-848).
+ * op_name is the layer's task family: "embedding", "rmsnorm", "rmsnorm_linear",
+ * "linear", "linear_with_residual", "paged_attention", "paged_attention_split_kv",
+ * "paged_attention_split_kv_merge", "silu_mul", "argmax", "argmax_partial",
+ * "argmax_reduce", "allreduce".  tensor_ids are the layer's operands in the
+ * order the Python method lists them; params are its integer parameters. */
+int mk_op(mk_handle* h, const char* op_name, const int* tensor_ids, int n_tensors, const int64_t* params, int n_params,
+          const int* grid_dim, const int* block_dim);
+
+/* Meta tensors of the constructor (persistent_kernel.py:417-452), device pointers in
+ * this order: step, tokens, input_tokens, output_tokens, num_new_tokens,
+ * prompt_lengths, qo_indptr_buffer, paged_kv_indptr_buffer,
+ * paged_kv_indices_buffer, paged_kv_last_page_len_buffer.
+ * Stands in for init_func (persistent_kernel.py:35) / init_persistent_kernel
+ * (persistent_kernel.cuh:1966). */
+int mk_set_meta(mk_handle* h, void* const meta_ptrs[10], int64_t total_num_requests, void* profiler_ptr);
+
+/* compile (persistent_kernel.py:2404-2618; generate_task_graph, src/kernel/runtime.cc:1652):
+ * validates the graph, lowers it to the device program, materialises shuffled
+ * weights, encodes TMA descriptors and allocates scratch.  No JIT. */
+int mk_compile(mk_handle* h);
+
+/* init_request_func / init_request_resources (persistent_kernel.cuh:1960):
+ * reset step[], the request slots and the page free list. */
+int mk_init_requests(mk_handle* h, void* stream);
+
+/* launch_func / launch_persistent_kernel (persistent_kernel.cuh:2260): run the whole
+ * generation (offline) or one pass (onepass) and wait for it.  Returns MK_E_DEVICE
+ * if the kernel raised its abort flag. */
+int mk_launch(mk_handle* h, void* stream);
+/* Same, without waiting; pair with mk_wait. */
+int mk_launch_async(mk_handle* h, void* stream);
+int mk_wait(mk_handle* h, void* stream);
+
+/* get_event_timing_func (persistent_kernel.cuh:2412): per-iteration records of the
+ * last launch as pairs (globaltimer ns at iteration start, active tokens).
+ * Returns the number of iterations copied. */
+int mk_get_event_timing(mk_handle* h, uint64_t* host_buf, int max_entries);
+
+/* finalize_func / finalize_persistent_kernel (persistent_kernel.cuh:2331). */
+int mk_finalize(mk_handle* h);
+
+int mk_last_error(mk_handle* h, char* buf, int n);
+
+/* Host-only half of mk_compile (validation, fusion decisions, device-op list); needs no GPU. */
+int mk_plan(mk_handle* h);
+
+/* Introspection used by the host-side tests and the benchmark. */
+int mk_num_device_ops(mk_handle* h);
+int mk_describe(mk_handle* h, char* buf, int n);       /* one line per device op */
+int mk_grid_size(mk_handle* h);
+int64_t mk_weight_bytes_per_step(mk_handle* h);        /* bytes the TMA producer streams per iteration */
+int mk_debug_partition(int64_t nblk, int64_t nkt, int grid, int64_t* begin_out /* grid+1 */, int* owner_check);
+void* mk_tensor_ptr(mk_handle* h, int tensor_id);      /* device address after compile (runtime-owned ones too) */
+int mk_tensor_read(mk_handle* h, int tensor_id, void* host_buf, int64_t bytes); /* copy a tensor's bytes to the host */
+
+#ifdef __cplusplus
+}
+#endif
+#endif
