@@ -219,8 +219,9 @@ __device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const 
       const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
       if (p.numerics == NUM_TORCH) {
         // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
+        // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
         const float var = rbf(tot / (float)K);
-        const float r = rbf(rsqrtf(var));
+        const float r = rbf(1.0f / rbf(sqrtf(var)));
         for (int v = c.tid; v < kvec; v += kNumConsumers) {
           float f[8], w[8];
           unpack8(xs[tb * nvec + v], f);
@@ -351,14 +352,15 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
   if (!whole) {
     // this CTA holds one of several k-ranges of the row block: publish the partial
     // sums; the CTA that arrives last adds them in CTA order and runs the epilogue
-    const int G = gridDim.x;
+    const long long total = (long long)op.nblk * op.nkt;
+    const int G = (int)min((long long)gridDim.x, total);  // CTAs that hold tiles of this op
+    const int GS = gridDim.x;
     const size_t slot_elems = (size_t)kTileRows * kMaxTokGroup;
-    float* mine = p.partial + (((size_t)group * G + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems;
+    float* mine = p.partial + (((size_t)group * GS + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems;
     for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) mine[e] = red[e];
     __threadfence();
     consumer_sync();
     volatile int* fl = c.flags();
-    const long long total = (long long)op.nblk * op.nkt;
     const int c_first = tile_owner((long long)blk * op.nkt, total, G);
     const int c_last = tile_owner((long long)blk * op.nkt + op.nkt - 1, total, G);
     unsigned* cnt = p.piece_count + (size_t)group * p.piece_stride + blk;
@@ -377,7 +379,7 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
       float s = 0.f;
       for (int cc = c_first; cc <= c_last; ++cc) {
         const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
-        const float* src = p.partial + (((size_t)group * G + cc) * 2 + (first ? 0 : 1)) * slot_elems;
+        const float* src = p.partial + (((size_t)group * GS + cc) * 2 + (first ? 0 : 1)) * slot_elems;
         s += __ldcg(src + e);
       }
       red[e] = s;
@@ -395,11 +397,11 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
   const int kp = op.nkt * kTileK;
   stage_x<TB>(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, T);
 
-  const int G = gridDim.x;
   const long long total = (long long)op.nblk * op.nkt;
+  const int G = (int)min((long long)gridDim.x, total);  // with fewer tiles than CTAs the rest idle
+  if ((int)blockIdx.x >= G) return;
   const long long t0 = tile_begin(blockIdx.x, total, G);
   const long long t1 = tile_begin(blockIdx.x + 1, total, G);
-  if (t0 >= t1) return;
   const int S = p.num_stages;
   const int c8 = c.tid & 7, rg = c.tid >> 3;
   const uint32_t w_off = (uint32_t)(rg * 128 + ((c8 ^ (rg & 7)) << 4));
@@ -487,8 +489,10 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
 // ------------------------------------------------------------------------------------
 // One head vector is spread over 16 lanes, 8 dims each.  Both halves of a warp run
 // this with full-mask shuffles (xor < 16 stays inside a half-warp).
+// `dbl`: the PyTorch CPU path rounds sqrt to bf16 before the reciprocal when it normalises
+// fewer than 32 heads in one call (scalar loop), and rounds once otherwise (vector loop).
 __device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, const void* cos_row, const void* sin_row,
-                                               int l16, int flags, int numerics) {
+                                               int l16, int flags, int numerics, bool dbl) {
   if (flags & F_QK_NORM) {
     float w[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(norm_w) + l16), w);
@@ -503,7 +507,8 @@ __device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, con
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (numerics == NUM_TORCH) {
-      const float r = rbf(rsqrtf(rbf(ss / (float)kHeadDim)));
+      const float var = rbf(ss / (float)kHeadDim);
+      const float r = dbl ? rbf(1.0f / rbf(sqrtf(var))) : rbf(1.0f / sqrtf(var));
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] = rbf(w[i] * rbf(x[i] * r));
     } else {
@@ -575,14 +580,14 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
 #pragma unroll
     for (int qh = 0; qh < QPK; ++qh) {
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + qh * kHeadDim) + l16), q[qh]);
-      head_norm_rope(q[qh], op.q_norm_w, cos_row, sin_row, l16, op.flags, p.numerics);
+      head_norm_rope(q[qh], op.q_norm_w, cos_row, sin_row, l16, op.flags, p.numerics, op.aux1 < 32);
     }
     // the new token's K (normalised, rotated) and V; the last chunk appends them to the cache
     uint4 knew, vnew;
     {
       float kf[8];
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + QPK * kHeadDim) + l16), kf);
-      head_norm_rope(kf, op.k_norm_w, cos_row, sin_row, l16, op.flags, p.numerics);
+      head_norm_rope(kf, op.k_norm_w, cos_row, sin_row, l16, op.flags, p.numerics, op.aux0 < 32);
       knew = pack8(kf);
       vnew = __ldcg(reinterpret_cast<const uint4*>(row + (QPK + 1) * kHeadDim) + l16);
     }
@@ -989,8 +994,10 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
       const OpDesc& op = p.ops[oi];
       if (op.type != OP_LINEAR) continue;
       const long long total = (long long)op.nblk * op.nkt;
-      const long long t0 = tile_begin(blockIdx.x, total, G);
-      const long long t1 = tile_begin(blockIdx.x + 1, total, G);
+      const int Gop = (int)min((long long)G, total);
+      if ((int)blockIdx.x >= Gop) continue;
+      const long long t0 = tile_begin(blockIdx.x, total, Gop);
+      const long long t1 = tile_begin(blockIdx.x + 1, total, Gop);
       for (int g = 0; g < passes && !dead; ++g) {
         int blk = (int)(t0 / op.nkt);
         int kt = (int)(t0 - (long long)blk * op.nkt);
