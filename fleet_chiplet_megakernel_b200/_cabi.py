@@ -3,7 +3,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200mk.so")
+LIB_PATH = os.environ.get("B200MK_LIB") or os.path.join(HERE, "libb200mk.so")
 
 MK_BF16, MK_F32, MK_I32, MK_I64, MK_U64, MK_F16 = range(6)
 MK_MODE_OFFLINE, MK_MODE_ONEPASS = 0, 1
@@ -19,7 +19,7 @@ class MkConfig(C.Structure):
         ("max_num_batched_tokens", C.c_int32), ("max_num_pages", C.c_int32), ("page_size", C.c_int32),
         ("numerics", C.c_int32), ("eos_token_id", C.c_int64), ("fuse", C.c_int32),
         ("max_iterations", C.c_int32), ("timeout_ms", C.c_int64), ("device", C.c_int32),
-        ("reserved", C.c_int32 * 7),
+        ("trace_op", C.c_int32), ("debug_flags", C.c_int32), ("max_stages", C.c_int32), ("reserved", C.c_int32 * 4),
     ]
 
 
@@ -32,6 +32,7 @@ SIGNATURES = {
     "mk_tensor_fuse": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]),
     "mk_op": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "mk_set_meta": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int64, C.c_void_p]),
+    "mk_set_profiler": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     "mk_compile": (C.c_int, [C.c_void_p]),
     "mk_init_requests": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mk_launch": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -98,6 +98,9 @@ struct Ctx {
   unsigned cons_idx;  // weight stages consumed
   int tid, lane, warp;
   int iter, cur_op;
+  unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
+  unsigned long long* pr;   // this op's trace record, or null
+  bool dead;                // abort flag seen at the op's barrier (CTA-uniform)
   __device__ Ctx(const KParams& p_) : p(p_) {}
   __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
@@ -106,6 +109,15 @@ struct Ctx {
 };
 // flags(): [0] go word written by consumers, read by the producer
 //          [1] stages issued by the producer   [2] broadcast slot   [3] dead flag of the op
+
+#ifdef MK_NO_STAMP
+#define MK_STAMP(c, k) do {} while (0)
+#else
+#define MK_STAMP(c, k)                                             \
+  do {                                                            \
+    if ((c).dbg != nullptr && (c).tid == 0) (c).dbg[k] = globaltimer(); \
+  } while (0)
+#endif
 
 __device__ __noinline__ void raise_abort(const Ctx& c, int code, int d0, int d1) {
   if (atomicCAS(c.p.abort_flag, 0, 1) == 0) {
@@ -122,21 +134,44 @@ __device__ __noinline__ void raise_abort(const Ctx& c, int code, int d0, int d1)
 __device__ __forceinline__ bool aborted(const Ctx& c) { return *(volatile int*)c.p.abort_flag != 0; }
 
 // Bounded wait on an mbarrier phase.  Returns false after raising the abort flag.
+// The clock is only consulted every few thousand failed polls: reading %globaltimer
+// is slow enough to throttle the weight stream if it sits on the per-tile path.
 __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
-  unsigned long long t0 = globaltimer();
+  unsigned long long t0 = 0;
+  unsigned polls = 0;
   while (true) {
-    for (int i = 0; i < 128; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (aborted(c)) return false;
-    if (globaltimer() - t0 > c.p.timeout_ns) {
-      raise_abort(c, code, (int)bar, (int)parity);
-      return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    if (((++polls) & 4095u) == 0) {
+      if (aborted(c)) return false;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > c.p.timeout_ns) {
+        raise_abort(c, code, (int)bar, (int)parity);
+        return false;
+      }
     }
   }
 }
+#ifndef MK_WAIT_STYLE
+#define MK_WAIT_STYLE 0
+#endif
 __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
+#if MK_WAIT_STYLE == 0
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+#elif MK_WAIT_STYLE == 1
   for (int i = 0; i < 16; ++i)
     if (mbar_try_wait(bar, parity)) return true;
+  (void)globaltimer();
+#elif MK_WAIT_STYLE == 2
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(32);
+  }
+#endif
   return mbar_wait_slow(c, bar, parity, code);
 }
 
@@ -149,24 +184,41 @@ __device__ __noinline__ void grid_sync(Ctx& c) {
     __threadfence();
     atomicAdd(c.p.grid_bar, 1u);
     const unsigned target = c.epoch * gridDim.x;
-    if (ld_acquire_u32(c.p.grid_bar) < target) {
-      unsigned long long t0 = globaltimer();
-      int spins = 0;
-      while (ld_acquire_u32(c.p.grid_bar) < target) {
-        if (((++spins) & 63) == 0) {
-          if (aborted(c)) break;
-          if (globaltimer() - t0 > c.p.timeout_ns) {
-            raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
-            break;
-          }
+    unsigned long long t0 = 0;
+    unsigned spins = 0;
+    while (ld_acquire_u32(c.p.grid_bar) < target) {
+      if (((++spins) & 1023u) == 0) {
+        if (aborted(c)) break;
+        const unsigned long long now = globaltimer();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > c.p.timeout_ns) {
+          raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+          break;
         }
       }
     }
     __threadfence();
+    c.flags()[3] = aborted(c) ? 1 : 0;
   } else {
     c.epoch += 1;
   }
   consumer_sync();
+}
+
+// Every op calls this once, after whatever it can fetch ahead of its dependencies:
+// the grid barrier (if the op has one) and the CTA-uniform abort check.  Returns
+// true when the abort flag is up and the op body must be skipped.
+__device__ __forceinline__ bool op_barrier(Ctx& c, const OpDesc& op) {
+  if (op.flags & F_SYNC_BEFORE) {
+    grid_sync(c);
+  } else {
+    if (c.tid == 0) c.flags()[3] = aborted(c) ? 1 : 0;
+    consumer_sync();
+  }
+  if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+  c.dead = c.flags()[3] != 0;
+  return c.dead;
 }
 
 // Sum over the 256 consumer threads; every thread gets the result.
@@ -184,24 +236,33 @@ __device__ __forceinline__ float block_sum(Ctx& c, float v) {
 }
 
 // ------------------------------------------------------------------------------------
+__device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
+
 // activations -> shared memory, with the optional fused RMSNorm
 // ------------------------------------------------------------------------------------
-// Stages rows tok0 .. tok0+TB-1 of op.in as bf16 [TB][kp] in the x region, zero padded.
-template <int TB>
-__device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0, int T) {
+// Stages rows tok0 .. tok0+rows-1 of `in` as bf16 [rows][pitch] in the x region
+// (pitch = padded K + 8 elements, so that the 8 token rows of an ldmatrix hit 8
+// different banks), zero padded, followed by one 16-byte chunk of zeros that
+// stands in for the rows of absent tokens.
+__device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0, int rows,
+                        int T) {
   const KParams& p = c.p;
   uint4* xs = reinterpret_cast<uint4*>(c.smem + p.x_off);
+  const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3;
   const int kvec = K >> 3;
-  for (int tb = 0; tb < TB; ++tb) {
+  if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+  for (int tb = 0; tb < rows; ++tb) {
     const int tok = tok0 + tb;
     const bool valid = tok < T;
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)tok * ld_in);
     float ss = 0.f;
-    for (int v = c.tid; v < nvec; v += kNumConsumers) {
+#pragma unroll 1
+    for (int v = c.tid; v < nvec + 1; v += kNumConsumers) {
       uint4 val = make_uint4(0, 0, 0, 0);
       if (valid && v < kvec) val = __ldcg(src + v);
-      xs[tb * nvec + v] = val;
+      xs[tb * pitch + v] = val;
       if (norm_w != nullptr) {
         float f[8];
         unpack8(val, f);
@@ -221,24 +282,26 @@ __device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const 
         // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
         // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
         const float var = rbf(tot / (float)K);
-        const float r = rbf(1.0f / rbf(sqrtf(var)));
+        const float r = torch_rsqrt_bf16(var, true);
+#pragma unroll 1
         for (int v = c.tid; v < kvec; v += kNumConsumers) {
           float f[8], w[8];
-          unpack8(xs[tb * nvec + v], f);
+          unpack8(xs[tb * pitch + v], f);
           unpack8(__ldg(wv + v), w);
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = w[i] * rbf(f[i] * r);
-          xs[tb * nvec + v] = pack8(f);
+          xs[tb * pitch + v] = pack8(f);
         }
       } else {
         const float r = rsqrtf(tot / (float)K + 1e-6f);
+#pragma unroll 1
         for (int v = c.tid; v < kvec; v += kNumConsumers) {
           float f[8], w[8];
-          unpack8(xs[tb * nvec + v], f);
+          unpack8(xs[tb * pitch + v], f);
           unpack8(__ldg(wv + v), w);
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = f[i] * (r * w[i]);
-          xs[tb * nvec + v] = pack8(f);
+          xs[tb * pitch + v] = pack8(f);
         }
       }
     }
@@ -247,8 +310,14 @@ __device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const 
 }
 
 // ------------------------------------------------------------------------------------
-// linear layer on the CUDA cores (up to 4 tokens per pass)
+// linear layer: weight tiles from the TMA ring x activations from shared memory on the
+// warp-level tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate)
 // ------------------------------------------------------------------------------------
+// Each of the 8 consumer warps owns 16 of a tile's 128 weight rows (the A operand, read
+// with ldmatrix from the 128-byte-swizzled stage); up to 8 tokens form the N dimension
+// (the B operand, token rows read with ldmatrix from the staged activations).  Every
+// (row, token) sum lives in exactly one thread, so a run of tiles ends without any
+// cross-lane reduction.
 struct ArgBest {
   float v;
   int i;
@@ -268,34 +337,49 @@ __device__ __forceinline__ ArgBest warp_argmax(ArgBest a) {
   }
   return a;
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-template <int TB>
-__device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int T) {
+constexpr int kRedStride = kMaxTokGroup;  // floats per row in the shared sums block
+
+// ntok tokens starting at tok0; sums at red[row * kRedStride + token]
+__device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int ntok) {
   const KParams& p = c.p;
   const float* red = c.red();
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
   if (op.flags & F_SILU_MUL) {
     // rows 0..63 of the tile are gate columns, rows 64..127 the matching up columns
     const int half = op.n >> 1;
-    for (int e = c.tid; e < 64 * TB; e += kNumConsumers) {
+#pragma unroll 1
+    for (int e = c.tid; e < 64 * ntok; e += kNumConsumers) {
       const int row = e & 63, tb = e >> 6;
-      const int tok = tok0 + tb, col = blk * 64 + row;
-      if (tok < T && col < half) {
-        const float g = rbf(red[row * TB + tb]);       // linear output is bf16 before the activation
-        const float u = rbf(red[(row + 64) * TB + tb]);
-        const float s = rbf(g / (1.0f + expf(-g)));
-        out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(s * u);
+      const int col = blk * 64 + row;
+      if (col < half) {
+        const float g = rbf(red[row * kRedStride + tb]);  // linear output is bf16 before the activation
+        const float u = rbf(red[(row + 64) * kRedStride + tb]);
+        const float s = rbf(__fdividef(g, 1.0f + __expf(-g)));
+        out[(size_t)(tok0 + tb) * op.ld_out + col] = __float2bfloat16_rn(s * u);
       }
     }
     return;
   }
   const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
-  for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) {
+#pragma unroll 1
+  for (int e = c.tid; e < kTileRows * ntok; e += kNumConsumers) {
     const int row = e & 127, tb = e >> 7;
     const int tok = tok0 + tb, col = blk * kTileRows + row;
-    if (tok < T && col < op.n) {
-      float v = red[row * TB + tb];
+    if (col < op.n) {
+      float v = red[row * kRedStride + tb];
       if (with_res) {
         const float r = __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
         v = (p.numerics == NUM_TORCH) ? rbf(v) + r : v + r;
@@ -305,14 +389,14 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   }
   if (op.flags & F_ARGMAX) {
     float* scratch = c.red() + 1024 + 32;
-    for (int tb = 0; tb < TB; ++tb) {
+    for (int tb = 0; tb < ntok; ++tb) {
       ArgBest b;
       b.v = -INFINITY;
       b.i = 0x7fffffff;
       if (c.tid < kTileRows) {
         const int col = blk * kTileRows + c.tid;
         if (col < op.n) {
-          b.v = rbf(red[c.tid * TB + tb]);
+          b.v = rbf(red[c.tid * kRedStride + tb]);
           b.i = col;
         }
       }
@@ -322,7 +406,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
         scratch[c.warp * 2 + 1] = __int_as_float(b.i);
       }
       consumer_sync();
-      if (c.tid == 0 && tok0 + tb < T) {
+      if (c.tid == 0) {
         ArgBest a;
         a.v = scratch[0];
         a.i = __float_as_int(scratch[1]);
@@ -341,125 +425,167 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 }
 
 // Called by all consumers at the end of a run of tiles of one row block, after the
-// per-row sums of the run were left in red[row * TB + token].
-template <int TB>
+// per-row sums of the run were left in red[row * kRedStride + token].
+//
+// When several CTAs hold k-ranges of the block, the CTA with the block's FIRST k-range
+// finishes it: that range is the tail of its own tile range, so it is the last piece to
+// be computed anyway.  The others publish their partial sums with a release and move on
+// without waiting for anything; the finisher waits (bounded) until they have all
+// arrived, adds the pieces in CTA order and runs the epilogue.
 __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int blk, int kt_first, int kt_last,
-                                                 bool first_of_cta, int tok0, int T, int group) {
+                                                 bool first_of_cta, int tok0, int ntok, int group) {
   const KParams& p = c.p;
   float* red = c.red();
   consumer_sync();
   const bool whole = (kt_first == 0) && (kt_last == op.nkt - 1);
   if (!whole) {
-    // this CTA holds one of several k-ranges of the row block: publish the partial
-    // sums; the CTA that arrives last adds them in CTA order and runs the epilogue
     const long long total = (long long)op.nblk * op.nkt;
     const int G = (int)min((long long)gridDim.x, total);  // CTAs that hold tiles of this op
     const int GS = gridDim.x;
-    const size_t slot_elems = (size_t)kTileRows * kMaxTokGroup;
-    float* mine = p.partial + (((size_t)group * GS + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems;
-    for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) mine[e] = red[e];
-    __threadfence();
-    consumer_sync();
-    volatile int* fl = c.flags();
+    const size_t slot_elems = (size_t)kTileRows * kRedStride;
     const int c_first = tile_owner((long long)blk * op.nkt, total, G);
     const int c_last = tile_owner((long long)blk * op.nkt + op.nkt - 1, total, G);
     unsigned* cnt = p.piece_count + (size_t)group * p.piece_stride + blk;
-    if (c.tid == 0) {
-      const unsigned old = atomicAdd(cnt, 1u);
-      fl[2] = (old == (unsigned)(c_last - c_first)) ? 1 : 0;
-    }
-    consumer_sync();
-    const bool last = fl[2] != 0;
-    if (!last) {
+    float4* red4 = reinterpret_cast<float4*>(red);
+    if ((int)blockIdx.x != c_first) {
+      float4* mine = reinterpret_cast<float4*>(
+          p.partial + (((size_t)group * GS + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems);
+      mine[c.tid] = red4[c.tid];  // 128 x 8 floats = one float4 per consumer thread
+      __threadfence();
       consumer_sync();
+      if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
       return;
     }
-    __threadfence();
-    for (int e = c.tid; e < kTileRows * TB; e += kNumConsumers) {
-      float s = 0.f;
-      for (int cc = c_first; cc <= c_last; ++cc) {
-        const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
-        const float* src = p.partial + (((size_t)group * GS + cc) * 2 + (first ? 0 : 1)) * slot_elems;
-        s += __ldcg(src + e);
+    const unsigned want = (unsigned)(c_last - c_first);
+    if (c.tid == 0) {
+      unsigned long long t0 = 0;
+      unsigned spins = 0;
+      while (ld_acquire_u32(cnt) < want) {
+        if (((++spins) & 1023u) == 0) {
+          if (aborted(c)) break;
+          const unsigned long long now = globaltimer();
+          if (t0 == 0) {
+            t0 = now;
+          } else if (now - t0 > c.p.timeout_ns) {
+            raise_abort(c, ST_TIMEOUT_PEER, blk, (int)ld_acquire_u32(cnt));
+            break;
+          }
+        }
       }
-      red[e] = s;
+      *cnt = 0u;
     }
-    if (c.tid == 0) *cnt = 0u;
+    consumer_sync();
+    __threadfence();
+    // all pieces' loads go out together: one L2 round trip instead of one per piece
+    float4 acc = red4[c.tid];
+#pragma unroll 1
+    for (int c0 = c_first + 1; c0 <= c_last; c0 += 4) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int cc = c0 + u;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cc <= c_last) {
+          const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
+          const float4* src = reinterpret_cast<const float4*>(
+              p.partial + (((size_t)group * GS + cc) * 2 + (first ? 0 : 1)) * slot_elems);
+          v[u] = __ldcg(src + c.tid);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        acc.x += v[u].x;
+        acc.y += v[u].y;
+        acc.z += v[u].z;
+        acc.w += v[u].w;
+      }
+    }
+    red4[c.tid] = acc;
     consumer_sync();
   }
-  linear_epilogue<TB>(c, op, blk, tok0, T);
+  linear_epilogue(c, op, blk, tok0, ntok);
   consumer_sync();
 }
 
-template <int TB>
+// Tokens one pass of a linear op covers (aux3, fixed by the host from the shared-memory
+// budget) and the passes its weight stream makes for T active tokens.
+__device__ __forceinline__ int linear_passes(const OpDesc& op, int T) { return (T + op.aux3 - 1) / op.aux3; }
+
 __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int T, int group) {
   const KParams& p = c.p;
-  const int kp = op.nkt * kTileK;
-  stage_x<TB>(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, T);
+  const int nkt = op.nkt;
+  const int kp = nkt * kTileK;
+  const int ntok = min(op.aux3, T - tok0);
+  MK_STAMP(c, 0);
+  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T);
+  MK_STAMP(c, 1);
 
-  const long long total = (long long)op.nblk * op.nkt;
+  const long long total = (long long)op.nblk * nkt;
   const int G = (int)min((long long)gridDim.x, total);  // with fewer tiles than CTAs the rest idle
   if ((int)blockIdx.x >= G) return;
   const long long t0 = tile_begin(blockIdx.x, total, G);
   const long long t1 = tile_begin(blockIdx.x + 1, total, G);
   const int S = p.num_stages;
-  const int c8 = c.tid & 7, rg = c.tid >> 3;
-  const uint32_t w_off = (uint32_t)(rg * 128 + ((c8 ^ (rg & 7)) << 4));
-  const uint32_t xs_addr = c.smem_addr + p.x_off + c8 * 16;
-  float acc[4][TB];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int tb = 0; tb < TB; ++tb) acc[i][tb] = 0.f;
+  const int lane = c.lane, warp = c.warp;
+  // A operand: lane l addresses row 16*warp + (l & 7) + 8 * ((l >> 3) & 1), 16-byte chunk 2*kb + (l >> 4)
+  const int a_row = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
+  const uint32_t a_base = (uint32_t)(a_row * 128);
+  const uint32_t a_xor = (uint32_t)(a_row & 7);
+  const uint32_t a_hi = (uint32_t)(lane >> 4);
+  // B operand: lane l addresses token (l & 7), chunk 4*half + (l >> 3); absent tokens read the zero chunk
+  const int pitch_b = (kp + 8) * 2;
+  const bool b_real = (lane & 7) < ntok;
+  const uint32_t xs0 = c.smem_addr + p.x_off;
+  const uint32_t b_zero = xs0 + (uint32_t)(ntok * pitch_b);
+  const uint32_t b_row = xs0 + (uint32_t)((lane & 7) * pitch_b + (lane >> 3) * 16);
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
 
-  int blk = (int)(t0 / op.nkt);
-  int kt = (int)(t0 - (long long)blk * op.nkt);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int blk = (int)(t0 / nkt);
+  int kt = (int)(t0 - (long long)blk * nkt);
   int kt_first = kt;
   bool first_of_cta = true;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+  const bool arith = !(p.debug_flags & 1);
   for (long long tile = t0; tile < t1; ++tile) {
-    const int s = c.cons_idx % S;
-    const uint32_t parity = (c.cons_idx / S) & 1;
-    mbar_wait(c, c.full_bar(s), parity, ST_TIMEOUT_FULL);
-    const uint32_t st = c.smem_addr + s * kStageBytes + w_off;
-    uint4 w[4];
+    mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+    if (tile == t0) MK_STAMP(c, 2);
+    const uint32_t st = c.smem_addr + (uint32_t)s * kStageBytes + a_base;
+    if (arith) {
+      uint32_t b[8];
+      const uint32_t bk = b_real ? b_row + (uint32_t)kt * (kTileK * 2) : b_zero;
+      ldmatrix_x4(bk, b[0], b[1], b[2], b[3]);
+      ldmatrix_x4(b_real ? bk + 64 : b_zero, b[4], b[5], b[6], b[7]);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = lds128(st + i * 32 * 128);
-#pragma unroll
-    for (int tb = 0; tb < TB; ++tb) {
-      float xf[8];
-      unpack8(lds128(xs_addr + (uint32_t)(tb * kp + kt * kTileK) * 2), xf);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float wf[8];
-        unpack8(w[i], wf);
-        float a = acc[i][tb];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) a = fmaf(wf[j], xf[j], a);
-        acc[i][tb] = a;
+      for (int kb = 0; kb < 4; ++kb) {
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(st + ((((uint32_t)(2 * kb) + a_hi) ^ a_xor) << 4), a0, a1, a2, a3);
+        mma_bf16(acc, a0, a1, a2, a3, b[2 * kb], b[2 * kb + 1]);
       }
     }
     __syncwarp();
-    if (c.lane == 0) mbar_arrive(c.empty_bar(s));
-    c.cons_idx += 1;
-    const bool end_blk = (kt == op.nkt - 1);
+    if (lane == 0) mbar_arrive(bar_empty0 + 8 * s);
+    ++consumed;
+    if (++s == S) {
+      s = 0;
+      parity ^= 1u;
+    }
+    const bool end_blk = (kt == nkt - 1);
+    if (tile == t1 - 1) MK_STAMP(c, 3);
     if (end_blk || tile == t1 - 1) {
-      // add up the 8 lanes that share a row group, leave the sums in shared memory
-      float* red = c.red();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-#pragma unroll
-        for (int tb = 0; tb < TB; ++tb) {
-          float v = acc[i][tb];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          v += __shfl_xor_sync(0xffffffffu, v, 4);
-          if (c8 == 0) red[(rg + 32 * i) * TB + tb] = v;
-          acc[i][tb] = 0.f;
-        }
-      }
-      linear_finish_piece<TB>(c, op, blk, kt_first, kt, first_of_cta, tok0, T, group);
+      // thread (lane) holds rows 16*warp + lane/4 (+8) and tokens 2*(lane%4) (+1)
+      float* red = c.red() + (16 * warp + (lane >> 2)) * kRedStride + 2 * (lane & 3);
+      red[0] = acc[0];
+      red[1] = acc[1];
+      red[8 * kRedStride] = acc[2];
+      red[8 * kRedStride + 1] = acc[3];
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group);
       first_of_cta = false;
       kt_first = 0;
+      if (tile == t1 - 1) MK_STAMP(c, 4);
     }
     if (end_blk) {
       kt = 0;
@@ -468,34 +594,42 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
       kt += 1;
     }
   }
+  c.cons_idx += consumed;
 }
 
-// Number of passes the weight stream of a linear op makes for T active tokens.
-__device__ __forceinline__ int linear_passes(int T) { return (T + kMaxTokGroup - 1) / kMaxTokGroup; }
-
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
-  const int passes = linear_passes(T);
-  for (int g = 0; g < passes; ++g) {
-    const int tok0 = g * kMaxTokGroup;
-    const int n = min(kMaxTokGroup, T - tok0);
-    if (n == 1) linear_pass<1>(c, op, tok0, T, g);
-    else if (n == 2) linear_pass<2>(c, op, tok0, T, g);
-    else linear_pass<4>(c, op, tok0, T, g);
-  }
+  if (op_barrier(c, op)) return;
+  const int passes = linear_passes(op, T);
+  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g);
 }
 
 // ------------------------------------------------------------------------------------
 // attention: QK-norm + RoPE + KV append + paged split-KV GQA decode + merge
 // ------------------------------------------------------------------------------------
-// One head vector is spread over 16 lanes, 8 dims each.  Both halves of a warp run
-// this with full-mask shuffles (xor < 16 stays inside a half-warp).
-// `dbl`: the PyTorch CPU path rounds sqrt to bf16 before the reciprocal when it normalises
-// fewer than 32 heads in one call (scalar loop), and rounds once otherwise (vector loop).
-__device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, const void* cos_row, const void* sin_row,
-                                               int l16, int flags, int numerics, bool dbl) {
+// Work split inside a CTA: warp w serves q head (w % qpk) of the task's kv-head group and
+// position group (w / qpk); its two half-warps take alternate positions.  One head
+// vector is spread over the 16 lanes of a half-warp, 8 dims each, so a cached K or V
+// row of 256 bytes is one 16-byte load per lane.  The code is kept small on purpose:
+// the megakernel switches between task bodies thousands of times per step and every
+// switch refills the instruction cache.
+
+// bf16 reciprocal square root the way the reference PyTorch model's CPU kernels round it:
+// `dbl` = scalar loop (sqrt rounded to bf16 before the reciprocal), else vector loop.
+__device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl) {
+  return dbl ? rbf(1.0f / rbf(sqrtf(var))) : rbf(1.0f / sqrtf(var));
+}
+
+// The norm weight and the cos/sin rows arrive already loaded (8 bf16 each).  Both halves
+// of a warp run this with full-mask shuffles (xor < 16 stays inside a half-warp).
+struct F8 {
+  float v[8];
+};
+__device__ __noinline__ F8 head_norm_rope(F8 xin, uint4 wv, uint4 csv, uint4 snv, int l16, int flags, int numerics,
+                                          bool dbl) {
+  float* x = xin.v;
   if (flags & F_QK_NORM) {
     float w[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(norm_w) + l16), w);
+    unpack8(wv, w);
     float ss = 0.f;
     if (numerics == NUM_TORCH) {
 #pragma unroll
@@ -507,8 +641,7 @@ __device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, con
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (numerics == NUM_TORCH) {
-      const float var = rbf(ss / (float)kHeadDim);
-      const float r = dbl ? rbf(1.0f / rbf(sqrtf(var))) : rbf(1.0f / sqrtf(var));
+      const float r = torch_rsqrt_bf16(rbf(ss / (float)kHeadDim), dbl);
 #pragma unroll
       for (int i = 0; i < 8; ++i) x[i] = rbf(w[i] * rbf(x[i] * r));
     } else {
@@ -519,8 +652,8 @@ __device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, con
   }
   if (flags & F_ROPE) {
     float cs[8], sn[8];
-    unpack8(__ldg(reinterpret_cast<const uint4*>(cos_row) + l16), cs);
-    unpack8(__ldg(reinterpret_cast<const uint4*>(sin_row) + l16), sn);
+    unpack8(csv, cs);
+    unpack8(snv, sn);
     const float sign = (l16 < 8) ? -1.f : 1.f;  // first half: x*cos - partner*sin
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -529,211 +662,286 @@ __device__ __forceinline__ void head_norm_rope(float* x, const void* norm_w, con
       else x[i] = rbf(x[i] * cs[i] + sign * other * sn[i]);
     }
   }
+  return xin;
 }
 
-// aux0 = kv heads, aux1 = q heads.  Tokens: one per request, token t == request slot t.
-template <int QPK>
+// Everything a (token, kv head, chunk) task needs that does not depend on the QKV
+// rows of this layer: lengths, page numbers, norm weights, cos/sin, and the first
+// four cached K/V rows of this half-warp.  Loaded before the op's grid barrier for
+// the CTA's first task, so that only the q path is left on the critical path.
+struct AttnTask {
+  int t, h, ch, L, p0, p1, nch, kv_base, new_page;
+  bool valid;
+  uint4 wq, wk, cs, sn;
+  uint4 kr[4], vr[4];
+};
+
+struct AttnPlan {
+  int HKV, qpk, CS, nch_max, ntasks;
+  int gi, ngroups;  // this half-warp's position group and the number of groups
+};
+
+// rows of positions p0 + (it0 + u) * ngroups + gi, u = 0..3
+__device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a,
+                                                int it0, int l16, uint4* kr, uint4* vr) {
+  const int PS = c.p.page_size;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int j = a.p0 + (it0 + u) * pl.ngroups + pl.gi;
+    kr[u] = make_uint4(0, 0, 0, 0);
+    vr[u] = make_uint4(0, 0, 0, 0);
+    if (j < a.p1 && j != a.L - 1) {
+      const int pg = __ldcg(c.p.kv_indices + a.kv_base + j / PS);
+      const size_t src = (((size_t)pg * PS + j % PS) * pl.HKV + a.h) * kHeadDim;
+      kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src) + l16);
+      vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src) + l16);
+    }
+  }
+}
+
+__device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int task,
+                                          int l16, AttnTask& a) {
+  a.valid = false;
+  if (task >= pl.ntasks) return;
+  a.ch = task % pl.nch_max;
+  a.h = (task / pl.nch_max) % pl.HKV;
+  a.t = task / (pl.nch_max * pl.HKV);
+  a.L = lens[a.t];
+  a.p0 = a.ch * pl.CS;
+  if (a.p0 >= a.L || a.L <= 0) return;
+  a.valid = true;
+  a.p1 = min(a.L, a.p0 + pl.CS);
+  a.nch = (a.L + pl.CS - 1) / pl.CS;
+  a.kv_base = __ldcg(c.p.kv_indptr + a.t);
+  const int pos = min(a.L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
+  a.wq = __ldg(reinterpret_cast<const uint4*>(op.q_norm_w) + l16);
+  a.wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
+  a.cs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
+  a.sn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
+  a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + (a.L - 1) / c.p.page_size) : 0;
+  attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr);
+}
+
+// aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
+// request, token t == request slot t.
 __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
-  const int HKV = op.aux0;
-  const int PS = p.page_size;
   const int G = gridDim.x;
-  int* lens = reinterpret_cast<int*>(c.red() + 1024 + 64);  // [<=64] sequence lengths incl. the new token
+  MK_STAMP(c, 0);
+  int* lens = reinterpret_cast<int*>(c.red() + 1024 + 64);  // sequence lengths incl. the new token
+#pragma unroll 1
   for (int r = c.tid; r < T; r += kNumConsumers) {
     const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
-    lens[r] = (last - first - 1) * PS + __ldcg(p.kv_last_page_len + r);
+    lens[r] = (last - first - 1) * p.page_size + __ldcg(p.kv_last_page_len + r);
   }
   consumer_sync();
   int Lmax = 1;
+#pragma unroll 1
   for (int r = 0; r < T; ++r) Lmax = max(Lmax, lens[r]);
-  const int nb_max = (Lmax + 63) >> 6;
-  int bpc = (T * HKV * nb_max + G - 1) / G;  // 64-position blocks per chunk: one round of tasks
+  AttnPlan pl;
+  pl.HKV = op.aux0;
+  pl.qpk = op.aux1 / op.aux0;
+  const int nb_max = (Lmax + 15) >> 4;
+  int bpc = (T * pl.HKV * nb_max + G - 1) / G;  // 16-position blocks per chunk: one round of tasks
   bpc = max(bpc, (nb_max + p.attn_max_chunks - 1) / p.attn_max_chunks);
   bpc = max(bpc, 1);
-  const int CS = bpc * 64;
-  const int nch_max = (nb_max + bpc - 1) / bpc;
-  const int ntasks = T * HKV * nch_max;
-  const int hw = c.tid >> 4, l16 = c.tid & 15;
-  constexpr int PART = QPK * (kHeadDim + 2);
-  const float sc = 1.4426950408889634f / sqrtf((float)kHeadDim);  // softmax scale in the exp2 domain
-  float* sm_o = reinterpret_cast<float*>(c.smem + p.x_off);       // [16][QPK][128]
-  float* sm_m = sm_o + 16 * QPK * kHeadDim;                       // [16][QPK]
-  float* sm_l = sm_m + 16 * QPK;
+  pl.CS = bpc * 16;
+  pl.nch_max = (nb_max + bpc - 1) / bpc;
+  pl.ntasks = T * pl.HKV * pl.nch_max;
+  const int l16 = c.lane & 15;
+  const int qh = c.warp % pl.qpk;                           // this warp's q head within the group
+  pl.ngroups = 2 * (kNumConsumerWarps / pl.qpk);
+  pl.gi = 2 * (c.warp / pl.qpk) + (c.lane >> 4);
+  const int hw = c.tid >> 4;                                // half-warp slot in the combine buffers
+  const int part_stride = pl.qpk * (kHeadDim + 2);
+  const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+  float* sm_o = reinterpret_cast<float*>(c.smem + p.x_off);     // [16 half-warps][128]
+  float* sm_m = sm_o + 16 * kHeadDim;                           // [16]
+  float* sm_l = sm_m + 16;
+  const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
 
-  for (int task = blockIdx.x; task < ntasks; task += G) {
-    const int ch = task % nch_max;
-    const int h = (task / nch_max) % HKV;
-    const int t = task / (nch_max * HKV);
-    const int L = lens[t];
-    const int p0 = ch * CS;
-    if (p0 >= L || L <= 0) continue;
-    const int p1 = min(L, p0 + CS);
-    const int nch = (L + CS - 1) / CS;
-    const int kv_base = __ldcg(p.kv_indptr + t);
-    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)t * op.ld_in +
-                               (size_t)h * (QPK + 2) * kHeadDim;
-    const int pos = min(L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
-    const __nv_bfloat16* cos_row = reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim;
-    const __nv_bfloat16* sin_row = reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim;
-
-    float q[QPK][8];
-#pragma unroll
-    for (int qh = 0; qh < QPK; ++qh) {
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + qh * kHeadDim) + l16), q[qh]);
-      head_norm_rope(q[qh], op.q_norm_w, cos_row, sin_row, l16, op.flags, p.numerics, op.aux1 < 32);
+  bool first = true;
+#pragma unroll 1
+  for (int task = blockIdx.x;; task += G) {
+    AttnTask a;
+    attn_prepare(c, op, pl, lens, task, l16, a);
+    if (first) {
+      // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
+      first = false;
+      MK_STAMP(c, 1);
+      if (op_barrier(c, op)) return;
     }
-    // the new token's K (normalised, rotated) and V; the last chunk appends them to the cache
-    uint4 knew, vnew;
-    {
-      float kf[8];
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + QPK * kHeadDim) + l16), kf);
-      head_norm_rope(kf, op.k_norm_w, cos_row, sin_row, l16, op.flags, p.numerics, op.aux0 < 32);
-      knew = pack8(kf);
-      vnew = __ldcg(reinterpret_cast<const uint4*>(row + (QPK + 1) * kHeadDim) + l16);
-    }
-    if (p1 == L && hw == 0) {
-      const int pg = __ldcg(p.kv_indices + kv_base + (L - 1) / PS);
-      const size_t dst = (((size_t)pg * PS + (L - 1) % PS) * HKV + h) * kHeadDim;
+    if (task >= pl.ntasks) break;
+    if (!a.valid) continue;
+    const int L = a.L;
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
+                               (size_t)a.h * (pl.qpk + 2) * kHeadDim;
+    // one batch of loads: this warp's q head, the new k and v
+    const uint4 rq = __ldcg(reinterpret_cast<const uint4*>(row + qh * kHeadDim) + l16);
+    const uint4 rk = __ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16);
+    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+    F8 q, kf;
+    unpack8(rq, q.v);
+    unpack8(rk, kf.v);
+    q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+    kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+    const uint4 knew = pack8(kf.v);
+    if (a.p1 == L && hw == 0) {  // the last chunk appends the new token's K and V to the cache
+      const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
       reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = knew;
       reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
     }
-
-    float m[QPK], l[QPK], o[QPK][8];
+    MK_STAMP(c, 2);
+    float m = -INFINITY, l = 0.f, o[8];
 #pragma unroll
-    for (int qh = 0; qh < QPK; ++qh) {
-      m[qh] = -INFINITY;
-      l[qh] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[qh][i] = 0.f;
-    }
-    const int niter = (p1 - p0 + 15) >> 4;
+    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
+#pragma unroll 1
     for (int it = 0; it < niter; it += 4) {
-      uint4 kr[4], vr[4];
-      bool ok[4];
+      // the next four rows are requested before this batch is used
+      uint4 nk[4], nv[4];
+      const bool more = it + 4 < niter;
+      if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
+      float s[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int j = p0 + (it + u) * 16 + hw;
-        ok[u] = (it + u < niter) && (j < p1);
-        kr[u] = make_uint4(0, 0, 0, 0);
-        vr[u] = make_uint4(0, 0, 0, 0);
-        if (ok[u] && j == L - 1) {
-          kr[u] = knew;
-          vr[u] = vnew;
-        } else if (ok[u]) {
-          const int pg = __ldcg(p.kv_indices + kv_base + j / PS);
-          const size_t src = (((size_t)pg * PS + j % PS) * HKV + h) * kHeadDim;
-          kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src) + l16);
-          vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src) + l16);
+        const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
+        const bool ok = j < a.p1;
+        if (ok && j == L - 1) {
+          a.kr[u] = knew;
+          a.vr[u] = vnew;
         }
+        float kk[8];
+        unpack8(a.kr[u], kk);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(q.v[i], kk[i], d);
+#pragma unroll
+        for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+        s[u] = ok ? d * sc : -INFINITY;
       }
-      float s[4][QPK];
+      const float mn = fmaxf(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])), m);
+      if (mn != -INFINITY) {
+        const float alpha = exp2f(m - mn);
+        l *= alpha;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        float kf[8];
-        unpack8(kr[u], kf);
-#pragma unroll
-        for (int qh = 0; qh < QPK; ++qh) {
-          float d = 0.f;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) d = fmaf(q[qh][i], kf[i], d);
-#pragma unroll
-          for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-          s[u][qh] = ok[u] ? d * sc : -INFINITY;
-        }
-      }
-#pragma unroll
-      for (int qh = 0; qh < QPK; ++qh) {
-        float mn = m[qh];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) mn = fmaxf(mn, s[u][qh]);
-        if (mn == -INFINITY) continue;
-        const float alpha = exp2f(m[qh] - mn);
-        float pr[4];
-        float ls = 0.f;
+        for (int i = 0; i < 8; ++i) o[i] *= alpha;
+        m = mn;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          pr[u] = exp2f(s[u][qh] - mn);
-          ls += pr[u];
-        }
-        l[qh] = l[qh] * alpha + ls;
-        m[qh] = mn;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[qh][i] *= alpha;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
+          const float pr = exp2f(s[u] - mn);
+          l += pr;
           float vf[8];
-          unpack8(vr[u], vf);
+          unpack8(a.vr[u], vf);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[qh][i] = fmaf(pr[u], vf[i], o[qh][i]);
+          for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i]);
+        }
+      }
+      if (more) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a.kr[u] = nk[u];
+          a.vr[u] = nv[u];
         }
       }
     }
-    // combine the 16 half-warps
-#pragma unroll
-    for (int qh = 0; qh < QPK; ++qh) {
-      float* dst = sm_o + ((size_t)hw * QPK + qh) * kHeadDim + l16 * 8;
-      reinterpret_cast<float4*>(dst)[0] = make_float4(o[qh][0], o[qh][1], o[qh][2], o[qh][3]);
-      reinterpret_cast<float4*>(dst)[1] = make_float4(o[qh][4], o[qh][5], o[qh][6], o[qh][7]);
+    MK_STAMP(c, 3);
+    // combine the position groups of each head
+    {
+      float* dst = sm_o + hw * kHeadDim + l16 * 8;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
       if (l16 == 0) {
-        sm_m[hw * QPK + qh] = m[qh];
-        sm_l[hw * QPK + qh] = l[qh];
+        sm_m[hw] = m;
+        sm_l[hw] = l;
       }
     }
     consumer_sync();
-    float* part = p.attn_part + (((size_t)t * HKV + h) * p.attn_max_chunks + ch) * PART;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)t * op.ld_out + (size_t)h * QPK * kHeadDim;
-    for (int e = c.tid; e < QPK * kHeadDim; e += kNumConsumers) {
-      const int qh = e >> 7, d = e & 127;
+    float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
+                         (size_t)a.h * pl.qpk * kHeadDim;
+#pragma unroll 1
+    for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
+      const int eh = e >> 7, d = e & 127;
       float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 16; ++w) M = fmaxf(M, sm_m[w * QPK + qh]);
+#pragma unroll 1
+      for (int w = eh; w < kNumConsumerWarps; w += pl.qpk) M = fmaxf(M, fmaxf(sm_m[2 * w], sm_m[2 * w + 1]));
       float Ls = 0.f, O = 0.f;
+#pragma unroll 1
+      for (int w = eh; w < kNumConsumerWarps; w += pl.qpk) {
 #pragma unroll
-      for (int w = 0; w < 16; ++w) {
-        const float mw = sm_m[w * QPK + qh];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        Ls += f * sm_l[w * QPK + qh];
-        O += f * sm_o[((size_t)w * QPK + qh) * kHeadDim + d];
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const float mw = sm_m[2 * w + h2];
+          const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+          Ls += f * sm_l[2 * w + h2];
+          O += f * sm_o[(2 * w + h2) * kHeadDim + d];
+        }
       }
-      if (nch == 1) {
-        out[e] = __float2bfloat16_rn(O / Ls);
+      if (a.nch == 1) {
+        out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
       } else {
         part[e] = O;
         if (d == 0) {
-          part[QPK * kHeadDim + qh] = M;
-          part[QPK * kHeadDim + QPK + qh] = Ls;
+          part[pl.qpk * kHeadDim + eh] = M;
+          part[pl.qpk * kHeadDim + pl.qpk + eh] = Ls;
         }
       }
     }
-    if (nch > 1) {
+    MK_STAMP(c, 4);
+    if (a.nch > 1) {
       __threadfence();
       consumer_sync();
+      MK_STAMP(c, 5);
       volatile int* fl = c.flags();
-      unsigned* cnt = p.attn_count + (size_t)t * HKV + h;
+      unsigned* cnt = p.attn_count + (size_t)a.t * pl.HKV + a.h;
       if (c.tid == 0) {
         const unsigned old = atomicAdd(cnt, 1u);
-        fl[2] = (old == (unsigned)(nch - 1)) ? 1 : 0;
+        fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
       }
       consumer_sync();
-      if (fl[2] != 0) {
+      MK_STAMP(c, 6);
+      if (fl[2] != 0) {  // the chunk that arrives last merges all of them
         __threadfence();
-        const float* base = p.attn_part + (((size_t)t * HKV + h) * p.attn_max_chunks) * PART;
-        for (int e = c.tid; e < QPK * kHeadDim; e += kNumConsumers) {
-          const int qh = e >> 7;
+        const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
+        // (max, sum) of every chunk and head into shared memory with one round of loads
+        float* sm_pm = sm_l + 16;                        // [chunks][qpk]
+        float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
+#pragma unroll 1
+        for (int i = c.tid; i < a.nch * pl.qpk; i += kNumConsumers) {
+          const float* pm = base + (size_t)(i / pl.qpk) * part_stride + pl.qpk * kHeadDim + (i % pl.qpk);
+          sm_pm[i] = __ldcg(pm);
+          sm_pl[i] = __ldcg(pm + pl.qpk);
+        }
+        consumer_sync();
+#pragma unroll 1
+        for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
+          const int eh = e >> 7;
           float M = -INFINITY;
-          for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, __ldcg(base + (size_t)cc * PART + QPK * kHeadDim + qh));
+#pragma unroll 1
+          for (int cc = 0; cc < a.nch; ++cc) M = fmaxf(M, sm_pm[cc * pl.qpk + eh]);
           float Ls = 0.f, O = 0.f;
-          for (int cc = 0; cc < nch; ++cc) {
-            const float f = exp2f(__ldcg(base + (size_t)cc * PART + QPK * kHeadDim + qh) - M);
-            Ls += f * __ldcg(base + (size_t)cc * PART + QPK * kHeadDim + QPK + qh);
-            O += f * __ldcg(base + (size_t)cc * PART + e);
+#pragma unroll 1
+          for (int c0 = 0; c0 < a.nch; c0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              v[u] = (c0 + u < a.nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              if (c0 + u < a.nch) {
+                const float f = exp2f(sm_pm[(c0 + u) * pl.qpk + eh] - M);
+                Ls += f * sm_pl[(c0 + u) * pl.qpk + eh];
+                O += f * v[u];
+              }
+            }
           }
-          out[e] = __float2bfloat16_rn(O / Ls);
+          out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
         }
         if (c.tid == 0) *cnt = 0u;
       }
     }
     consumer_sync();
+    MK_STAMP(c, 7);
   }
 }
 
@@ -762,7 +970,7 @@ __device__ void op_embed(Ctx& c, const OpDesc& op, int T) {
 __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   const int kp = ((op.n + 63) / 64) * 64;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    stage_x<1>(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1);
+    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out);
     for (int v = c.tid; v < (op.n >> 3); v += kNumConsumers) dst[v] = xs[v];
@@ -970,7 +1178,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     // wait for the consumers to publish this iteration's token count (or the end)
     int go;
     {
-      unsigned long long t0 = globaltimer();
+      unsigned long long t0 = 0;
       int spins = 0;
       while (true) {
         go = fl[0];
@@ -978,7 +1186,9 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
         __nanosleep(40);
         if (((++spins) & 255) == 0) {
           if (aborted(c)) { go = -1; break; }
-          if (globaltimer() - t0 > c.p.timeout_ns) {
+          const unsigned long long now = globaltimer();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > c.p.timeout_ns) {
             raise_abort(c, ST_TIMEOUT_GO, iter, go);
             go = -1;
             break;
@@ -988,11 +1198,11 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     }
     if (go < 0) break;
     const int T = go & 255;
-    const int passes = linear_passes(T);
     bool dead = false;
     for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
       const OpDesc& op = p.ops[oi];
       if (op.type != OP_LINEAR) continue;
+      const int passes = linear_passes(op, T);
       const long long total = (long long)op.nblk * op.nkt;
       const int Gop = (int)min((long long)G, total);
       if ((int)blockIdx.x >= Gop) continue;
@@ -1010,7 +1220,9 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           mbar_arrive_expect_tx(c.full_bar(s), kStageBytes);
           tma_load_2d(c.smem_addr + s * kStageBytes, op.tmap_w, c.full_bar(s), kt * kTileK, blk * kTileRows);
           issued += 1;
+#ifndef MK_ISSUED_LAZY
           fl[1] = (int)issued;
+#endif
           if (++kt == op.nkt) {
             kt = 0;
             ++blk;
@@ -1041,6 +1253,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.warp = threadIdx.x >> 5;
   c.iter = 0;
   c.cur_op = -1;
+  c.dbg = nullptr;
+  c.pr = nullptr;
+  c.dead = false;
   volatile int* fl = c.flags();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
@@ -1064,6 +1279,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       c.iter = iter;
       c.cur_op = -1;
       int T;
+      unsigned long long* prof = p.prof;
+      if (prof && c.tid == 0) prof[((size_t)p.num_ops * gridDim.x + blockIdx.x) * 4 + 0] = globaltimer();
       if (p.mode == MODE_OFFLINE) {
         if (blockIdx.x == 0) {
           consumer_sync();
@@ -1099,6 +1316,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       consumer_sync();
       T = fl[3];
       consumer_sync();
+      if (prof && c.tid == 0) prof[((size_t)p.num_ops * gridDim.x + blockIdx.x) * 4 + 2] = globaltimer();
       if (T <= 0) break;
       if (T > 255) T = 255;
       if (c.tid == 0) fl[0] = (iter << 8) | T;
@@ -1106,28 +1324,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       for (int oi = 0; oi < p.num_ops; ++oi) {
         const OpDesc& op = p.ops[oi];
         c.cur_op = oi;
-        if (op.flags & F_SYNC_BEFORE) grid_sync(c);
-        // once the abort flag is up the op bodies are skipped; the decision is CTA-uniform
-        if (c.tid == 0) fl[3] = aborted(c) ? 1 : 0;
-        consumer_sync();
-        const bool dead = fl[3] != 0;
-        consumer_sync();
-        if (dead) break;
-        if ((op.flags & F_CTA0_ONLY) && blockIdx.x != 0) continue;
+        unsigned long long* pr = prof ? prof + ((size_t)oi * gridDim.x + blockIdx.x) * 4 : nullptr;
+        c.dbg = (prof && oi == p.trace_op) ? prof + ((size_t)(p.num_ops + 1) * gridDim.x) * 4 + (size_t)blockIdx.x * 16 : nullptr;
+        if (pr && c.tid == 0) pr[0] = globaltimer();
+        c.pr = pr;
+        c.dead = false;
+        if ((op.flags & F_CTA0_ONLY) && blockIdx.x != 0) {
+          if (op_barrier(c, op)) break;
+          if (pr && c.tid == 0) pr[2] = pr[1];
+          continue;
+        }
         switch (op.type) {
-          case OP_EMBED: op_embed(c, op, T); break;
-          case OP_RMSNORM: op_rmsnorm(c, op, T); break;
+          case OP_EMBED: if (!op_barrier(c, op)) op_embed(c, op, T); break;
+          case OP_RMSNORM: if (!op_barrier(c, op)) op_rmsnorm(c, op, T); break;
           case OP_LINEAR: op_linear(c, op, T); break;
           case OP_ATTN:
-            if (op.aux1 / op.aux0 == 4) op_attention<4>(c, op, T);
-            else if (op.aux1 / op.aux0 == 2) op_attention<2>(c, op, T);
-            else op_attention<8>(c, op, T);
+            op_attention(c, op, T);
             break;
-          case OP_SILU_MUL: op_silu_mul(c, op, T); break;
-          case OP_ARGMAX_PARTIAL: op_argmax_partial(c, op, T); break;
-          case OP_ARGMAX_REDUCE: op_argmax_reduce(c, op, T); break;
-          default: break;
+          case OP_SILU_MUL: if (!op_barrier(c, op)) op_silu_mul(c, op, T); break;
+          case OP_ARGMAX_PARTIAL: if (!op_barrier(c, op)) op_argmax_partial(c, op, T); break;
+          case OP_ARGMAX_REDUCE: if (!op_barrier(c, op)) op_argmax_reduce(c, op, T); break;
+          default: op_barrier(c, op); break;
         }
+        if (pr && c.tid == 0) pr[2] = globaltimer();
+        if (c.dead) break;
       }
       if (p.mode == MODE_ONEPASS) break;
       if (aborted(c)) {

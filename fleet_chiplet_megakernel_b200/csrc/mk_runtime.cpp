@@ -106,6 +106,8 @@ struct mk_handle {
   int max_nblk = 1;
   int64_t weight_bytes = 0;
   bool launched = false;
+  void* prof_ptr = nullptr;
+  int64_t prof_entries = 0;
 
   int fail(int code, const char* fmt, ...) {
     char buf[1024];
@@ -338,8 +340,8 @@ int plan_graph(mk_handle* h) {
       if (kc.dims[0] != cfg.max_num_pages || kc.dims[1] != cfg.page_size || kc.dims[2] != po.aux0)
         return h->fail(MK_E_INVALID, "attention: KV cache must be [max_num_pages, page_size, kv_heads, 128]");
       const int qpk = po.aux0 > 0 ? po.aux1 / po.aux0 : 0;
-      if (po.aux0 <= 0 || po.aux1 % po.aux0 || (qpk != 2 && qpk != 4 && qpk != 8))
-        return h->fail(MK_E_UNSUPPORTED, "attention: q heads per kv head must be 2, 4 or 8");
+      if (po.aux0 <= 0 || po.aux1 % po.aux0 || (qpk != 1 && qpk != 2 && qpk != 4 && qpk != 8))
+        return h->fail(MK_E_UNSUPPORTED, "attention: q heads per kv head must be 1, 2, 4 or 8");
       if (qkv.dims[1] != (int64_t)(po.aux1 + 2 * po.aux0) * mk::kHeadDim || to.dims[1] != (int64_t)po.aux1 * mk::kHeadDim)
         return h->fail(MK_E_INVALID, "attention: qkv/output widths do not match the head counts");
       po.aux2 = (int)h->tensors[po.cos].dims[0];
@@ -577,6 +579,15 @@ int mk_set_meta(mk_handle* h, void* const meta[10], int64_t total_num_requests, 
   return 0;
 }
 
+int mk_set_profiler(mk_handle* h, void* ptr, int64_t n_entries) {
+  if (!h) return MK_E_INVALID;
+  if (h->compiled) return h->fail(MK_E_STATE, "set the profiler buffer before compile");
+  if (ptr && (n_entries <= 0 || (((uintptr_t)ptr) & 7))) return h->fail(MK_E_INVALID, "profiler buffer must be 8-byte aligned and non-empty");
+  h->prof_ptr = ptr;
+  h->prof_entries = ptr ? n_entries : 0;
+  return 0;
+}
+
 int mk_plan(mk_handle* h) {
   if (!h) return MK_E_INVALID;
   const mk_config& c = h->cfg;
@@ -665,27 +676,36 @@ int mk_compile(mk_handle* h) {
       if (int e = materialise_shuffle(h, t)) return e;
   if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return h->cuda_fail(ce, "shuffle copies");
 
-  // 2. shared-memory carve-up
+  // 2. shared-memory carve-up: the activations of one pass (up to 8 token rows of the widest
+  // linear op, fewer if they would leave less than 6 weight stages) plus the weight ring
   const int tb_max = std::min(mk::kMaxTokGroup, cfg.max_num_batched_tokens);
+  const int x_budget = kMaxSmem - 1024 - kRedBytes - 1024 - 6 * mk::kStageBytes;
   int x_bytes = cfg.max_num_pages * 4;
-  int max_nblk = 1, n_linear = 0;
-  for (const PlanOp& p : h->plan) {
+  int max_nblk = 1, n_linear = 0, min_tpp = tb_max;
+  for (PlanOp& p : h->plan) {
     if (p.type == mk::OP_LINEAR) {
       const int kp = (p.k + mk::kTileK - 1) / mk::kTileK * mk::kTileK;
-      x_bytes = std::max(x_bytes, tb_max * kp * 2);
+      const int row_bytes = (kp + 8) * 2;
+      int tpp = std::min(tb_max, (x_budget - 16) / row_bytes);
+      if (tpp < 1) return h->fail(MK_E_UNSUPPORTED, "K=%d is too wide for the shared-memory activation buffer", p.k);
+      p.aux3 = tpp;
+      min_tpp = std::min(min_tpp, tpp);
+      x_bytes = std::max(x_bytes, tpp * row_bytes + 16);
       max_nblk = std::max(max_nblk, (p.n + mk::kTileRows - 1) / mk::kTileRows);
       ++n_linear;
     } else if (p.type == mk::OP_RMSNORM) {
-      x_bytes = std::max(x_bytes, (p.n + 63) / 64 * 64 * 2);
+      x_bytes = std::max(x_bytes, ((p.n + 63) / 64 * 64 + 8) * 2 + 16);
     } else if (p.type == mk::OP_ATTN) {
       const int qpk = p.aux1 / p.aux0;
-      x_bytes = std::max(x_bytes, 16 * qpk * (mk::kHeadDim + 2) * 4);
+      (void)qpk;
+      x_bytes = std::max(x_bytes, 16 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 256);
     }
   }
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
   const int fixed = 1024 /*alignment slack*/ + x_bytes + kRedBytes + 1024 /*barriers, flags*/;
   int stages = (kMaxSmem - fixed) / mk::kStageBytes;
   stages = std::min(stages, 24);
+  if (cfg.max_stages > 0) stages = std::min(stages, cfg.max_stages);
   if (stages < 2) return h->fail(MK_E_UNSUPPORTED, "activations need %d bytes of shared memory; too large for the CUDA-core path", x_bytes);
   mk::KParams& kp = h->kp;
   memset(&kp, 0, sizeof(kp));
@@ -703,7 +723,7 @@ int mk_compile(mk_handle* h) {
 
   // 3. scratch and state
   const int G = h->grid;
-  const int groups = (cfg.max_num_batched_tokens + mk::kMaxTokGroup - 1) / mk::kMaxTokGroup;
+  const int groups = (cfg.max_num_batched_tokens + min_tpp - 1) / min_tpp;
   void* p = nullptr;
   if (int e = h->dmalloc(&p, (size_t)groups * G * 2 * mk::kTileRows * mk::kMaxTokGroup * 4)) return e;
   kp.partial = (float*)p;
@@ -846,6 +866,14 @@ int mk_compile(mk_handle* h) {
   kp.eos = cfg.eos_token_id;
   kp.max_iters = cfg.max_iterations;
   kp.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+  kp.trace_op = -1;
+  kp.debug_flags = cfg.debug_flags;
+  if (h->prof_ptr) {
+    const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;
+    if (h->prof_entries < need) return h->fail(MK_E_INVALID, "profiler buffer has %lld words, the trace needs %lld", (long long)h->prof_entries, (long long)need);
+    kp.prof = (unsigned long long*)h->prof_ptr;
+    kp.trace_op = cfg.trace_op - 1;
+  }
   h->compiled = true;
   if (cfg.mode == MK_MODE_OFFLINE) return mk_init_requests(h, nullptr);
   return 0;

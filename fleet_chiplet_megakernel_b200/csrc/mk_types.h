@@ -17,7 +17,7 @@ constexpr int kStageBytes = kTileRows * kTileK * 2;
 constexpr int kNumConsumerWarps = 8;
 constexpr int kNumConsumers = kNumConsumerWarps * 32;
 constexpr int kNumThreads = kNumConsumers + 32;  // + one TMA producer warp
-constexpr int kMaxTokGroup = 4;                  // tokens per CUDA-core pass
+constexpr int kMaxTokGroup = 8;                  // tokens per pass of a linear op (one mma n-tile)
 constexpr int kHeadDim = 128;
 
 enum OpType : int {
@@ -133,6 +133,11 @@ struct KParams {
   float* attn_part;       // [tokens][kv heads][max chunks][qpk*(128+2)]
   unsigned* attn_count;   // [tokens][kv heads]
   int attn_max_chunks;
+  // optional per-op trace of the last iteration: [(op * grid + cta) * 4 + k] globaltimer ns,
+  // k = 0 op reached, 1 barrier passed, 2 op done; op == num_ops is the iteration prologue
+  unsigned long long* prof;
+  int trace_op;     // op whose inner phases are stamped: prof[(num_ops + 1) * grid * 4 + cta * 16 + k]; -1 none
+  int debug_flags;  // bit 0: linear tasks skip the arithmetic
   // shared-memory carve-up (bytes from the 1024-aligned base)
   int num_stages;
   int x_off, x_bytes;

@@ -105,6 +105,8 @@ class PersistentKernel:
         fuse: bool | None = None,
         max_iterations: int = 0,
         timeout_ms: int = 0,
+        trace_op: int = -1,
+        debug_flags: int = 0,
     ):
         self.__finalized__ = False
         self._is_compiled = False
@@ -176,6 +178,9 @@ class PersistentKernel:
         cfg.max_iterations = int(max_iterations)
         cfg.timeout_ms = int(timeout_ms)
         cfg.device = -1
+        cfg.trace_op = int(trace_op) + 1
+        cfg.debug_flags = int(debug_flags)
+        cfg.max_stages = int(os.environ.get("B200MK_MAX_STAGES", "0"))
         self._h = self._lib.mk_create(C.byref(cfg))
         if not self._h:
             raise RuntimeError("mk_create failed")
@@ -398,6 +403,9 @@ class PersistentKernel:
         ptrs = (C.c_void_p * 10)(*[C.c_void_p(self.meta_tensors[k].data_ptr()) for k in _META_ORDER])
         prof = C.c_void_p(self.profiler_tensor.data_ptr()) if self.profiler_tensor is not None else None
         self._check(self._lib.mk_set_meta(self._h, ptrs, self.total_num_requests, prof), "set_meta")
+        if self.profiler_tensor is not None:
+            assert self.profiler_tensor.dtype in (torch.uint64, torch.int64)
+            self._check(self._lib.mk_set_profiler(self._h, prof, self.profiler_tensor.numel()), "set_profiler")
         self._check(self._lib.mk_compile(self._h), "compile")
         self._is_compiled = True
 
@@ -428,6 +436,15 @@ class PersistentKernel:
         buf = (C.c_uint64 * (2 * max_entries))()
         n = self._check(self._lib.mk_get_event_timing(self._h, buf, max_entries), "get_event_timing")
         return np.ctypeslib.as_array(buf)[: 2 * n].reshape(n, 2).copy()
+
+    def num_device_ops(self):
+        return self._check(self._lib.mk_num_device_ops(self._h), "num_device_ops")
+
+    def op_trace(self):
+        """The profiler tensor as [ops + 1, grid, 4] int64 ns (row `ops` = iteration prologue)."""
+        assert self.profiler_tensor is not None and self._is_compiled
+        n, g = self.num_device_ops() + 1, self.grid_size()
+        return self.profiler_tensor.view(torch.int64)[: n * g * 4].reshape(n, g, 4).cpu()
 
     def grid_size(self):
         return self._check(self._lib.mk_grid_size(self._h), "grid_size")

@@ -158,7 +158,8 @@ class Qwen3Decoder:
     def __init__(self, geom: Qwen3Geometry, weights: dict, max_seq_length: int, max_requests: int,
                  total_requests: int | None = None, page_size: int = 64, max_num_pages: int | None = None,
                  device="cuda", numerics=None, fuse=None, keep_logits=False, eos_token_id: int = 0x7FFFFFFF,
-                 max_iterations: int = 0, num_layers=None, timeout_ms: int = 0):
+                 max_iterations: int = 0, num_layers=None, timeout_ms: int = 0, trace: bool = False,
+                 trace_op: int = -1, debug_flags: int = 0):
         self.geom, self.device = geom, torch.device(device)
         R = max_requests
         total = total_requests if total_requests is not None else R
@@ -181,6 +182,7 @@ class Qwen3Decoder:
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(geom, max(max_seq_length, 8), dev)
         self.logits = torch.zeros(R, weights["lm_head"].shape[0], dtype=torch.bfloat16, device=dev) if keep_logits else None
+        self.profiler = torch.zeros(1 << 20, dtype=torch.int64, device=dev) if trace else None
         self.mpk = PersistentKernel(
             mode="offline", world_size=1, mpi_rank=0, num_workers=0, num_local_schedulers=0,
             num_remote_schedulers=0, max_seq_length=max_seq_length, max_num_batched_requests=R,
@@ -190,9 +192,9 @@ class Qwen3Decoder:
                           "prompt_lengths": self.prompt_lengths, "qo_indptr_buffer": self.qo_indptr,
                           "paged_kv_indptr_buffer": self.kv_indptr, "paged_kv_indices_buffer": self.kv_indices,
                           "paged_kv_last_page_len_buffer": self.kv_last_page_len},
-            profiler_tensor=None, trace_name="", spec_decode_config=None, use_cutlass_kernel=True,
+            profiler_tensor=self.profiler, trace_name="", spec_decode_config=None, use_cutlass_kernel=True,
             eos_token_id=eos_token_id, numerics=numerics, fuse=fuse, max_iterations=max_iterations,
-            timeout_ms=timeout_ms)
+            timeout_ms=timeout_ms, trace_op=trace_op, debug_flags=debug_flags)
         build_qwen3_graph(self.mpk, geom, weights, self.k_cache, self.v_cache, self.cos, self.sin,
                           self.input_tokens, self.output_tokens, logits=self.logits, num_layers=num_layers)
         self.mpk.compile()

@@ -51,7 +51,10 @@ typedef struct mk_config {
   int32_t max_iterations;           /* 0 = run until every request has finished */
   int64_t timeout_ms;               /* bound of every in-kernel wait; 0 = default (4000) */
   int32_t device;                   /* CUDA device ordinal, -1 = current */
-  int32_t reserved[7];
+  int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer, -1 = none (stored +1: 0 = none) */
+  int32_t debug_flags;              /* bit 0: linear tasks skip the arithmetic (weight-stream timing only) */
+  int32_t max_stages;               /* cap on the weight ring depth, 0 = as many 16 KB stages as fit */
+  int32_t reserved[4];
 } mk_config;
 
 /* PersistentKernel.__init__ -> KNGraph(CyKNGraph(...)) (persistent_kernel.py:404). */
@@ -90,6 +93,13 @@ int mk_op(mk_handle* h, const char* op_name, const int* tensor_ids, int n_tensor
  * Stands in for init_func (persistent_kernel.py:35) / init_persistent_kernel
  * (persistent_kernel.cuh:1966). */
 int mk_set_meta(mk_handle* h, void* const meta_ptrs[10], int64_t total_num_requests, void* profiler_ptr);
+
+/* profiler_tensor of the constructor (persistent_kernel.py:361-362, profiler.h:116-181): a
+ * caller-owned uint64 device buffer of n_entries words.  When set before mk_compile, the
+ * kernel leaves a trace of the LAST iteration in it: word [(op * grid + cta) * 4 + k] is the
+ * globaltimer (ns) at which CTA `cta` reached device op `op` (k=0), passed its barrier (k=1)
+ * and finished it (k=2); op == mk_num_device_ops() is the iteration prologue. */
+int mk_set_profiler(mk_handle* h, void* device_ptr, int64_t n_entries);
 
 /* compile (persistent_kernel.py:2404-2618; generate_task_graph, src/kernel/runtime.cc:1652):
  * validates the graph, lowers it to the device program, materialises shuffled
