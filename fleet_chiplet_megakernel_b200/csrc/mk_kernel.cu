@@ -61,6 +61,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -181,8 +184,8 @@ __device__ __noinline__ void grid_sync(Ctx& c) {
   consumer_sync();
   if (c.tid == 0) {
     c.epoch += 1;
-    __threadfence();
-    atomicAdd(c.p.grid_bar, 1u);
+    // arrive with a release reduction: nothing comes back, polling starts at once
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
     const unsigned target = c.epoch * gridDim.x;
     unsigned long long t0 = 0;
     unsigned spins = 0;
@@ -244,19 +247,64 @@ __device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
 // (pitch = padded K + 8 elements, so that the 8 token rows of an ldmatrix hit 8
 // different banks), zero padded, followed by one 16-byte chunk of zeros that
 // stands in for the rows of absent tokens.
+// `pre_w`: this thread's two norm-weight vectors (index tid and tid + 256), loaded by the
+// caller ahead of the op's barrier; only used when the row has at most 512 vectors.
 __device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0, int rows,
-                        int T) {
+                        int T, const uint4* pre_w) {
   const KParams& p = c.p;
   uint4* xs = reinterpret_cast<uint4*>(c.smem + p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3;
   const int kvec = K >> 3;
   if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);
+  const bool small = norm_w != nullptr && pre_w != nullptr && nvec <= 2 * kNumConsumers;
 #pragma unroll 1
   for (int tb = 0; tb < rows; ++tb) {
     const int tok = tok0 + tb;
     const bool valid = tok < T;
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)tok * ld_in);
+    if (small) {
+      // the row stays in registers between the sum of squares and the scaling
+      uint4 raw[2];
+      float f[2][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int v = c.tid + i * kNumConsumers;
+        raw[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        unpack8(raw[i], f[i]);
+        if (p.numerics == NUM_TORCH) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += rbf(f[i][j] * f[i][j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += f[i][j] * f[i][j];
+        }
+      }
+      const float tot = block_sum(c, ss);
+      float r;
+      if (p.numerics == NUM_TORCH) r = torch_rsqrt_bf16(rbf(tot / (float)K), true);
+      else r = rsqrtf(tot / (float)K + 1e-6f);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int v = c.tid + i * kNumConsumers;
+        float w[8];
+        unpack8(pre_w[i], w);
+        if (p.numerics == NUM_TORCH) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[i][j] = w[j] * rbf(f[i][j] * r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[i][j] = f[i][j] * (r * w[j]);
+        }
+        if (v < nvec) xs[tb * pitch + v] = (v < kvec) ? pack8(f[i]) : make_uint4(0, 0, 0, 0);
+      }
+      if (c.tid == 0) xs[tb * pitch + nvec] = make_uint4(0, 0, 0, 0);  // the row's padding vector
+      continue;
+    }
     float ss = 0.f;
 #pragma unroll 1
     for (int v = c.tid; v < nvec + 1; v += kNumConsumers) {
@@ -278,31 +326,23 @@ __device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const 
     if (norm_w != nullptr) {
       const float tot = block_sum(c, ss);
       const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
-      if (p.numerics == NUM_TORCH) {
-        // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
-        // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
-        const float var = rbf(tot / (float)K);
-        const float r = torch_rsqrt_bf16(var, true);
+      // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
+      // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
+      const bool torch_num = p.numerics == NUM_TORCH;
+      const float r = torch_num ? torch_rsqrt_bf16(rbf(tot / (float)K), true) : rsqrtf(tot / (float)K + 1e-6f);
 #pragma unroll 1
-        for (int v = c.tid; v < kvec; v += kNumConsumers) {
-          float f[8], w[8];
-          unpack8(xs[tb * pitch + v], f);
-          unpack8(__ldg(wv + v), w);
+      for (int v = c.tid; v < kvec; v += kNumConsumers) {
+        float f[8], w[8];
+        unpack8(xs[tb * pitch + v], f);
+        unpack8(__ldg(wv + v), w);
+        if (torch_num) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = w[i] * rbf(f[i] * r);
-          xs[tb * pitch + v] = pack8(f);
-        }
-      } else {
-        const float r = rsqrtf(tot / (float)K + 1e-6f);
-#pragma unroll 1
-        for (int v = c.tid; v < kvec; v += kNumConsumers) {
-          float f[8], w[8];
-          unpack8(xs[tb * pitch + v], f);
-          unpack8(__ldg(wv + v), w);
+        } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = f[i] * (r * w[i]);
-          xs[tb * pitch + v] = pack8(f);
         }
+        xs[tb * pitch + v] = pack8(f);
       }
     }
   }
@@ -352,7 +392,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 constexpr int kRedStride = kMaxTokGroup;  // floats per row in the shared sums block
 
 // ntok tokens starting at tok0; sums at red[row * kRedStride + token]
-__device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int ntok) {
+__device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int ntok, float res0) {
   const KParams& p = c.p;
   const float* red = c.red();
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
@@ -381,7 +421,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     if (col < op.n) {
       float v = red[row * kRedStride + tb];
       if (with_res) {
-        const float r = __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
+        const float r = (e < kNumConsumers) ? res0 : __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
         v = (p.numerics == NUM_TORCH) ? rbf(v) + r : v + r;
       }
       out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(v);
@@ -433,18 +473,18 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 // without waiting for anything; the finisher waits (bounded) until they have all
 // arrived, adds the pieces in CTA order and runs the epilogue.
 __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int blk, int kt_first, int kt_last,
-                                                 bool first_of_cta, int tok0, int ntok, int group) {
+                                                 bool first_of_cta, int tok0, int ntok, int group, float res0) {
   const KParams& p = c.p;
   float* red = c.red();
   consumer_sync();
   const bool whole = (kt_first == 0) && (kt_last == op.nkt - 1);
   if (!whole) {
-    const long long total = (long long)op.nblk * op.nkt;
-    const int G = (int)min((long long)gridDim.x, total);  // CTAs that hold tiles of this op
+    const unsigned total = (unsigned)op.nblk * (unsigned)op.nkt;
+    const int G = (int)min(gridDim.x, total);  // CTAs that hold tiles of this op
     const int GS = gridDim.x;
     const size_t slot_elems = (size_t)kTileRows * kRedStride;
-    const int c_first = tile_owner((long long)blk * op.nkt, total, G);
-    const int c_last = tile_owner((long long)blk * op.nkt + op.nkt - 1, total, G);
+    const int c_first = tile_owner((unsigned)blk * op.nkt, total, G);
+    const int c_last = tile_owner((unsigned)blk * op.nkt + op.nkt - 1, total, G);
     unsigned* cnt = p.piece_count + (size_t)group * p.piece_stride + blk;
     float4* red4 = reinterpret_cast<float4*>(red);
     if ((int)blockIdx.x != c_first) {
@@ -503,7 +543,7 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
     red4[c.tid] = acc;
     consumer_sync();
   }
-  linear_epilogue(c, op, blk, tok0, ntok);
+  linear_epilogue(c, op, blk, tok0, ntok, res0);
   consumer_sync();
 }
 
@@ -511,20 +551,20 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
 // budget) and the passes its weight stream makes for T active tokens.
 __device__ __forceinline__ int linear_passes(const OpDesc& op, int T) { return (T + op.aux3 - 1) / op.aux3; }
 
-__device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int T, int group) {
+__device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int T, int group, const uint4* pre_w) {
   const KParams& p = c.p;
   const int nkt = op.nkt;
   const int kp = nkt * kTileK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T);
+  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
   MK_STAMP(c, 1);
 
-  const long long total = (long long)op.nblk * nkt;
-  const int G = (int)min((long long)gridDim.x, total);  // with fewer tiles than CTAs the rest idle
+  const unsigned total = (unsigned)op.nblk * (unsigned)nkt;
+  const int G = (int)min(gridDim.x, total);  // with fewer tiles than CTAs the rest idle
   if ((int)blockIdx.x >= G) return;
-  const long long t0 = tile_begin(blockIdx.x, total, G);
-  const long long t1 = tile_begin(blockIdx.x + 1, total, G);
+  const unsigned t0 = tile_begin(blockIdx.x, total, G);
+  const unsigned t1 = tile_begin(blockIdx.x + 1, total, G);
   const int S = p.num_stages;
   const int lane = c.lane, warp = c.warp;
   // A operand: lane l addresses row 16*warp + (l & 7) + 8 * ((l >> 3) & 1), 16-byte chunk 2*kb + (l >> 4)
@@ -540,29 +580,45 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
   const uint32_t b_row = xs0 + (uint32_t)((lane & 7) * pitch_b + (lane >> 3) * 16);
   const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
 
+  // The residual element this thread adds first in the epilogue of a row block is requested
+  // when the block starts, a whole run of tiles ahead of its use.
+  const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
+  const __nv_bfloat16* res_ptr = reinterpret_cast<const __nv_bfloat16*>(op.res) +
+                                 (size_t)(tok0 + (c.tid >> 7)) * op.ld_res + (c.tid & 127);
+  const bool res_tok = with_res && (c.tid >> 7) < ntok;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  int blk = (int)(t0 / nkt);
-  int kt = (int)(t0 - (long long)blk * nkt);
+  int blk = (int)(t0 / (unsigned)nkt);
+  int kt = (int)(t0 - (unsigned)blk * (unsigned)nkt);
   int kt_first = kt;
   bool first_of_cta = true;
   int s = (int)(c.cons_idx % (unsigned)S);
   uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
   unsigned consumed = 0;
   const bool arith = !(p.debug_flags & 1);
-  for (long long tile = t0; tile < t1; ++tile) {
+  float res0 = 0.f;
+  bool new_blk = true;
+  for (unsigned tile = t0; tile < t1; ++tile) {
+    if (new_blk) {
+      new_blk = false;
+      res0 = 0.f;
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+    }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
     if (tile == t0) MK_STAMP(c, 2);
     const uint32_t st = c.smem_addr + (uint32_t)s * kStageBytes + a_base;
     if (arith) {
-      uint32_t b[8];
-      const uint32_t bk = b_real ? b_row + (uint32_t)kt * (kTileK * 2) : b_zero;
-      ldmatrix_x4(bk, b[0], b[1], b[2], b[3]);
-      ldmatrix_x4(b_real ? bk + 64 : b_zero, b[4], b[5], b[6], b[7]);
 #pragma unroll
-      for (int kb = 0; kb < 4; ++kb) {
-        uint32_t a0, a1, a2, a3;
-        ldmatrix_x4(st + ((((uint32_t)(2 * kb) + a_hi) ^ a_xor) << 4), a0, a1, a2, a3);
-        mma_bf16(acc, a0, a1, a2, a3, b[2 * kb], b[2 * kb + 1]);
+      for (int sub = 0; sub < kSubTiles; ++sub) {
+        uint32_t b[8];
+        const uint32_t bk = b_real ? b_row + (uint32_t)kt * (kTileK * 2) + (uint32_t)sub * (kBoxK * 2) : b_zero;
+        ldmatrix_x4(bk, b[0], b[1], b[2], b[3]);
+        ldmatrix_x4(b_real ? bk + 64 : b_zero, b[4], b[5], b[6], b[7]);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4(st + (uint32_t)sub * kSubBytes + ((((uint32_t)(2 * kb) + a_hi) ^ a_xor) << 4), a0, a1, a2, a3);
+          mma_bf16(acc, a0, a1, a2, a3, b[2 * kb], b[2 * kb + 1]);
+        }
       }
     }
     __syncwarp();
@@ -582,7 +638,7 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
       red[8 * kRedStride] = acc[2];
       red[8 * kRedStride + 1] = acc[3];
       acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-      linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group);
+      linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group, res0);
       first_of_cta = false;
       kt_first = 0;
       if (tile == t1 - 1) MK_STAMP(c, 4);
@@ -590,6 +646,7 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
     if (end_blk) {
       kt = 0;
       blk += 1;
+      new_blk = true;
     } else {
       kt += 1;
     }
@@ -598,9 +655,19 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
 }
 
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
+  // the norm weights do not depend on other CTAs: fetched ahead of the barrier
+  uint4 pre_w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  const bool pre = (op.flags & F_NORM_IN) && (op.k >> 3) <= 2 * kNumConsumers;
+  if (pre) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = c.tid + i * kNumConsumers;
+      if (v < (op.k >> 3)) pre_w[i] = __ldg(reinterpret_cast<const uint4*>(op.norm_w) + v);
+    }
+  }
   if (op_barrier(c, op)) return;
   const int passes = linear_passes(op, T);
-  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g);
+  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, pre ? pre_w : nullptr);
 }
 
 // ------------------------------------------------------------------------------------
@@ -903,39 +970,50 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       if (fl[2] != 0) {  // the chunk that arrives last merges all of them
         __threadfence();
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
-        // (max, sum) of every chunk and head into shared memory with one round of loads
-        float* sm_pm = sm_l + 16;                        // [chunks][qpk]
-        float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
+        // every load of the merge (values, maxima, sums of up to 8 chunks, for two output
+        // elements) goes out before the first use: one L2 round trip per batch
+        const int nout = pl.qpk * kHeadDim;
 #pragma unroll 1
-        for (int i = c.tid; i < a.nch * pl.qpk; i += kNumConsumers) {
-          const float* pm = base + (size_t)(i / pl.qpk) * part_stride + pl.qpk * kHeadDim + (i % pl.qpk);
-          sm_pm[i] = __ldcg(pm);
-          sm_pl[i] = __ldcg(pm + pl.qpk);
-        }
-        consumer_sync();
-#pragma unroll 1
-        for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
-          const int eh = e >> 7;
-          float M = -INFINITY;
-#pragma unroll 1
-          for (int cc = 0; cc < a.nch; ++cc) M = fmaxf(M, sm_pm[cc * pl.qpk + eh]);
-          float Ls = 0.f, O = 0.f;
+        for (int e0 = c.tid; e0 < nout; e0 += 2 * kNumConsumers) {
+          float M[2] = {-INFINITY, -INFINITY}, Ls[2] = {0.f, 0.f}, O[2] = {0.f, 0.f};
 #pragma unroll 1
           for (int c0 = 0; c0 < a.nch; c0 += 8) {
-            float v[8];
+            float v[2][8], mm[2][8], ll[2][8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-              v[u] = (c0 + u < a.nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
+            for (int q = 0; q < 2; ++q) {
+              const int e = e0 + q * kNumConsumers;
+              const float* pm = base + nout + (e >> 7);
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              if (c0 + u < a.nch) {
-                const float f = exp2f(sm_pm[(c0 + u) * pl.qpk + eh] - M);
-                Ls += f * sm_pl[(c0 + u) * pl.qpk + eh];
-                O += f * v[u];
+              for (int u = 0; u < 8; ++u) {
+                const bool ok = (c0 + u < a.nch) && (e < nout);
+                const size_t off = (size_t)(c0 + u) * part_stride;
+                v[q][u] = ok ? __ldcg(base + off + e) : 0.f;
+                mm[q][u] = ok ? __ldcg(pm + off) : -INFINITY;
+                ll[q][u] = ok ? __ldcg(pm + off + pl.qpk) : 0.f;
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              float Mn = M[q];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, mm[q][u]);
+              const float resc = (M[q] == -INFINITY) ? 0.f : exp2f(M[q] - Mn);
+              Ls[q] *= resc;
+              O[q] *= resc;
+              M[q] = Mn;
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float f = (mm[q][u] == -INFINITY) ? 0.f : exp2f(mm[q][u] - Mn);
+                Ls[q] += f * ll[q][u];
+                O[q] += f * v[q][u];
               }
             }
           }
-          out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int e = e0 + q * kNumConsumers;
+            if (e < nout) out[e] = __float2bfloat16_rn(__fdividef(O[q], Ls[q]));
+          }
         }
         if (c.tid == 0) *cnt = 0u;
       }
@@ -970,7 +1048,7 @@ __device__ void op_embed(Ctx& c, const OpDesc& op, int T) {
 __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   const int kp = ((op.n + 63) / 64) * 64;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1);
+    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1, nullptr);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out);
     for (int v = c.tid; v < (op.n >> 3); v += kNumConsumers) dst[v] = xs[v];
@@ -1168,12 +1246,65 @@ __device__ __noinline__ int bookkeep_prepare(Ctx& c) {
 // ------------------------------------------------------------------------------------
 // the TMA producer
 // ------------------------------------------------------------------------------------
+// Position in this CTA's weight-tile sequence: the linear ops in program order, each
+// with the CTA's contiguous tile range.
+struct TileCursor {
+  int oi;
+  unsigned tile, t1;
+  int blk, kt, nkt;
+  const void* tmap;
+  bool valid;
+};
+
+// Open the CTA's range of linear op `oi`; false if the op is not linear or gives this CTA nothing.
+__device__ __forceinline__ bool cursor_open(const KParams& p, TileCursor& tc, int oi) {
+  const OpDesc& op = p.ops[oi];
+  if (op.type != OP_LINEAR) return false;
+  const unsigned total = (unsigned)op.nblk * (unsigned)op.nkt;
+  const int G = (int)min(gridDim.x, total);
+  if ((int)blockIdx.x >= G) return false;
+  tc.oi = oi;
+  tc.tile = tile_begin(blockIdx.x, total, G);
+  tc.t1 = tile_begin(blockIdx.x + 1, total, G);
+  tc.nkt = op.nkt;
+  tc.blk = (int)(tc.tile / (unsigned)op.nkt);
+  tc.kt = (int)(tc.tile - (unsigned)tc.blk * (unsigned)op.nkt);
+  tc.tmap = op.tmap_w;
+  return tc.tile < tc.t1;
+}
+
+// Step the look-ahead cursor one tile, wrapping from the last linear op to the first
+// (the next iteration streams the same weights).
+__device__ __forceinline__ void cursor_advance_wrap(const KParams& p, TileCursor& tc) {
+  tc.tile += 1;
+  if (++tc.kt == tc.nkt) {
+    tc.kt = 0;
+    tc.blk += 1;
+  }
+  if (tc.tile < tc.t1) return;
+  int oi = tc.oi;
+  for (int n = 0; n < p.num_ops; ++n) {
+    oi = (oi + 1 == p.num_ops) ? 0 : oi + 1;
+    if (cursor_open(p, tc, oi)) return;
+  }
+  tc.valid = false;
+}
+
 __device__ __noinline__ void producer_loop(Ctx& c) {
   const KParams& p = c.p;
   const int S = p.num_stages;
-  const int G = gridDim.x;
   volatile int* fl = c.flags();
   unsigned issued = 0;
+  int s = 0;
+  uint32_t empty_parity = 1;  // a fresh barrier passes a wait on the "previous" phase
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
+  // look-ahead: tiles beyond the shared-memory ring are requested into L2 so that HBM
+  // keeps streaming while the consumers sit in barriers, staging and epilogues
+  TileCursor pc;
+  pc.valid = false;
+  int ahead = 0;
+  if (p.prefetch_tiles > 0)
+    for (int oi = 0; oi < p.num_ops && !pc.valid; ++oi) pc.valid = cursor_open(p, pc, oi);
   for (int iter = 1;; ++iter) {
     // wait for the consumers to publish this iteration's token count (or the end)
     int go;
@@ -1200,32 +1331,40 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     const int T = go & 255;
     bool dead = false;
     for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
-      const OpDesc& op = p.ops[oi];
-      if (op.type != OP_LINEAR) continue;
-      const int passes = linear_passes(op, T);
-      const long long total = (long long)op.nblk * op.nkt;
-      const int Gop = (int)min((long long)G, total);
-      if ((int)blockIdx.x >= Gop) continue;
-      const long long t0 = tile_begin(blockIdx.x, total, Gop);
-      const long long t1 = tile_begin(blockIdx.x + 1, total, Gop);
+      TileCursor lc;
+      if (!cursor_open(p, lc, oi)) continue;
+      const int passes = linear_passes(p.ops[oi], T);
+      const unsigned t0 = lc.tile;
       for (int g = 0; g < passes && !dead; ++g) {
-        int blk = (int)(t0 / op.nkt);
-        int kt = (int)(t0 - (long long)blk * op.nkt);
-        for (long long tile = t0; tile < t1; ++tile) {
-          const int s = issued % S;
-          if (!mbar_wait(c, c.empty_bar(s), ((issued / S) & 1) ^ 1, ST_TIMEOUT_EMPTY)) {
+        if (g > 0) cursor_open(p, lc, oi);
+        for (unsigned tile = t0; tile < lc.t1; ++tile) {
+          if (g == 0 && pc.valid) {
+            while (ahead < p.prefetch_tiles) {
+              tma_prefetch_2d(pc.tmap, pc.kt * kTileK, pc.blk * kTileRows);
+              tma_prefetch_2d(pc.tmap, pc.kt * kTileK + kBoxK, pc.blk * kTileRows);
+              cursor_advance_wrap(p, pc);
+              ++ahead;
+            }
+            --ahead;
+          }
+          if (!mbar_wait(c, bar_empty0 + 8 * s, empty_parity, ST_TIMEOUT_EMPTY)) {
             dead = true;
             break;
           }
-          mbar_arrive_expect_tx(c.full_bar(s), kStageBytes);
-          tma_load_2d(c.smem_addr + s * kStageBytes, op.tmap_w, c.full_bar(s), kt * kTileK, blk * kTileRows);
+          const uint32_t full = bar_full0 + 8 * s;
+          const uint32_t dst = c.smem_addr + (uint32_t)s * kStageBytes;
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_2d(dst, lc.tmap, full, lc.kt * kTileK, lc.blk * kTileRows);
+          tma_load_2d(dst + kSubBytes, lc.tmap, full, lc.kt * kTileK + kBoxK, lc.blk * kTileRows);
           issued += 1;
-#ifndef MK_ISSUED_LAZY
           fl[1] = (int)issued;
-#endif
-          if (++kt == op.nkt) {
-            kt = 0;
-            ++blk;
+          if (++s == S) {
+            s = 0;
+            empty_parity ^= 1u;
+          }
+          if (++lc.kt == lc.nkt) {
+            lc.kt = 0;
+            lc.blk += 1;
           }
         }
       }
@@ -1321,8 +1460,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       if (T > 255) T = 255;
       if (c.tid == 0) fl[0] = (iter << 8) | T;
 
+      // The op descriptors are read from a two-slot copy in shared memory: the next op's
+      // descriptor is fetched asynchronously while the current op runs, so that no op starts
+      // with a round trip to L2 for its own parameters.
+      constexpr int kDescVecs = (int)(sizeof(OpDesc) / 16);
+      OpDesc* sdesc = reinterpret_cast<OpDesc*>(c.smem + p.bar_off + 512);
+      if (c.tid < kDescVecs)
+        reinterpret_cast<uint4*>(&sdesc[0])[c.tid] = __ldg(reinterpret_cast<const uint4*>(&p.ops[0]) + c.tid);
       for (int oi = 0; oi < p.num_ops; ++oi) {
-        const OpDesc& op = p.ops[oi];
+        if (c.tid < kDescVecs) asm volatile("cp.async.wait_all;" ::: "memory");
+        consumer_sync();
+        const OpDesc& op = sdesc[oi & 1];
+        if (oi + 1 < p.num_ops && c.tid < kDescVecs) {
+          const uint32_t dst = smem_u32(&sdesc[(oi + 1) & 1]) + 16 * c.tid;
+          const void* src = reinterpret_cast<const uint4*>(&p.ops[oi + 1]) + c.tid;
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        }
         c.cur_op = oi;
         unsigned long long* pr = prof ? prof + ((size_t)oi * gridDim.x + blockIdx.x) * 4 : nullptr;
         c.dbg = (prof && oi == p.trace_op) ? prof + ((size_t)(p.num_ops + 1) * gridDim.x) * 4 + (size_t)blockIdx.x * 16 : nullptr;

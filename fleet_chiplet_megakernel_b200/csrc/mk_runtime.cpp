@@ -637,10 +637,11 @@ int mk_tensor_read(mk_handle* h, int id, void* host_buf, int64_t bytes) {
 
 int mk_debug_partition(int64_t nblk, int64_t nkt, int grid, int64_t* begin_out, int* owner_check) {
   if (nblk < 1 || nkt < 1 || grid < 1 || !begin_out) return MK_E_INVALID;
-  const long long total = nblk * nkt;
+  if ((unsigned long long)nblk * nkt * (grid + 1ull) >= (1ull << 32)) return MK_E_INVALID;
+  const unsigned total = (unsigned)(nblk * nkt);
   for (int c = 0; c <= grid; ++c) begin_out[c] = mk::tile_begin(c, total, grid);
   int bad = 0;
-  for (long long t = 0; t < total; ++t) {
+  for (unsigned t = 0; t < total; ++t) {
     const int o = mk::tile_owner(t, total, grid);
     if (o < 0 || o >= grid || t < begin_out[o] || t >= begin_out[o + 1]) ++bad;
   }
@@ -679,7 +680,7 @@ int mk_compile(mk_handle* h) {
   // 2. shared-memory carve-up: the activations of one pass (up to 8 token rows of the widest
   // linear op, fewer if they would leave less than 6 weight stages) plus the weight ring
   const int tb_max = std::min(mk::kMaxTokGroup, cfg.max_num_batched_tokens);
-  const int x_budget = kMaxSmem - 1024 - kRedBytes - 1024 - 6 * mk::kStageBytes;
+  const int x_budget = kMaxSmem - 1024 - kRedBytes - 1024 - 4 * mk::kStageBytes;
   int x_bytes = cfg.max_num_pages * 4;
   int max_nblk = 1, n_linear = 0, min_tpp = tb_max;
   for (PlanOp& p : h->plan) {
@@ -704,8 +705,9 @@ int mk_compile(mk_handle* h) {
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
   const int fixed = 1024 /*alignment slack*/ + x_bytes + kRedBytes + 1024 /*barriers, flags*/;
   int stages = (kMaxSmem - fixed) / mk::kStageBytes;
-  stages = std::min(stages, 24);
-  if (cfg.max_stages > 0) stages = std::min(stages, cfg.max_stages);
+  // about 128 KB of weights in flight per SM is the measured sweet spot: deeper rings lower
+  // the DRAM efficiency of the 148 concurrent streams
+  stages = std::min(stages, cfg.max_stages > 0 ? cfg.max_stages : 4);
   if (stages < 2) return h->fail(MK_E_UNSUPPORTED, "activations need %d bytes of shared memory; too large for the CUDA-core path", x_bytes);
   mk::KParams& kp = h->kp;
   memset(&kp, 0, sizeof(kp));
@@ -794,7 +796,7 @@ int mk_compile(mk_handle* h) {
       CUtensorMap m;
       cuuint64_t gdim[2] = {(cuuint64_t)po.k, (cuuint64_t)po.n};
       cuuint64_t gstr[1] = {(cuuint64_t)w.strides[0] * 2};
-      cuuint32_t box[2] = {(cuuint32_t)mk::kTileK, (cuuint32_t)mk::kTileRows};
+      cuuint32_t box[2] = {(cuuint32_t)mk::kBoxK, (cuuint32_t)mk::kTileRows};
       cuuint32_t estr[2] = {1, 1};
       if (((uintptr_t)w.ptr) & 15) return h->fail(MK_E_INVALID, "weight %s is not 16-byte aligned", w.name.c_str());
       CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w.ptr, gdim, gstr, box, estr,
@@ -803,6 +805,8 @@ int mk_compile(mk_handle* h) {
       if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %s [%d x %d]", (int)r, w.name.c_str(), po.n, po.k);
       map_of[i] = (int)maps.size();
       maps.push_back(m);
+      if ((unsigned long long)d.nblk * d.nkt * (G + 1ull) >= (1ull << 32))
+        return h->fail(MK_E_UNSUPPORTED, "%s has too many weight tiles for 32-bit tile arithmetic", w.name.c_str());
       h->weight_bytes += (int64_t)d.nblk * d.nkt * mk::kStageBytes;
       if (po.flags & mk::F_ARGMAX) {
         void* q = nullptr;
@@ -868,6 +872,7 @@ int mk_compile(mk_handle* h) {
   kp.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
   kp.trace_op = -1;
   kp.debug_flags = cfg.debug_flags;
+  kp.prefetch_tiles = cfg.prefetch_kb > 0 ? std::max(1, cfg.prefetch_kb * 1024 / mk::kStageBytes) : 0;
   if (h->prof_ptr) {
     const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;
     if (h->prof_entries < need) return h->fail(MK_E_INVALID, "profiler buffer has %lld words, the trace needs %lld", (long long)h->prof_entries, (long long)need);

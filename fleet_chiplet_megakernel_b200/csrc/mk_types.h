@@ -9,11 +9,16 @@
 namespace mk {
 
 // ---- geometry of the weight stream -------------------------------------------------
-// A weight tile is 128 output rows x 64 k-elements of bf16 (16 KB), fetched by one
-// 2-D TMA copy into a 128-byte-swizzled shared-memory stage.
+// A weight tile is 128 output rows x 128 k-elements of bf16 (32 KB): two 2-D TMA boxes
+// of 128 rows x 64 k-elements, adjacent in k, each landing 128-byte-swizzled in its half
+// of a shared-memory stage.  One mbarrier round trip per 32 KB keeps the producer and
+// consumer loops off the critical path.
 constexpr int kTileRows = 128;
-constexpr int kTileK = 64;
-constexpr int kStageBytes = kTileRows * kTileK * 2;
+constexpr int kBoxK = 64;                         // k-elements of one TMA box (128 bytes: the swizzle span)
+constexpr int kSubTiles = 2;                      // boxes per stage, adjacent in k
+constexpr int kTileK = kBoxK * kSubTiles;         // k-elements per stage
+constexpr int kSubBytes = kTileRows * kBoxK * 2;  // 16 KB
+constexpr int kStageBytes = kSubBytes * kSubTiles;
 constexpr int kNumConsumerWarps = 8;
 constexpr int kNumConsumers = kNumConsumerWarps * 32;
 constexpr int kNumThreads = kNumConsumers + 32;  // + one TMA producer warp
@@ -62,7 +67,7 @@ enum Status : int {
   ST_OUT_OF_PAGES = 7,
 };
 
-struct OpDesc {
+struct alignas(16) OpDesc {
   int type;
   int flags;
   // generic shapes
@@ -138,6 +143,7 @@ struct KParams {
   unsigned long long* prof;
   int trace_op;     // op whose inner phases are stamped: prof[(num_ops + 1) * grid * 4 + cta * 16 + k]; -1 none
   int debug_flags;  // bit 0: linear tasks skip the arithmetic
+  int prefetch_tiles;  // weight tiles per CTA requested into L2 ahead of the ring (0 = off)
   // shared-memory carve-up (bytes from the 1024-aligned base)
   int num_stages;
   int x_off, x_bytes;
@@ -145,13 +151,16 @@ struct KParams {
   int bar_off;
 };
 
-// The CTA that owns weight tile `tile` when `total` tiles are dealt to `grid`
-// CTAs as contiguous ranges [c*total/grid, (c+1)*total/grid).
-__host__ __device__ inline long long tile_begin(long long c, long long total, long long grid) {
+// Weight tiles of a linear op are dealt to `grid` CTAs as contiguous ranges
+// [c*total/grid, (c+1)*total/grid); tile_owner is the inverse.  32-bit arithmetic: the
+// host refuses ops with total * (grid + 1) >= 2^32 tiles.
+__host__ __device__ inline unsigned tile_begin(unsigned c, unsigned total, unsigned grid) {
   return c * total / grid;
 }
-__host__ __device__ inline int tile_owner(long long tile, long long total, long long grid) {
-  return (int)(((tile + 1) * grid - 1) / total);
+__host__ __device__ inline int tile_owner(unsigned tile, unsigned total, unsigned grid) {
+  return (int)(((tile + 1u) * grid - 1u) / total);
 }
+
+static_assert(sizeof(OpDesc) % 16 == 0 && sizeof(OpDesc) <= 256, "OpDesc is copied to shared memory in 16-byte pieces");
 
 }  // namespace mk

@@ -181,6 +181,7 @@ class PersistentKernel:
         cfg.trace_op = int(trace_op) + 1
         cfg.debug_flags = int(debug_flags)
         cfg.max_stages = int(os.environ.get("B200MK_MAX_STAGES", "0"))
+        cfg.prefetch_kb = int(os.environ.get("B200MK_PREFETCH_KB", "0"))
         self._h = self._lib.mk_create(C.byref(cfg))
         if not self._h:
             raise RuntimeError("mk_create failed")
