@@ -8,8 +8,8 @@ device tensors and streams at this edge.
 """
 from .persistent_kernel import (PersistentKernel, DTensor, bfloat16, float16, float32, int32, int64, uint64,
                                 valid_persistent_kernel_modes, get_configurations_from_gpu)
-from .qwen3_graph import Qwen3Geometry, build_qwen3_graph, Qwen3Decoder
+from .qwen3_graph import Qwen3Geometry, build_qwen3_graph, Qwen3Decoder, shard_qwen3_weights
 
 __all__ = ["PersistentKernel", "DTensor", "bfloat16", "float16", "float32", "int32", "int64", "uint64",
            "valid_persistent_kernel_modes", "get_configurations_from_gpu", "Qwen3Geometry", "build_qwen3_graph",
-           "Qwen3Decoder"]
+           "Qwen3Decoder", "shard_qwen3_weights"]

@@ -41,6 +41,8 @@ SIGNATURES = {
     "mk_get_event_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64), C.c_int]),
     "mk_finalize": (C.c_int, [C.c_void_p]),
     "mk_last_error": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "mk_comm_prepare": (C.c_int, [C.c_void_p, C.POINTER(C.c_ubyte)]),
+    "mk_comm_connect": (C.c_int, [C.c_void_p, C.POINTER(C.c_ubyte), C.c_int]),
     "mk_plan": (C.c_int, [C.c_void_p]),
     "mk_num_device_ops": (C.c_int, [C.c_void_p]),
     "mk_describe": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),

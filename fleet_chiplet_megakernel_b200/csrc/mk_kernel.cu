@@ -104,6 +104,7 @@ struct Ctx {
   unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
   unsigned long long* pr;   // this op's trace record, or null
   bool dead;                // abort flag seen at the op's barrier (CTA-uniform)
+  unsigned ar_seq;          // allreduce ops executed so far in this launch
   __device__ Ctx(const KParams& p_) : p(p_) {}
   __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
@@ -1140,6 +1141,92 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
 }
 
 // ------------------------------------------------------------------------------------
+// tensor-parallel allreduce over NVLink peer memory
+// ------------------------------------------------------------------------------------
+// aux0 = world size, aux1 = this rank.  in: this rank's partial sums [T, n] bf16, out: the
+// sum over ranks [T, n] bf16 (fp32 addition in rank order, one rounding: the reference's
+// reduction task, tasks/ampere/reduction.cuh:139-166).  One-shot push: the CTA that owns a
+// 4 KB unit of the tensor stores it into its slot in every peer's exchange region with
+// plain 16-byte stores, then publishes a sequence number with a system-scope release; the
+// same CTA waits (bounded) for the peers' numbers on its own unit and adds the slots up.
+// Data always lands in the consumer's own memory; nothing here loads through TMA or
+// multicast.  Slots are double-buffered by sequence parity: a rank can be at most one
+// allreduce ahead of a peer on any unit, because finishing one needs that peer's push.
+__device__ __forceinline__ uint4 ld_sys_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __noinline__ void op_allreduce(Ctx& c, const OpDesc& op, int T) {
+  const KParams& p = c.p;
+  if (op_barrier(c, op)) return;
+  const int world = op.aux0, me = op.aux1;
+  const unsigned seq = p.xchg_seq_base + (++c.ar_seq);
+  const int nvec = op.n >> 3;
+  const int upr = (nvec + kNumConsumers - 1) / kNumConsumers;  // units per row
+  const size_t slot_row = (size_t)p.xchg_cols * 2;             // bytes
+  const size_t slot_rank = slot_row * p.xchg_tokens;
+  const size_t slot_par = slot_rank * world;
+  const size_t flags_off = 2 * slot_par;
+  const size_t par_off = (size_t)(seq & 1u) * slot_par;
+#pragma unroll 1
+  for (int unit = blockIdx.x; unit < T * upr; unit += gridDim.x) {
+    const int row = unit / upr, v = (unit % upr) * kNumConsumers + c.tid;
+    const bool valid = v < nvec;
+    uint4 mine = make_uint4(0, 0, 0, 0);
+    if (valid) mine = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)row * op.ld_in) + v);
+    if (valid) {
+#pragma unroll 1
+      for (int r = 0; r < world; ++r) {
+        if (r == me) continue;
+        uint4* dst = reinterpret_cast<uint4*>(p.xchg[r] + par_off + (size_t)me * slot_rank + (size_t)row * slot_row) + v;
+        *dst = mine;
+      }
+    }
+    __threadfence_system();
+    consumer_sync();
+    if (c.tid < world && c.tid != me) {
+      unsigned* theirs = reinterpret_cast<unsigned*>(p.xchg[c.tid] + flags_off) + (size_t)me * p.xchg_units + unit;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(seq) : "memory");
+      const unsigned* ours = reinterpret_cast<const unsigned*>(p.xchg[me] + flags_off) + (size_t)c.tid * p.xchg_units + unit;
+      unsigned long long t0 = 0;
+      unsigned spins = 0;
+      while (true) {
+        unsigned got;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(ours) : "memory");
+        if ((int)(got - seq) >= 0) break;
+        if (((++spins) & 255u) == 0) {
+          if (aborted(c)) break;
+          const unsigned long long now = globaltimer();
+          if (t0 == 0) {
+            t0 = now;
+          } else if (now - t0 > c.p.timeout_ns) {
+            raise_abort(c, ST_TIMEOUT_RANK, c.tid, (int)got);
+            break;
+          }
+        }
+      }
+    }
+    consumer_sync();
+    if (valid) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 1
+      for (int r = 0; r < world; ++r) {
+        uint4 x = mine;
+        if (r != me) x = ld_sys_v4(reinterpret_cast<const uint4*>(p.xchg[me] + par_off + (size_t)r * slot_rank + (size_t)row * slot_row) + v);
+        float f[8];
+        unpack8(x, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)row * op.ld_out)[v] = pack8(acc);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // continuous-batching bookkeeping between iterations (CTA 0, one thread)
 // ------------------------------------------------------------------------------------
 // Same protocol as the reference's offline mode (persistent_kernel.cuh:380-536):
@@ -1395,6 +1482,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.dbg = nullptr;
   c.pr = nullptr;
   c.dead = false;
+  c.ar_seq = 0;
   volatile int* fl = c.flags();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
@@ -1498,6 +1586,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
           case OP_SILU_MUL: if (!op_barrier(c, op)) op_silu_mul(c, op, T); break;
           case OP_ARGMAX_PARTIAL: if (!op_barrier(c, op)) op_argmax_partial(c, op, T); break;
           case OP_ARGMAX_REDUCE: if (!op_barrier(c, op)) op_argmax_reduce(c, op, T); break;
+          case OP_ALLREDUCE: op_allreduce(c, op, T); break;
           default: op_barrier(c, op); break;
         }
         if (pr && c.tid == 0) pr[2] = globaltimer();

@@ -108,6 +108,12 @@ struct mk_handle {
   bool launched = false;
   void* prof_ptr = nullptr;
   int64_t prof_entries = 0;
+  // tensor-parallel exchange
+  void* xchg_local = nullptr;
+  void* xchg_peer[8] = {};
+  bool xchg_ready = false;
+  int xchg_tokens = 0, xchg_cols = 0, xchg_units = 0;
+  unsigned launches = 0;
 
   int fail(int code, const char* fmt, ...) {
     char buf[1024];
@@ -384,7 +390,19 @@ int plan_graph(mk_handle* h) {
     } else if (starts_with(nm, "argmax_reduce")) {
       return h->fail(MK_E_UNSUPPORTED, "argmax_reduce without a preceding argmax_partial");
     } else if (nm == "allreduce") {
-      return h->fail(MK_E_UNSUPPORTED, "allreduce: tensor-parallel exchange is not built in this library version");
+      if (op.t.size() != 3) return h->fail(MK_E_INVALID, "allreduce takes (input, buffer, output)");
+      if (int e = check_2d_bf16(h, op.t[0], "allreduce")) return e;
+      if (int e = check_2d_bf16(h, op.t[2], "allreduce")) return e;
+      const Tensor &in = h->tensors[op.t[0]], &out = h->tensors[op.t[2]];
+      if (in.dims[1] != out.dims[1] || in.dims[1] % 8) return h->fail(MK_E_INVALID, "allreduce: column counts must match and be a multiple of 8");
+      if (op.params.size() >= 2 && (op.params[0] != cfg.world_size || op.params[1] != cfg.rank))
+        return h->fail(MK_E_INVALID, "allreduce: (num_gpus, my_gpu_id) differ from the constructor's world_size / mpi_rank");
+      if (cfg.world_size > 8) return h->fail(MK_E_UNSUPPORTED, "at most 8 ranks");
+      po.type = mk::OP_ALLREDUCE;
+      po.in = op.t[0]; po.out = op.t[2];  // the reference's staging buffer (operand 1) is replaced by the exchange region
+      po.n = (int)in.dims[1];
+      po.aux0 = cfg.world_size;
+      po.aux1 = cfg.rank;
     } else {
       return h->fail(MK_E_UNSUPPORTED, "unknown layer '%s'", nm.c_str());
     }
@@ -585,6 +603,54 @@ int mk_set_profiler(mk_handle* h, void* ptr, int64_t n_entries) {
   if (ptr && (n_entries <= 0 || (((uintptr_t)ptr) & 7))) return h->fail(MK_E_INVALID, "profiler buffer must be 8-byte aligned and non-empty");
   h->prof_ptr = ptr;
   h->prof_entries = ptr ? n_entries : 0;
+  return 0;
+}
+
+// Size of this rank's exchange region for the allreduce layers of the planned graph (0 if none).
+static size_t xchg_bytes(mk_handle* h) {
+  int cols = 0;
+  for (const PlanOp& po : h->plan)
+    if (po.type == mk::OP_ALLREDUCE) cols = std::max(cols, po.n);
+  if (cols == 0 || h->cfg.world_size < 2) return 0;
+  h->xchg_tokens = h->cfg.max_num_batched_tokens;
+  h->xchg_cols = cols;
+  h->xchg_units = h->xchg_tokens * ((cols / 8 + mk::kNumConsumers - 1) / mk::kNumConsumers);
+  const size_t slots = (size_t)2 * h->cfg.world_size * h->xchg_tokens * cols * 2;
+  return slots + (size_t)h->cfg.world_size * h->xchg_units * 4;
+}
+
+int mk_comm_prepare(mk_handle* h, unsigned char handle_out[64]) {
+  if (!h || !handle_out) return MK_E_INVALID;
+  if (h->compiled) return h->fail(MK_E_STATE, "already compiled");
+  if (int e = mk_plan(h)) return e;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memset(handle_out, 0, 64);
+  const size_t bytes = xchg_bytes(h);
+  if (bytes == 0) return 0;  // nothing to exchange (single rank or no allreduce layer)
+  if (!h->xchg_local)
+    if (int e = h->dmalloc(&h->xchg_local, bytes)) return e;
+  cudaIpcMemHandle_t ipc;
+  cudaError_t ce = cudaIpcGetMemHandle(&ipc, h->xchg_local);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "cudaIpcGetMemHandle");
+  memcpy(handle_out, &ipc, 64);
+  return 1;
+}
+
+int mk_comm_connect(mk_handle* h, const unsigned char* handles, int n) {
+  if (!h || !handles) return MK_E_INVALID;
+  if (n != h->cfg.world_size) return h->fail(MK_E_INVALID, "expected %d handles, got %d", h->cfg.world_size, n);
+  if (!h->xchg_local) return h->fail(MK_E_STATE, "mk_comm_prepare must come first");
+  for (int r = 0; r < n; ++r) {
+    if (r == h->cfg.rank) {
+      h->xchg_peer[r] = h->xchg_local;
+      continue;
+    }
+    cudaIpcMemHandle_t ipc;
+    memcpy(&ipc, handles + (size_t)r * 64, 64);
+    cudaError_t ce = cudaIpcOpenMemHandle(&h->xchg_peer[r], ipc, cudaIpcMemLazyEnablePeerAccess);
+    if (ce != cudaSuccess) return h->cuda_fail(ce, "cudaIpcOpenMemHandle (is the peer GPU reachable over NVLink/PCIe?)");
+  }
+  h->xchg_ready = true;
   return 0;
 }
 
@@ -870,6 +936,13 @@ int mk_compile(mk_handle* h) {
   kp.eos = cfg.eos_token_id;
   kp.max_iters = cfg.max_iterations;
   kp.timeout_ns = (unsigned long long)cfg.timeout_ms * 1000000ull;
+  if (xchg_bytes(h) > 0) {
+    if (!h->xchg_ready) return h->fail(MK_E_STATE, "the graph has allreduce layers: exchange handles with mk_comm_prepare / mk_comm_connect before mk_compile");
+    for (int r = 0; r < cfg.world_size; ++r) kp.xchg[r] = (unsigned char*)h->xchg_peer[r];
+    kp.xchg_tokens = h->xchg_tokens;
+    kp.xchg_cols = h->xchg_cols;
+    kp.xchg_units = h->xchg_units;
+  }
   kp.trace_op = -1;
   kp.debug_flags = cfg.debug_flags;
   kp.prefetch_tiles = cfg.prefetch_kb > 0 ? std::max(1, cfg.prefetch_kb * 1024 / mk::kStageBytes) : 0;
@@ -902,6 +975,8 @@ int mk_launch_async(mk_handle* h, void* stream) {
   // grid barrier, control word, abort flag and status live in one 256-byte block behind sched[0..15]
   cudaError_t ce = cudaMemsetAsync((char*)h->kp.sched + 64, 0, 192, s);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  h->launches += 1;
+  h->kp.xchg_seq_base = h->launches << 20;  // exchange sequence numbers keep growing across launches
   int e = mk_kernel_launch(&h->kp, h->grid, h->smem_bytes, stream);
   if (e) return h->cuda_fail((cudaError_t)e, "cooperative launch");
   h->launched = true;
@@ -919,11 +994,11 @@ int mk_wait(mk_handle* h, void* stream) {
   if (st[0] != 0) {
     static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
                                   "producer never got the next iteration", "peer never arrived", "token id out of range",
-                                  "out of KV pages"};
+                                  "out of KV pages", "a peer rank never delivered its allreduce share"};
     const int* s = st + 8;
     const int code = s[0];
     return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
-                   (code >= 0 && code < 8) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
+                   (code >= 0 && code < 9) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
   }
   return 0;
 }
@@ -949,6 +1024,8 @@ int mk_get_event_timing(mk_handle* h, uint64_t* buf, int max_entries) {
 
 int mk_finalize(mk_handle* h) {
   if (!h) return MK_E_INVALID;
+  for (int r = 0; r < 8; ++r)
+    if (h->xchg_peer[r] && h->xchg_peer[r] != h->xchg_local) cudaIpcCloseMemHandle(h->xchg_peer[r]);
   for (void* p : h->allocs) cudaFree(p);
   delete h;
   return 0;

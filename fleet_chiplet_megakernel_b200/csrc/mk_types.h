@@ -65,6 +65,7 @@ enum Status : int {
   ST_TIMEOUT_PEER = 5,
   ST_BAD_TOKEN = 6,
   ST_OUT_OF_PAGES = 7,
+  ST_TIMEOUT_RANK = 8,
 };
 
 struct alignas(16) OpDesc {
@@ -138,6 +139,12 @@ struct KParams {
   float* attn_part;       // [tokens][kv heads][max chunks][qpk*(128+2)]
   unsigned* attn_count;   // [tokens][kv heads]
   int attn_max_chunks;
+  // tensor-parallel exchange: every rank's exchange region mapped into this GPU's address space
+  // (xchg[rank] is the local one).  Layout of a region: slots [2][world][xchg_tokens][xchg_cols] bf16,
+  // then flags [world][xchg_units] u32 (last push sequence number seen from each source rank).
+  unsigned char* xchg[8];
+  int xchg_tokens, xchg_cols, xchg_units;
+  unsigned xchg_seq_base;  // launches so far << 20: sequence numbers grow across launches
   // optional per-op trace of the last iteration: [(op * grid + cta) * 4 + k] globaltimer ns,
   // k = 0 op reached, 1 barrier passed, 2 op done; op == num_ops is the iteration prologue
   unsigned long long* prof;

@@ -407,8 +407,31 @@ class PersistentKernel:
         if self.profiler_tensor is not None:
             assert self.profiler_tensor.dtype in (torch.uint64, torch.int64)
             self._check(self._lib.mk_set_profiler(self._h, prof, self.profiler_tensor.numel()), "set_profiler")
+        if self.world_size > 1:
+            self._exchange_handles()
         self._check(self._lib.mk_compile(self._h), "compile")
         self._is_compiled = True
+        if self.world_size > 1:
+            import torch.distributed as dist
+            dist.barrier()  # every rank's exchange region exists and is mapped before anyone launches
+
+    def _exchange_handles(self):
+        """Tensor parallel set-up: gather the CUDA IPC handles of all ranks' exchange regions over
+        torch.distributed (the reference bootstraps NVSHMEM over MPI, persistent_kernel.cuh:2002-2015)."""
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("world_size > 1 needs an initialised torch.distributed process group")
+        if dist.get_world_size() != self.world_size or dist.get_rank() != self.mpi_rank:
+            raise ValueError("world_size / mpi_rank differ from the torch.distributed group")
+        mine = (C.c_ubyte * 64)()
+        need = self._check(self._lib.mk_comm_prepare(self._h, mine), "comm_prepare")
+        if need == 0:
+            return
+        gathered = [None] * self.world_size
+        dist.all_gather_object(gathered, bytes(mine))
+        blob = b"".join(gathered)
+        arr = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        self._check(self._lib.mk_comm_connect(self._h, arr, self.world_size), "comm_connect")
 
     def init_requests(self, stream=None):
         s = stream if stream is not None else torch.cuda.current_stream()
@@ -465,6 +488,10 @@ class PersistentKernel:
 
     def finalize(self):
         assert not self.__finalized__
+        if self.world_size > 1 and self._is_compiled:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.barrier()  # nobody unmaps a region a peer may still be writing
         if self._h:
             self._lib.mk_finalize(self._h)
             self._h = None

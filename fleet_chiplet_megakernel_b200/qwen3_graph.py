@@ -41,6 +41,24 @@ def rope_tables(geom: Qwen3Geometry, max_pos: int, device):
     return emb.cos().to(torch.bfloat16).to(device).contiguous(), emb.sin().to(torch.bfloat16).to(device).contiguous()
 
 
+def shard_qwen3_weights(weights: dict, world_size: int, rank: int) -> dict:
+    """Tensor-parallel shard of a full weight dict, as the reference's converter cuts a checkpoint
+    (demo/qwen3/models/convert.py:13-28): q/k/v/gate/up by output rows (column parallel), o/down by
+    input columns (row parallel), everything else replicated."""
+    if world_size == 1:
+        return weights
+    out = {}
+    for name, t in weights.items():
+        leaf = name.split(".")[-1]
+        if leaf in ("q", "k", "v", "gate", "up"):
+            out[name] = t.chunk(world_size, dim=0)[rank].contiguous()
+        elif leaf in ("o", "down"):
+            out[name] = t.chunk(world_size, dim=1)[rank].contiguous()
+        else:
+            out[name] = t
+    return out
+
+
 def build_qwen3_graph(mpk: PersistentKernel, geom: Qwen3Geometry, weights: dict, k_cache, v_cache, cos, sin,
                       input_tokens, output_tokens, logits=None, num_layers=None, lm_head=True):
     """Record the decode graph.  ``weights`` uses the keys embed, l{i}.{q,k,v,o,gate,up,down,ln1,ln2,qn,kn},
@@ -159,7 +177,8 @@ class Qwen3Decoder:
                  total_requests: int | None = None, page_size: int = 64, max_num_pages: int | None = None,
                  device="cuda", numerics=None, fuse=None, keep_logits=False, eos_token_id: int = 0x7FFFFFFF,
                  max_iterations: int = 0, num_layers=None, timeout_ms: int = 0, trace: bool = False,
-                 trace_op: int = -1, debug_flags: int = 0):
+                 trace_op: int = -1, debug_flags: int = 0, world_size: int = 1, rank: int = 0):
+        """``weights`` are this rank's shard (see ``shard_qwen3_weights``) when world_size > 1."""
         self.geom, self.device = geom, torch.device(device)
         R = max_requests
         total = total_requests if total_requests is not None else R
@@ -177,14 +196,14 @@ class Qwen3Decoder:
         self.kv_indptr = torch.zeros(R + 1, dtype=torch.int32, device=dev)
         self.kv_indices = torch.zeros(self.max_num_pages, dtype=torch.int32, device=dev)
         self.kv_last_page_len = torch.zeros(R, dtype=torch.int32, device=dev)
-        self.k_cache = torch.zeros(L, self.max_num_pages, page_size, geom.n_kv, geom.head_dim, dtype=torch.bfloat16,
-                                   device=dev)
+        self.k_cache = torch.zeros(L, self.max_num_pages, page_size, geom.n_kv // world_size, geom.head_dim,
+                                   dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(geom, max(max_seq_length, 8), dev)
         self.logits = torch.zeros(R, weights["lm_head"].shape[0], dtype=torch.bfloat16, device=dev) if keep_logits else None
         self.profiler = torch.zeros(1 << 20, dtype=torch.int64, device=dev) if trace else None
         self.mpk = PersistentKernel(
-            mode="offline", world_size=1, mpi_rank=0, num_workers=0, num_local_schedulers=0,
+            mode="offline", world_size=world_size, mpi_rank=rank, num_workers=0, num_local_schedulers=0,
             num_remote_schedulers=0, max_seq_length=max_seq_length, max_num_batched_requests=R,
             max_num_batched_tokens=R, max_num_pages=self.max_num_pages, page_size=page_size,
             meta_tensors={"step": self.step, "tokens": self.tokens, "input_tokens": self.input_tokens,

@@ -82,7 +82,7 @@ int mk_tensor_fuse(mk_handle* h, const char* name, const int* tensor_ids, int n,
  * op_name is the layer's task family: "embedding", "rmsnorm", "rmsnorm_linear",
  * "linear", "linear_with_residual", "paged_attention", "paged_attention_split_kv",
  * "paged_attention_split_kv_merge", "silu_mul", "argmax", "argmax_partial",
- * "argmax_reduce", "allreduce".  tensor_ids are the layer's operands in the
+ * "argmax_reduce", "allreduce" (params: num_gpus, my_gpu_id).  tensor_ids are the layer's operands in the
  * order the Python method lists them; params are its integer parameters. */
 int mk_op(mk_handle* h, const char* op_name, const int* tensor_ids, int n_tensors, const int64_t* params, int n_params,
           const int* grid_dim, const int* block_dim);
@@ -128,6 +128,17 @@ int mk_get_event_timing(mk_handle* h, uint64_t* host_buf, int max_entries);
 int mk_finalize(mk_handle* h);
 
 int mk_last_error(mk_handle* h, char* buf, int n);
+
+/* Tensor parallelism.  The reference puts its activation buffers on the NVSHMEM symmetric heap
+ * (persistent_kernel.cuh:1921-1938, 2002-2015) and exchanges 128-byte slices with
+ * nvshmemx_putmem_signal_block (src/kernel/task_register.cc:1649-1673).  Here each rank (one
+ * process per GPU) owns one exchange region; the in-kernel allreduce stores straight into the
+ * peers' regions over NVLink.  mk_comm_prepare plans the graph, allocates the region and writes
+ * its 64-byte CUDA IPC handle (returns 1; 0 when the graph needs no exchange); the caller
+ * gathers the handles of all ranks (any transport: torch.distributed, MPI, files) and passes
+ * them, ordered by rank, to mk_comm_connect; then mk_compile.  All ranks must launch together. */
+int mk_comm_prepare(mk_handle* h, unsigned char handle_out[64]);
+int mk_comm_connect(mk_handle* h, const unsigned char* handles /* world_size x 64 */, int n);
 
 /* Host-only half of mk_compile (validation, fusion decisions, device-op list); needs no GPU. */
 int mk_plan(mk_handle* h);

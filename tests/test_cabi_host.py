@@ -123,7 +123,11 @@ def test_error_behaviour_follows_the_reference_api(native_lib):
     b = k.new_tensor(dims=(3, 2, 64), name="buf")
     o = k.new_tensor(dims=(2, 64), name="o")
     k.allreduce_layer(input=a, buffer=b, output=o, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
-    with pytest.raises(NotImplementedError):
+    assert "allreduce" in k.plan()  # planned; a single rank just copies
+    k.finalize()
+    k = _kernel()
+    with pytest.raises(NotImplementedError, match="unknown layer"):
+        k._op("gang_linear", [k.new_tensor(dims=(2, 64), name="z")])
         k.plan()
     k.finalize()
 
