@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200mk.so")
-SOURCES = ["mk_kernel.cu", "mk_runtime.cpp"]
+SOURCES = ["mk_kernel.cu", "mk_runtime.cpp", "mk_noalloc.cu"]
 HEADERS = ["mk_types.h", os.path.join("..", "..", "include", "b200mk.h")]
 
 

@@ -9,7 +9,7 @@ MK_BF16, MK_F32, MK_I32, MK_I64, MK_U64, MK_F16 = range(6)
 MK_MODE_OFFLINE, MK_MODE_ONEPASS = 0, 1
 MK_NUMERICS_MPK, MK_NUMERICS_TORCH = 0, 1
 MK_CAT_CUDA, MK_CAT_SYMMETRIC = 0, 1
-MK_E_INVALID, MK_E_STATE, MK_E_CUDA, MK_E_UNSUPPORTED, MK_E_DEVICE, MK_E_NOMEM = -1, -2, -3, -4, -5, -6
+MK_E_INVALID, MK_E_STATE, MK_E_CUDA, MK_E_UNSUPPORTED, MK_E_DEVICE, MK_E_NOMEM, MK_E_TOO_LARGE = -1, -2, -3, -4, -5, -6, -7
 
 
 class MkConfig(C.Structure):
@@ -51,6 +51,7 @@ SIGNATURES = {
     "mk_debug_partition": (C.c_int, [C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int)]),
     "mk_tensor_ptr": (C.c_void_p, [C.c_void_p, C.c_int]),
     "mk_tensor_read": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64]),
+    "mk_linear_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
 }
 
 _lib = None

@@ -30,7 +30,8 @@ enum {
   MK_E_CUDA = -3,      /* a CUDA runtime/driver call failed */
   MK_E_UNSUPPORTED = -4,
   MK_E_DEVICE = -5,    /* the kernel reported a timeout or bad data; see mk_last_error */
-  MK_E_NOMEM = -6
+  MK_E_NOMEM = -6,
+  MK_E_TOO_LARGE = -7  /* a size beyond a fixed built-in limit */
 };
 
 /* Constructor arguments of PersistentKernel
@@ -151,6 +152,28 @@ int64_t mk_weight_bytes_per_step(mk_handle* h);        /* bytes the TMA producer
 int mk_debug_partition(int64_t nblk, int64_t nkt, int grid, int64_t* begin_out /* grid+1 */, int* owner_check);
 void* mk_tensor_ptr(mk_handle* h, int tensor_id);      /* device address after compile (runtime-owned ones too) */
 int mk_tensor_read(mk_handle* h, int tensor_id, void* host_buf, int64_t bytes); /* copy a tensor's bytes to the host */
+
+/* No counterpart in the reference (its runtime allocates everything it needs).
+ *
+ * A linear layer for hosts that cannot allocate device memory where they need it: a server
+ * that gave the whole GPU to its own arena at start-up, or a loop that must not run into
+ * the device-wide synchronisation of cudaMalloc / cudaFree.  Computes
+ *     out[t][j] = bf16( sum_i x[t][i] * w[j][i]  (+ residual[t][j]) ),   fp32 accumulation,
+ * for row-major bf16 x [tokens, k], w [n, k], residual (may be NULL) and out [tokens, n],
+ * all caller-owned device memory, 16-byte aligned, k a multiple of 8.  The call allocates
+ * and frees nothing: the partial sums of its k-splits live in a fixed array inside the
+ * library (about 4 MB on every GPU that loads it, held until the process exits), which is
+ * why the sizes are capped: tokens <= MK_STATIC_MAX_TOKENS, n <= MK_STATIC_MAX_N,
+ * k <= MK_STATIC_MAX_K; anything larger returns MK_E_TOO_LARGE (and says so on stderr).
+ * The first call on a device looks up that array's device address; make this first call
+ * outside any stream capture.  All calls share the array: calls that overlap on the GPU
+ * race on it, so issue them on one stream or otherwise serialise them.  The launch is
+ * asynchronous on `stream`; the return value covers argument checks and launch errors. */
+#define MK_STATIC_MAX_TOKENS 8
+#define MK_STATIC_MAX_N 16384
+#define MK_STATIC_MAX_K 32768
+int mk_linear_static(const void* x, const void* w, const void* residual, void* out, int tokens, int n, int k,
+                     void* stream);
 
 #ifdef __cplusplus
 }
