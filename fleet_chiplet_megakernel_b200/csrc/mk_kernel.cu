@@ -54,7 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// 2-D tiled TMA load, no multicast: box {64 k-elements, 128 rows} at (x = k, y = row).
+// 2-D tiled TMA load into this CTA only: box {64 k-elements, 128 rows} at (x = k, y = row).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -1149,8 +1149,8 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
 // 4 KB unit of the tensor stores it into its slot in every peer's exchange region with
 // plain 16-byte stores, then publishes a sequence number with a system-scope release; the
 // same CTA waits (bounded) for the peers' numbers on its own unit and adds the slots up.
-// Data always lands in the consumer's own memory; nothing here loads through TMA or
-// multicast.  Slots are double-buffered by sequence parity: a rank can be at most one
+// Data always lands in the consumer's own memory; no bulk or tensor copy ever reads a
+// peer's memory.  Slots are double-buffered by sequence parity: a rank can be at most one
 // allreduce ahead of a peer on any unit, because finishing one needs that peer's push.
 __device__ __forceinline__ uint4 ld_sys_v4(const uint4* p) {
   uint4 v;
