@@ -971,50 +971,44 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       if (fl[2] != 0) {  // the chunk that arrives last merges all of them
         __threadfence();
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
-        // every load of the merge (values, maxima, sums of up to 8 chunks, for two output
-        // elements) goes out before the first use: one L2 round trip per batch
+        // The (max, sum) pairs of all chunks go through shared memory; the values are read in
+        // small batches: more than a few dozen loads in flight per thread slowed the merge down.
+#ifndef MK_MERGE_BATCH
+#define MK_MERGE_BATCH 8
+#endif
         const int nout = pl.qpk * kHeadDim;
+        float* sm_pm = sm_l + 16;                        // [chunks][qpk]
+        float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
 #pragma unroll 1
-        for (int e0 = c.tid; e0 < nout; e0 += 2 * kNumConsumers) {
-          float M[2] = {-INFINITY, -INFINITY}, Ls[2] = {0.f, 0.f}, O[2] = {0.f, 0.f};
+        for (int i = c.tid; i < a.nch * pl.qpk; i += kNumConsumers) {
+          const float* pm = base + (size_t)(i / pl.qpk) * part_stride + nout + (i % pl.qpk);
+          sm_pm[i] = __ldcg(pm);
+          sm_pl[i] = __ldcg(pm + pl.qpk);
+        }
+        consumer_sync();
 #pragma unroll 1
-          for (int c0 = 0; c0 < a.nch; c0 += 8) {
-            float v[2][8], mm[2][8], ll[2][8];
+        for (int e = c.tid; e < nout; e += kNumConsumers) {
+          const int eh = e >> 7;
+          float M = -INFINITY;
+#pragma unroll 1
+          for (int cc = 0; cc < a.nch; ++cc) M = fmaxf(M, sm_pm[cc * pl.qpk + eh]);
+          float Ls = 0.f, O = 0.f;
+#pragma unroll 1
+          for (int c0 = 0; c0 < a.nch; c0 += MK_MERGE_BATCH) {
+            float v[MK_MERGE_BATCH];
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const int e = e0 + q * kNumConsumers;
-              const float* pm = base + nout + (e >> 7);
+            for (int u = 0; u < MK_MERGE_BATCH; ++u)
+              v[u] = (c0 + u < a.nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const bool ok = (c0 + u < a.nch) && (e < nout);
-                const size_t off = (size_t)(c0 + u) * part_stride;
-                v[q][u] = ok ? __ldcg(base + off + e) : 0.f;
-                mm[q][u] = ok ? __ldcg(pm + off) : -INFINITY;
-                ll[q][u] = ok ? __ldcg(pm + off + pl.qpk) : 0.f;
-              }
-            }
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              float Mn = M[q];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, mm[q][u]);
-              const float resc = (M[q] == -INFINITY) ? 0.f : exp2f(M[q] - Mn);
-              Ls[q] *= resc;
-              O[q] *= resc;
-              M[q] = Mn;
-#pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const float f = (mm[q][u] == -INFINITY) ? 0.f : exp2f(mm[q][u] - Mn);
-                Ls[q] += f * ll[q][u];
-                O[q] += f * v[q][u];
+            for (int u = 0; u < MK_MERGE_BATCH; ++u) {
+              if (c0 + u < a.nch) {
+                const float f = exp2f(sm_pm[(c0 + u) * pl.qpk + eh] - M);
+                Ls += f * sm_pl[(c0 + u) * pl.qpk + eh];
+                O += f * v[u];
               }
             }
           }
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int e = e0 + q * kNumConsumers;
-            if (e < nout) out[e] = __float2bfloat16_rn(__fdividef(O[q], Ls[q]));
-          }
+          out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
         }
         if (c.tid == 0) *cnt = 0u;
       }
