@@ -105,14 +105,18 @@ struct Ctx {
   unsigned long long* pr;   // this op's trace record, or null
   bool dead;                // abort flag seen at the op's barrier (CTA-uniform)
   unsigned ar_seq;          // allreduce ops executed so far in this launch
+  unsigned lin_seq;         // linear ops whose barrier has been passed in this launch
   __device__ Ctx(const KParams& p_) : p(p_) {}
   __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
-  __device__ volatile int* flags() const { return (volatile int*)(smem + p.bar_off + 16 * p.num_stages); }
+  __device__ uint32_t xfull_bar(int s) const { return smem_addr + p.bar_off + 8 * (2 * p.num_stages + s); }
+  __device__ volatile int* flags() const { return (volatile int*)(smem + p.bar_off + 24 * p.num_stages); }
+  __device__ float* sums() const { return (float*)(smem + p.sums_off); }
   __device__ float* red() const { return (float*)(smem + p.red_off); }
 };
 // flags(): [0] go word written by consumers, read by the producer
 //          [1] stages issued by the producer   [2] broadcast slot   [3] dead flag of the op
+//          [4] linear ops whose barrier the consumers have passed   [5] activation stages issued
 
 #ifdef MK_NO_STAMP
 #define MK_STAMP(c, k) do {} while (0)
@@ -390,12 +394,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int kRedStride = kMaxTokGroup;  // floats per row in the shared sums block
 
-// ntok tokens starting at tok0; sums at red[row * kRedStride + token]
+// ntok tokens starting at tok0; sums at sums()[row * sums_stride + token]
 __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int ntok, float res0) {
   const KParams& p = c.p;
-  const float* red = c.red();
+  const float* red = c.sums();
+  const int kRedStride = p.sums_stride;
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
   if (op.flags & F_SILU_MUL) {
     // rows 0..63 of the tile are gate columns, rows 64..127 the matching up columns
@@ -466,7 +470,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 }
 
 // Called by all consumers at the end of a run of tiles of one row block, after the
-// per-row sums of the run were left in red[row * kRedStride + token].
+// per-row sums of the run were left in sums()[row * sums_stride + token].
 //
 // When several CTAs hold k-ranges of the block, the CTA with the block's FIRST k-range
 // finishes it: that range is the tail of its own tile range, so it is the last piece to
@@ -476,7 +480,9 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int blk, int kt_first, int kt_last,
                                                  bool first_of_cta, int tok0, int ntok, int group, float res0) {
   const KParams& p = c.p;
-  float* red = c.red();
+  float* red = c.sums();
+  const int kRedStride = p.sums_stride;
+  const int nvec4 = kTileRows * kRedStride / 4;  // float4 pieces of the sums block
   consumer_sync();
   const bool whole = (kt_first == 0) && (kt_last == op.nkt - 1);
   if (!whole) {
@@ -491,7 +497,8 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
     if ((int)blockIdx.x != c_first) {
       float4* mine = reinterpret_cast<float4*>(
           p.partial + (((size_t)group * GS + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems);
-      mine[c.tid] = red4[c.tid];  // 128 x 8 floats = one float4 per consumer thread
+#pragma unroll 1
+      for (int i = c.tid; i < nvec4; i += kNumConsumers) mine[i] = red4[i];
       __threadfence();
       consumer_sync();
       if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
@@ -518,30 +525,33 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
     consumer_sync();
     __threadfence();
     // all pieces' loads go out together: one L2 round trip instead of one per piece
-    float4 acc = red4[c.tid];
 #pragma unroll 1
-    for (int c0 = c_first + 1; c0 <= c_last; c0 += 4) {
-      float4 v[4];
+    for (int i = c.tid; i < nvec4; i += kNumConsumers) {
+      float4 acc = red4[i];
+#pragma unroll 1
+      for (int c0 = c_first + 1; c0 <= c_last; c0 += 4) {
+        float4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int cc = c0 + u;
-        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cc <= c_last) {
-          const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
-          const float4* src = reinterpret_cast<const float4*>(
-              p.partial + (((size_t)group * GS + cc) * 2 + (first ? 0 : 1)) * slot_elems);
-          v[u] = __ldcg(src + c.tid);
+        for (int u = 0; u < 4; ++u) {
+          const int cc = c0 + u;
+          v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (cc <= c_last) {
+            const bool first = (tile_begin(cc, total, G) / op.nkt) == blk;
+            const float4* src = reinterpret_cast<const float4*>(
+                p.partial + (((size_t)group * GS + cc) * 2 + (first ? 0 : 1)) * slot_elems);
+            v[u] = __ldcg(src + i);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc.x += v[u].x;
+          acc.y += v[u].y;
+          acc.z += v[u].z;
+          acc.w += v[u].w;
         }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        acc.x += v[u].x;
-        acc.y += v[u].y;
-        acc.z += v[u].z;
-        acc.w += v[u].w;
-      }
+      red4[i] = acc;
     }
-    red4[c.tid] = acc;
     consumer_sync();
   }
   linear_epilogue(c, op, blk, tok0, ntok, res0);
@@ -606,7 +616,7 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
     if (tile == t0) MK_STAMP(c, 2);
-    const uint32_t st = c.smem_addr + (uint32_t)s * kStageBytes + a_base;
+    const uint32_t st = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + a_base;
     if (arith) {
 #pragma unroll
       for (int sub = 0; sub < kSubTiles; ++sub) {
@@ -633,11 +643,11 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
     if (tile == t1 - 1) MK_STAMP(c, 3);
     if (end_blk || tile == t1 - 1) {
       // thread (lane) holds rows 16*warp + lane/4 (+8) and tokens 2*(lane%4) (+1)
-      float* red = c.red() + (16 * warp + (lane >> 2)) * kRedStride + 2 * (lane & 3);
+      float* red = c.sums() + (16 * warp + (lane >> 2)) * p.sums_stride + 2 * (lane & 3);
       red[0] = acc[0];
       red[1] = acc[1];
-      red[8 * kRedStride] = acc[2];
-      red[8 * kRedStride + 1] = acc[3];
+      red[8 * p.sums_stride] = acc[2];
+      red[8 * p.sums_stride + 1] = acc[3];
       acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
       linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group, res0);
       first_of_cta = false;
@@ -655,6 +665,115 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
   c.cons_idx += consumed;
 }
 
+// Batches above 8 tokens: the input rows of a pass (16, 32 or 64 token rows x 128 k) come
+// with every weight stage as two more TMA boxes (issued by the activation producer once the
+// op's barrier has opened), 128-byte swizzled like the weights, and each warp multiplies its
+// 16 weight rows against NT n-tiles of 8 tokens.  The weights are streamed once per pass of
+// up to 64 tokens instead of once per 8.
+template <int NT>
+__device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0, int T, int group) {
+  const KParams& p = c.p;
+  const int nkt = op.nkt;
+  const int ntok = min(8 * NT, T - tok0);
+  const unsigned total = (unsigned)op.nblk * (unsigned)nkt;
+  const int G = (int)min(gridDim.x, total);
+  if ((int)blockIdx.x >= G) return;
+  const unsigned t0 = tile_begin(blockIdx.x, total, G);
+  const unsigned t1 = tile_begin(blockIdx.x + 1, total, G);
+  const int S = p.num_stages;
+  const int lane = c.lane, warp = c.warp;
+  const int a_row = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
+  const uint32_t a_base = (uint32_t)(a_row * 128);
+  const uint32_t a_xor = (uint32_t)(a_row & 7);
+  const uint32_t a_hi = (uint32_t)(lane >> 4);
+  // B operand: lane l addresses token row 8*nt + (l & 7), 16-byte chunk 4*half + (l >> 3)
+  const uint32_t b_row = (uint32_t)((lane & 7) * 128);
+  const uint32_t b_xor = (uint32_t)(lane & 7);
+  const uint32_t b_hi = (uint32_t)(lane >> 3);
+  const uint32_t x_sub = (uint32_t)(8 * NT * 128);  // bytes of one activation box
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0), bar_x0 = c.xfull_bar(0);
+  const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
+  const __nv_bfloat16* res_ptr = reinterpret_cast<const __nv_bfloat16*>(op.res) +
+                                 (size_t)(tok0 + (c.tid >> 7)) * op.ld_res + (c.tid & 127);
+  const bool res_tok = with_res && (c.tid >> 7) < ntok;
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+  int blk = (int)(t0 / (unsigned)nkt);
+  int kt = (int)(t0 - (unsigned)blk * (unsigned)nkt);
+  int kt_first = kt;
+  bool first_of_cta = true;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+  float res0 = 0.f;
+  bool new_blk = true;
+  for (unsigned tile = t0; tile < t1; ++tile) {
+    if (new_blk) {
+      new_blk = false;
+      res0 = 0.f;
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+    }
+    mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+    mbar_wait(c, bar_x0 + 8 * s, parity, ST_TIMEOUT_FULL);
+    const uint32_t st = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+    const uint32_t xt = st + kStageBytes;
+#pragma unroll
+    for (int sub = 0; sub < kSubTiles; ++sub) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          ldmatrix_x4(st + a_base + (uint32_t)sub * kSubBytes + ((((uint32_t)(2 * (2 * half + q)) + a_hi) ^ a_xor) << 4),
+                      a[q][0], a[q][1], a[q][2], a[q][3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(xt + (uint32_t)sub * x_sub + (uint32_t)nt * 1024u + b_row + ((((uint32_t)(4 * half) + b_hi) ^ b_xor) << 4),
+                      b0, b1, b2, b3);
+          mma_bf16(acc[nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+          mma_bf16(acc[nt], a[1][0], a[1][1], a[1][2], a[1][3], b2, b3);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty0 + 8 * s);
+    ++consumed;
+    if (++s == S) {
+      s = 0;
+      parity ^= 1u;
+    }
+    const bool end_blk = (kt == nkt - 1);
+    if (end_blk || tile == t1 - 1) {
+      float* red = c.sums() + (16 * warp + (lane >> 2)) * p.sums_stride + 2 * (lane & 3);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        red[8 * nt] = acc[nt][0];
+        red[8 * nt + 1] = acc[nt][1];
+        red[8 * p.sums_stride + 8 * nt] = acc[nt][2];
+        red[8 * p.sums_stride + 8 * nt + 1] = acc[nt][3];
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      }
+      linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group, res0);
+      first_of_cta = false;
+      kt_first = 0;
+    }
+    if (end_blk) {
+      kt = 0;
+      blk += 1;
+      new_blk = true;
+    } else {
+      kt += 1;
+    }
+  }
+  c.cons_idx += consumed;
+}
+
+__device__ __forceinline__ int p_x_rows(const Ctx& c) { return c.p.x_rows; }
+
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   // the norm weights do not depend on other CTAs: fetched ahead of the barrier
   uint4 pre_w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
@@ -667,7 +786,17 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
     }
   }
   if (op_barrier(c, op)) return;
+  c.lin_seq += 1;
+  if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the activation producer may now read this op's input
   const int passes = linear_passes(op, T);
+  if (op.flags & F_XTILE) {
+    for (int g = 0; g < passes; ++g) {
+      if (p_x_rows(c) == 16) linear_pass_wide<2>(c, op, g * op.aux3, T, g);
+      else if (p_x_rows(c) == 32) linear_pass_wide<4>(c, op, g * op.aux3, T, g);
+      else linear_pass_wide<8>(c, op, g * op.aux3, T, g);
+    }
+    return;
+  }
   for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, pre ? pre_w : nullptr);
 }
 
@@ -1433,7 +1562,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
             break;
           }
           const uint32_t full = bar_full0 + 8 * s;
-          const uint32_t dst = c.smem_addr + (uint32_t)s * kStageBytes;
+          const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
           mbar_arrive_expect_tx(full, kStageBytes);
           tma_load_2d(dst, lc.tmap, full, lc.kt * kTileK, lc.blk * kTileRows);
           tma_load_2d(dst + kSubBytes, lc.tmap, full, lc.kt * kTileK + kBoxK, lc.blk * kTileRows);
@@ -1453,6 +1582,93 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     if (dead || p.mode == MODE_ONEPASS) break;
   }
   fl[1] = (int)issued;
+}
+
+// The activation producer (warp 9, one lane).  For wide-batch linear ops it walks the same
+// tile sequence as the weight producer and adds the input boxes to every stage, but only
+// after the consumers have passed the op's barrier: unlike weights, activations are the
+// previous op's output.
+__device__ __noinline__ void xproducer_loop(Ctx& c) {
+  const KParams& p = c.p;
+  if (p.x_rows == 0) return;
+  const int S = p.num_stages;
+  volatile int* fl = c.flags();
+  int s = 0;
+  uint32_t empty_parity = 1;
+  unsigned lin_seq = 0, issued = 0;
+  const uint32_t bar_x0 = c.xfull_bar(0), bar_empty0 = c.empty_bar(0);
+  const uint32_t x_sub = (uint32_t)p.x_rows * 128u;
+  for (int iter = 1;; ++iter) {
+    int go;
+    {
+      unsigned long long t0 = 0;
+      int spins = 0;
+      while (true) {
+        go = fl[0];
+        if (go < 0 || (go >> 8) >= iter) break;
+        __nanosleep(40);
+        if (((++spins) & 255) == 0) {
+          if (aborted(c)) { go = -1; break; }
+          const unsigned long long now = globaltimer();
+          if (t0 == 0) t0 = now;
+          if (now - t0 > c.p.timeout_ns) { go = -1; break; }
+        }
+      }
+    }
+    if (go < 0) break;
+    const int T = go & 255;
+    bool dead = false;
+    for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
+      const OpDesc& op = p.ops[oi];
+      if (op.type != OP_LINEAR) continue;
+      lin_seq += 1;
+      TileCursor lc;
+      if (!cursor_open(p, lc, oi)) continue;
+      if (!(op.flags & F_XTILE)) {
+        // stages of this op carry no activation boxes, but they advance the ring
+        const unsigned n = (lc.t1 - lc.tile) * (unsigned)linear_passes(op, T);
+        for (unsigned i = 0; i < n; ++i)
+          if (++s == S) { s = 0; empty_parity ^= 1u; }
+        continue;
+      }
+      // wait until the consumers have passed this op's barrier
+      {
+        unsigned long long t0 = 0;
+        int spins = 0;
+        while ((unsigned)fl[4] < lin_seq) {
+          if (fl[0] < 0) { dead = true; break; }
+          if (((++spins) & 1023) == 0) {
+            if (aborted(c)) { dead = true; break; }
+            const unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > c.p.timeout_ns) { dead = true; break; }
+          }
+        }
+      }
+      if (dead) break;
+      const int passes = linear_passes(op, T);
+      const unsigned t0 = lc.tile;
+      for (int g = 0; g < passes && !dead; ++g) {
+        if (g > 0) cursor_open(p, lc, oi);
+        for (unsigned tile = t0; tile < lc.t1; ++tile) {
+          if (!mbar_wait(c, bar_empty0 + 8 * s, empty_parity, ST_TIMEOUT_EMPTY)) {
+            dead = true;
+            break;
+          }
+          const uint32_t full = bar_x0 + 8 * s;
+          const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + kStageBytes;
+          mbar_arrive_expect_tx(full, 2 * x_sub);
+          tma_load_2d(dst, op.tmap_x, full, lc.kt * kTileK, g * op.aux3);
+          tma_load_2d(dst + x_sub, op.tmap_x, full, lc.kt * kTileK + kBoxK, g * op.aux3);
+          issued += 1;
+          fl[5] = (int)issued;
+          if (++s == S) { s = 0; empty_parity ^= 1u; }
+          if (++lc.kt == lc.nkt) { lc.kt = 0; lc.blk += 1; }
+        }
+      }
+    }
+    if (dead || p.mode == MODE_ONEPASS) break;
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -1477,16 +1693,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.pr = nullptr;
   c.dead = false;
   c.ar_seq = 0;
+  c.lin_seq = 0;
   volatile int* fl = c.flags();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; ++s) {
       mbar_init(c.full_bar(s), 1);
       mbar_init(c.empty_bar(s), kNumConsumerWarps);
+      mbar_init(c.xfull_bar(s), 1);
     }
     fl[0] = 0;
     fl[1] = 0;
     fl[2] = 0;
     fl[3] = 0;
+    fl[4] = 0;
+    fl[5] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -1494,6 +1714,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
 
   if (c.warp == kNumConsumerWarps) {
     if (c.lane == 0) producer_loop(c);
+    __syncwarp();
+  } else if (c.warp == kNumConsumerWarps + 1) {
+    if (c.lane == 0) xproducer_loop(c);
     __syncwarp();
   } else {
     for (int iter = 1;; ++iter) {
@@ -1601,6 +1824,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     const unsigned issued = (unsigned)fl[1];
     for (unsigned i = c.cons_idx; i < issued; ++i)
       mbar_wait(c, c.full_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
+    const unsigned xissued = (unsigned)fl[5];  // wide batches: every stage also carries activation boxes
+    for (unsigned i = c.cons_idx; i < xissued; ++i)
+      mbar_wait(c, c.xfull_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
     if (p.mode == MODE_OFFLINE && blockIdx.x == 0 && c.iter - 1 < p.max_step_times) {
       // closing timestamp
     }

@@ -197,6 +197,9 @@ int plan_graph(mk_handle* h) {
       if (valid_tensor(h, op.t[i])) h->tensors[op.t[i]].readers++;
   }
   const bool fuse = cfg.fuse != 0;
+  // RMSNorm is fused into the activation staging of the next linear; batches above 8 tokens
+  // stream their activations by TMA instead, so the norm stays a task of its own there
+  const bool fuse_norm = fuse && cfg.max_num_batched_tokens <= mk::kMaxTokGroup;
   const int nops_all = (int)h->ops.size();
   // True when the value layer `i` writes into tensor `tid` is read by layer i+1 only:
   // walk the layers in execution order (wrapping into the next iteration) until the
@@ -244,7 +247,7 @@ int plan_graph(mk_handle* h) {
       if (w.numel() != in.dims[1] || out.dims[1] != in.dims[1] || in.dims[1] % 8)
         return h->fail(MK_E_INVALID, "rmsnorm: shape mismatch on %s", in.name.c_str());
       // fuse into the next linear when the normalised rows are only an intermediate
-      if (fuse && i + 1 < nops && is_linear(h->ops[i + 1].name) && h->ops[i + 1].name != "rmsnorm_linear" &&
+      if (fuse_norm && i + 1 < nops && is_linear(h->ops[i + 1].name) && h->ops[i + 1].name != "rmsnorm_linear" &&
           h->ops[i + 1].t[0] == op.t[2] && only_next_reads(i, op.t[2])) {
         pending_norm_in = op.t[0];
         pending_norm_w = op.t[1];
@@ -743,14 +746,29 @@ int mk_compile(mk_handle* h) {
       if (int e = materialise_shuffle(h, t)) return e;
   if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return h->cuda_fail(ce, "shuffle copies");
 
-  // 2. shared-memory carve-up: the activations of one pass (up to 8 token rows of the widest
-  // linear op, fewer if they would leave less than 6 weight stages) plus the weight ring
+  // 2. shared-memory carve-up.  Up to 8 batched tokens: the activation rows of one pass are
+  // staged in shared memory by the consumers (fused RMSNorm) beside the weight ring.  Above 8:
+  // every stage carries two activation boxes of x_rows token rows, the sums block of a tile
+  // (128 x x_rows floats) takes the place of the staged rows.
+  const bool wide = cfg.max_num_batched_tokens > mk::kMaxTokGroup;
+  int x_rows = 0;
+  if (wide) x_rows = cfg.max_num_batched_tokens <= 16 ? 16 : (cfg.max_num_batched_tokens <= 32 ? 32 : 64);
+  const int stage_bytes = mk::kStageBytes + 2 * x_rows * 128;
   const int tb_max = std::min(mk::kMaxTokGroup, cfg.max_num_batched_tokens);
   const int x_budget = kMaxSmem - 1024 - kRedBytes - 1024 - 4 * mk::kStageBytes;
   int x_bytes = cfg.max_num_pages * 4;
-  int max_nblk = 1, n_linear = 0, min_tpp = tb_max;
+  if (wide) x_bytes = std::max(x_bytes, mk::kTileRows * x_rows * 4);
+  int max_nblk = 1, n_linear = 0, min_tpp = wide ? x_rows : tb_max;
   for (PlanOp& p : h->plan) {
     if (p.type == mk::OP_LINEAR) {
+      max_nblk = std::max(max_nblk, (p.n + mk::kTileRows - 1) / mk::kTileRows);
+      ++n_linear;
+      if (wide) {
+        if (p.flags & mk::F_NORM_IN) return h->fail(MK_E_UNSUPPORTED, "rmsnorm_linear is only built for up to 8 batched tokens");
+        p.flags |= mk::F_XTILE;
+        p.aux3 = x_rows;
+        continue;
+      }
       const int kp = (p.k + mk::kTileK - 1) / mk::kTileK * mk::kTileK;
       const int row_bytes = (kp + 8) * 2;
       int tpp = std::min(tb_max, (x_budget - 16) / row_bytes);
@@ -758,30 +776,30 @@ int mk_compile(mk_handle* h) {
       p.aux3 = tpp;
       min_tpp = std::min(min_tpp, tpp);
       x_bytes = std::max(x_bytes, tpp * row_bytes + 16);
-      max_nblk = std::max(max_nblk, (p.n + mk::kTileRows - 1) / mk::kTileRows);
-      ++n_linear;
     } else if (p.type == mk::OP_RMSNORM) {
       x_bytes = std::max(x_bytes, ((p.n + 63) / 64 * 64 + 8) * 2 + 16);
     } else if (p.type == mk::OP_ATTN) {
-      const int qpk = p.aux1 / p.aux0;
-      (void)qpk;
       x_bytes = std::max(x_bytes, 16 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 256);
     }
   }
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
   const int fixed = 1024 /*alignment slack*/ + x_bytes + kRedBytes + 1024 /*barriers, flags*/;
-  int stages = (kMaxSmem - fixed) / mk::kStageBytes;
+  int stages = (kMaxSmem - fixed) / stage_bytes;
   // about 128 KB of weights in flight per SM is the measured sweet spot: deeper rings lower
   // the DRAM efficiency of the 148 concurrent streams
-  stages = std::min(stages, cfg.max_stages > 0 ? cfg.max_stages : 4);
-  if (stages < 2) return h->fail(MK_E_UNSUPPORTED, "activations need %d bytes of shared memory; too large for the CUDA-core path", x_bytes);
+  stages = std::min(stages, cfg.max_stages > 0 ? std::min(cfg.max_stages, 16) : 4);
+  if (stages < 2) return h->fail(MK_E_UNSUPPORTED, "activations need %d bytes of shared memory: no room for the weight ring", x_bytes);
   mk::KParams& kp = h->kp;
   memset(&kp, 0, sizeof(kp));
   kp.num_stages = stages;
-  kp.x_off = stages * mk::kStageBytes;
+  kp.stage_bytes = stage_bytes;
+  kp.x_rows = x_rows;
+  kp.x_off = stages * stage_bytes;
   kp.x_bytes = x_bytes;
   kp.red_off = kp.x_off + x_bytes;
   kp.bar_off = kp.red_off + kRedBytes;
+  kp.sums_off = wide ? kp.x_off : kp.red_off;
+  kp.sums_stride = wide ? x_rows : mk::kMaxTokGroup;
   h->smem_bytes = kp.bar_off + 1024 + 1024;
   const int per_sm = mk_kernel_max_ctas_per_sm(h->smem_bytes);
   if (per_sm < 1) return h->fail(MK_E_CUDA, "the megakernel does not fit on an SM with %d bytes of shared memory", h->smem_bytes);
@@ -793,7 +811,7 @@ int mk_compile(mk_handle* h) {
   const int G = h->grid;
   const int groups = (cfg.max_num_batched_tokens + min_tpp - 1) / min_tpp;
   void* p = nullptr;
-  if (int e = h->dmalloc(&p, (size_t)groups * G * 2 * mk::kTileRows * mk::kMaxTokGroup * 4)) return e;
+  if (int e = h->dmalloc(&p, (size_t)groups * G * 2 * mk::kTileRows * kp.sums_stride * 4)) return e;
   kp.partial = (float*)p;
   if (int e = h->dmalloc(&p, (size_t)groups * max_nblk * 4)) return e;
   kp.piece_count = (unsigned*)p;
@@ -826,7 +844,7 @@ int mk_compile(mk_handle* h) {
   // 4. the program
   std::vector<mk::OpDesc> descs(h->plan.size());
   std::vector<CUtensorMap> maps;
-  std::vector<int> map_of(h->plan.size(), -1);
+  std::vector<int> map_of(h->plan.size(), -1), xmap_of(h->plan.size(), -1);
   EncodeTiledFn encode = get_encode_fn();
   if (n_linear && !encode) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   auto tp = [&](int id) -> void* { return id >= 0 ? h->tensors[id].ptr : nullptr; };
@@ -871,6 +889,19 @@ int mk_compile(mk_handle* h) {
       if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %s [%d x %d]", (int)r, w.name.c_str(), po.n, po.k);
       map_of[i] = (int)maps.size();
       maps.push_back(m);
+      if (po.flags & mk::F_XTILE) {
+        const Tensor& x = h->tensors[po.in];
+        CUtensorMap mx;
+        cuuint64_t xdim[2] = {(cuuint64_t)po.k, (cuuint64_t)x.dims[0]};
+        cuuint64_t xstr[1] = {(cuuint64_t)x.strides[0] * 2};
+        cuuint32_t xbox[2] = {(cuuint32_t)mk::kBoxK, (cuuint32_t)kp.x_rows};
+        if ((((uintptr_t)x.ptr) & 15) || (x.strides[0] % 8)) return h->fail(MK_E_INVALID, "input %s of a wide-batch linear must be 16-byte aligned with a pitch multiple of 8", x.name.c_str());
+        r = encode(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x.ptr, xdim, xstr, xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for the input %s", (int)r, x.name.c_str());
+        xmap_of[i] = (int)maps.size();
+        maps.push_back(mx);
+      }
       if ((unsigned long long)d.nblk * d.nkt * (G + 1ull) >= (1ull << 32))
         return h->fail(MK_E_UNSUPPORTED, "%s has too many weight tiles for 32-bit tile arithmetic", w.name.c_str());
       h->weight_bytes += (int64_t)d.nblk * d.nkt * mk::kStageBytes;
@@ -906,6 +937,8 @@ int mk_compile(mk_handle* h) {
       return h->cuda_fail(ce, "tensor map upload");
     for (size_t i = 0; i < descs.size(); ++i)
       if (map_of[i] >= 0) descs[i].tmap_w = (const char*)p + (size_t)map_of[i] * sizeof(CUtensorMap);
+    for (size_t i = 0; i < descs.size(); ++i)
+      if (xmap_of[i] >= 0) descs[i].tmap_x = (const char*)p + (size_t)xmap_of[i] * sizeof(CUtensorMap);
   }
   if (int e = h->dmalloc(&p, descs.size() * sizeof(mk::OpDesc), false)) return e;
   if ((ce = cudaMemcpy(p, descs.data(), descs.size() * sizeof(mk::OpDesc), cudaMemcpyHostToDevice)) != cudaSuccess)

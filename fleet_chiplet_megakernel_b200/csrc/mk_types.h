@@ -21,7 +21,7 @@ constexpr int kSubBytes = kTileRows * kBoxK * 2;  // 16 KB
 constexpr int kStageBytes = kSubBytes * kSubTiles;
 constexpr int kNumConsumerWarps = 8;
 constexpr int kNumConsumers = kNumConsumerWarps * 32;
-constexpr int kNumThreads = kNumConsumers + 32;  // + one TMA producer warp
+constexpr int kNumThreads = kNumConsumers + 64;  // + the weight producer warp and the activation producer warp
 constexpr int kMaxTokGroup = 8;                  // tokens per pass of a linear op (one mma n-tile)
 constexpr int kHeadDim = 128;
 
@@ -47,6 +47,7 @@ enum OpFlags : int {
   F_ROPE = 1 << 7,          // attention
   F_WRITE_NORM = 1 << 8,    // linear with F_NORM_IN: CTA 0 also stores the normalised rows
   F_RES_RANK0 = 1 << 9,     // residual only contributed when rank == 0 (row-parallel TP)
+  F_XTILE = 1 << 10,        // linear: input rows arrive per stage by TMA (batches above 8 tokens)
 };
 
 enum Numerics : int {
@@ -85,7 +86,7 @@ struct alignas(16) OpDesc {
   void* out2;
   const void* tmap_w;  // device address of the CUtensorMap of w
   // attention
-  const void* k_cache_c;  // unused alias kept for alignment
+  const void* tmap_x;     // linear, wide batches: device address of the CUtensorMap of the input rows
   void* k_cache;
   void* v_cache;
   const void* q_norm_w;
@@ -153,6 +154,10 @@ struct KParams {
   int prefetch_tiles;  // weight tiles per CTA requested into L2 ahead of the ring (0 = off)
   // shared-memory carve-up (bytes from the 1024-aligned base)
   int num_stages;
+  int stage_bytes;  // weights (kStageBytes) + the activation boxes of a wide-batch stage
+  int x_rows;       // token rows of an activation box (0: activations are staged by the consumers)
+  int sums_off;     // per-(row, token) sums of a run of tiles: [128][sums_stride] floats
+  int sums_stride;
   int x_off, x_bytes;
   int red_off;
   int bar_off;

@@ -108,6 +108,44 @@ def test_gate_up_silu_mul(fuse):
     k.finalize()
 
 
+@pytest.mark.parametrize("T,N,K", [(9, 512, 512), (16, 4096, 4096), (24, 384, 1024), (33, 1024, 12288), (64, 6144, 4096),
+                                   (64, 200, 264), (12, 136, 72)])
+def test_linear_wide_batches(T, N, K):
+    """Above 8 tokens the activations ride along with the weight stages (16/32/64-row boxes)."""
+    x, w, r = _rand((T, K), 31), _rand((N, K), 32, 0.05), _rand((T, N), 33)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, N, dtype=BF, device="cuda")
+    k.linear_with_residual_layer(input=k.attach_input(x.cuda(), "x"), weight=k.attach_input(w.cuda(), "w"),
+                                 residual=k.attach_input(r.cuda(), "r"), output=k.attach_input(od, "o"),
+                                 grid_dim=(max(1, N // 64), 1, 1), block_dim=(256, 1, 1))
+    k.compile()
+    k()
+    bf16_close(od, O.mpk_linear(x, w, residual=r), 1e-2, f"wide linear {T}x{N}x{K}")
+    k.finalize()
+
+
+def test_wide_rmsnorm_gate_up_silu_mul():
+    T, K, I = 20, 512, 1024
+    x, wn = _rand((T, K), 34), (1 + 0.3 * _rand((K,), 35).float()).to(BF)
+    wg, wu = _rand((I, K), 36, 0.05), _rand((I, K), 37, 0.05)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, I, dtype=BF, device="cuda")
+    groups = I // 128
+    mid0 = k.new_tensor(dims=(T, K), name="rmsnorm_out")
+    k.rmsnorm_layer(input=k.attach_input(x.cuda(), "x"), weight=k.attach_input(wn.cuda(), "wn"), output=mid0,
+                    grid_dim=(T, 1, 1), block_dim=(128, 1, 1))
+    wgu = k.shuffle_tensors([k.attach_input(wg.cuda(), "wg"), k.attach_input(wu.cuda(), "wu")], 0, groups, "wgu")
+    mid = k.new_tensor(dims=(T, 2 * I), name="mlp_mid")
+    k.linear_layer(input=mid0, weight=wgu, output=mid, grid_dim=(2 * I // 64, 1, 1), block_dim=(128, 1, 1))
+    k.silu_mul_layer(input=mid, output=k.attach_input(od, "o"), grid_dim=(groups, 1, 1), block_dim=(128, 1, 1))
+    assert [ln.split()[1] for ln in k.plan().strip().splitlines()] == ["rmsnorm", "linear"]
+    k.compile()
+    k()
+    xn = O.mpk_rmsnorm(x, wn)
+    bf16_close(od, O.mpk_silu_mul(O.mpk_linear(xn, wg), O.mpk_linear(xn, wu)), 1e-2, "wide norm + gate/up + silu")
+    k.finalize()
+
+
 def test_embedding_is_exact():
     T, V, H = 6, 1000, 512
     tab = _rand((V, H), 14)
