@@ -99,6 +99,7 @@ struct Ctx {
   uint32_t smem_addr;
   unsigned epoch;     // grid barriers passed
   unsigned cons_idx;  // weight stages consumed
+  unsigned xphase;    // per stage: parity of the next activation-box phase (only some ops use the boxes)
   int tid, lane, warp;
   int iter, cur_op;
   unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
@@ -112,7 +113,7 @@ struct Ctx {
   __device__ uint32_t xfull_bar(int s) const { return smem_addr + p.bar_off + 8 * (2 * p.num_stages + s); }
   __device__ volatile int* flags() const { return (volatile int*)(smem + p.bar_off + 24 * p.num_stages); }
   __device__ float* sums() const { return (float*)(smem + p.sums_off); }
-  __device__ float* red() const { return (float*)(smem + p.red_off); }
+  __device__ float* red() const { return (float*)(smem + p.red_off); }  // small scratch: reductions, lengths
 };
 // flags(): [0] go word written by consumers, read by the producer
 //          [1] stages issued by the producer   [2] broadcast slot   [3] dead flag of the op
@@ -231,7 +232,7 @@ __device__ __forceinline__ bool op_barrier(Ctx& c, const OpDesc& op) {
 
 // Sum over the 256 consumer threads; every thread gets the result.
 __device__ __forceinline__ float block_sum(Ctx& c, float v) {
-  float* r = c.red() + 1024;  // scratch behind the 128x4 accumulator block
+  float* r = c.red();  // scratch behind the 128x4 accumulator block
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   if (c.lane == 0) r[c.warp] = v;
@@ -252,103 +253,141 @@ __device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
 // (pitch = padded K + 8 elements, so that the 8 token rows of an ldmatrix hit 8
 // different banks), zero padded, followed by one 16-byte chunk of zeros that
 // stands in for the rows of absent tokens.
-// `pre_w`: this thread's two norm-weight vectors (index tid and tid + 256), loaded by the
-// caller ahead of the op's barrier; only used when the row has at most 512 vectors.
-__device__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0, int rows,
-                        int T, const uint4* pre_w) {
-  const KParams& p = c.p;
-  uint4* xs = reinterpret_cast<uint4*>(c.smem + p.x_off);
-  const int pitch = (kp >> 3) + 1;  // uint4 per row
-  const int nvec = kp >> 3;
+// Stage `rows` (at most 8) token rows (tokens tok0.. of T; absent ones zero) of a K-wide
+// bf16 input in shared memory, row pitch kp + 8, RMS-normalised when norm_w is given.  All
+// rows are staged concurrently: the 8 consumer warps split into one group per row (8 warps
+// on a single row, 1 warp per row for 5 to 8 rows), a group's warps take interleaved
+// 512-byte pieces of the row and meet once to add up their sums of squares.  The loops are
+// kept rolled on purpose: this runs once per op, straight from a cold instruction cache.
+//
+// `pre_w`: when not null, this lane's first 4 norm-weight vectors (vector index
+// part * 32 + lane + 32 * wpr * i), loaded by the caller ahead of the op's barrier; rows of
+// at most 4 vectors per lane then stay in registers between the two passes.
+__device__ __forceinline__ int stage_warps_per_row(int rows) { return rows <= 1 ? 8 : (rows == 2 ? 4 : (rows <= 4 ? 2 : 1)); }
+
+// sum of squares of 8 bf16 values; `torch_num`: each square rounded to bf16 first
+__device__ __forceinline__ float sumsq8(const uint4& val, bool torch_num, float ss) {
+  float f[8];
+  unpack8(val, f);
+  if (torch_num) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += rbf(f[i] * f[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  return ss;
+}
+// 8 values scaled by r and the norm weight: w * bf16(x * r), or x * (r * w) in fp32
+__device__ __forceinline__ uint4 scale8(const uint4& val, const uint4& wvec, float r, bool torch_num) {
+  float f[8], w[8];
+  unpack8(val, f);
+  unpack8(wvec, w);
+  if (torch_num) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = w[i] * rbf(f[i] * r);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * (r * w[i]);
+  }
+  return pack8(f);
+}
+
+// The scaling factor of a row from the sums of squares its warps left in red[].
+__device__ __forceinline__ float row_rms_scale(const float* red, int first, int wpr, int K, bool torch_num) {
+  float ss = 0.f;
+  for (int q = 0; q < wpr; ++q) ss += red[first + q];
+  // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
+  // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
+  return torch_num ? torch_rsqrt_bf16(rbf(ss / (float)K), true) : rsqrtf(ss / (float)K + 1e-6f);
+}
+
+// A normalised row of at most NV vectors per lane, kept in registers between the sum of
+// squares and the scaling; the norm weights were loaded ahead of the op's barrier.
+template <int NV>
+__device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* dst, const uint4* pre_w, int K, int nvec,
+                                               int v0, int vstep, bool active, bool valid, int red_first, int wpr) {
   const int kvec = K >> 3;
-  if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);
-  const bool small = norm_w != nullptr && pre_w != nullptr && nvec <= 2 * kNumConsumers;
-#pragma unroll 1
-  for (int tb = 0; tb < rows; ++tb) {
-    const int tok = tok0 + tb;
-    const bool valid = tok < T;
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)tok * ld_in);
-    if (small) {
-      // the row stays in registers between the sum of squares and the scaling
-      uint4 raw[2];
-      float f[2][8];
-      float ss = 0.f;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
+  float* red = c.red();
+  uint4 raw[NV];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int v = c.tid + i * kNumConsumers;
-        raw[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
-      }
+  for (int i = 0; i < NV; ++i) {
+    const int v = v0 + vstep * i;
+    raw[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+  }
+  float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        unpack8(raw[i], f[i]);
-        if (p.numerics == NUM_TORCH) {
+  for (int i = 0; i < NV; ++i) ss = sumsq8(raw[i], torch_num, ss);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ss += rbf(f[i][j] * f[i][j]);
-        } else {
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (c.lane == 0) red[c.warp] = ss;
+  consumer_sync();
+  if (active) {
+    const float r = row_rms_scale(red, red_first, wpr, K, torch_num);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ss += f[i][j] * f[i][j];
-        }
-      }
-      const float tot = block_sum(c, ss);
-      float r;
-      if (p.numerics == NUM_TORCH) r = torch_rsqrt_bf16(rbf(tot / (float)K), true);
-      else r = rsqrtf(tot / (float)K + 1e-6f);
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int v = c.tid + i * kNumConsumers;
-        float w[8];
-        unpack8(pre_w[i], w);
-        if (p.numerics == NUM_TORCH) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[i][j] = w[j] * rbf(f[i][j] * r);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) f[i][j] = f[i][j] * (r * w[j]);
-        }
-        if (v < nvec) xs[tb * pitch + v] = (v < kvec) ? pack8(f[i]) : make_uint4(0, 0, 0, 0);
-      }
-      if (c.tid == 0) xs[tb * pitch + nvec] = make_uint4(0, 0, 0, 0);  // the row's padding vector
-      continue;
+    for (int i = 0; i < NV; ++i) {
+      const int v = v0 + vstep * i;
+      if (v < nvec) dst[v] = scale8(raw[i], pre_w[i], r, torch_num);
     }
-    float ss = 0.f;
+  }
+  consumer_sync();
+}
+
+__device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0,
+                                     int rows, int T, const uint4* pre_w) {
+  uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
+  const int pitch = (kp >> 3) + 1;  // uint4 per row
+  const int nvec = kp >> 3, kvec = K >> 3;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
+  const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
+  const int wpr = stage_warps_per_row(rows);
+  const int tb = c.warp / wpr, part = c.warp % wpr;
+  const bool active = tb < rows;
+  const bool valid = active && tok0 + tb < T;
+  const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)(tok0 + tb) * ld_in);
+  uint4* dst = xs + tb * pitch;
+  float* red = c.red();
+  const int v0 = part * 32 + c.lane, vstep = 32 * wpr;
+  if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);  // the chunk absent tokens point at
+  if (active && part == 0 && c.lane == 0) dst[nvec] = make_uint4(0, 0, 0, 0);  // the row's padding vector
+  if (wv != nullptr && pre_w != nullptr && nvec <= 4 * vstep) {
+    if (nvec <= 2 * vstep) stage_row_regs<2>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr);
+    else stage_row_regs<4>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr);
+    return;
+  }
+  float ss = 0.f;
+  if (active) {
+    // four loads in flight at a time (a store to shared memory between two loads would
+    // order them: the compiler cannot tell the two address spaces apart here)
 #pragma unroll 1
-    for (int v = c.tid; v < nvec + 1; v += kNumConsumers) {
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (valid && v < kvec) val = __ldcg(src + v);
-      xs[tb * pitch + v] = val;
-      if (norm_w != nullptr) {
-        float f[8];
-        unpack8(val, f);
-        if (p.numerics == NUM_TORCH) {
+    for (int vb = v0; vb < nvec; vb += 4 * vstep) {
+      uint4 val[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ss += rbf(f[i] * f[i]);
-        } else {
+      for (int i = 0; i < 4; ++i) {
+        const int v = vb + i * vstep;
+        val[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      for (int i = 0; i < 4; ++i) {
+        const int v = vb + i * vstep;
+        if (v < nvec) {
+          dst[v] = val[i];
+          if (wv != nullptr) ss = sumsq8(val[i], torch_num, ss);
         }
       }
     }
-    if (norm_w != nullptr) {
-      const float tot = block_sum(c, ss);
-      const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
-      // reference PyTorch RMSNorm: bf16 mean of bf16 squares, bf16 rsqrt, two bf16 products
-      // (a one-element bf16 rsqrt on the CPU is 1 / bf16(sqrt(x)) rounded again)
-      const bool torch_num = p.numerics == NUM_TORCH;
-      const float r = torch_num ? torch_rsqrt_bf16(rbf(tot / (float)K), true) : rsqrtf(tot / (float)K + 1e-6f);
-#pragma unroll 1
-      for (int v = c.tid; v < kvec; v += kNumConsumers) {
-        float f[8], w[8];
-        unpack8(xs[tb * pitch + v], f);
-        unpack8(__ldg(wv + v), w);
-        if (torch_num) {
+  }
+  if (wv != nullptr) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = w[i] * rbf(f[i] * r);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = f[i] * (r * w[i]);
-        }
-        xs[tb * pitch + v] = pack8(f);
-      }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (c.lane == 0) red[c.warp] = ss;
+    consumer_sync();
+    if (active) {
+      const float r = row_rms_scale(red, tb * wpr, wpr, K, torch_num);
+#pragma unroll 2
+      for (int v = v0; v < kvec; v += vstep)  // a lane re-reads only what it wrote itself
+        dst[v] = scale8(dst[v], __ldg(wv + v), r, torch_num);
     }
   }
   consumer_sync();
@@ -433,7 +472,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     }
   }
   if (op.flags & F_ARGMAX) {
-    float* scratch = c.red() + 1024 + 32;
+    float* scratch = c.red() + 32;
     for (int tb = 0; tb < ntok; ++tb) {
       ArgBest b;
       b.v = -INFINITY;
@@ -717,7 +756,8 @@ __device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0
       if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
-    mbar_wait(c, bar_x0 + 8 * s, parity, ST_TIMEOUT_FULL);
+    mbar_wait(c, bar_x0 + 8 * s, (c.xphase >> s) & 1u, ST_TIMEOUT_FULL);
+    c.xphase ^= 1u << s;
     const uint32_t st = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
     const uint32_t xt = st + kStageBytes;
 #pragma unroll
@@ -776,12 +816,13 @@ __device__ __forceinline__ int p_x_rows(const Ctx& c) { return c.p.x_rows; }
 
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   // the norm weights do not depend on other CTAs: fetched ahead of the barrier
-  uint4 pre_w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-  const bool pre = (op.flags & F_NORM_IN) && (op.k >> 3) <= 2 * kNumConsumers;
+  uint4 pre_w[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  const int wpr0 = stage_warps_per_row(min(op.aux3, T));
+  const bool pre = (op.flags & F_NORM_IN) && op.nkt * (kTileK >> 3) <= 128 * wpr0;
   if (pre) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = c.tid + i * kNumConsumers;
+    for (int i = 0; i < 4; ++i) {
+      const int v = (c.warp % wpr0) * 32 + c.lane + 32 * wpr0 * i;
       if (v < (op.k >> 3)) pre_w[i] = __ldg(reinterpret_cast<const uint4*>(op.norm_w) + v);
     }
   }
@@ -791,13 +832,14 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   const int passes = linear_passes(op, T);
   if (op.flags & F_XTILE) {
     for (int g = 0; g < passes; ++g) {
-      if (p_x_rows(c) == 16) linear_pass_wide<2>(c, op, g * op.aux3, T, g);
+      if (p_x_rows(c) == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
+      else if (p_x_rows(c) == 16) linear_pass_wide<2>(c, op, g * op.aux3, T, g);
       else if (p_x_rows(c) == 32) linear_pass_wide<4>(c, op, g * op.aux3, T, g);
       else linear_pass_wide<8>(c, op, g * op.aux3, T, g);
     }
     return;
   }
-  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, pre ? pre_w : nullptr);
+  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
 }
 
 // ------------------------------------------------------------------------------------
@@ -925,7 +967,11 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
   const int G = gridDim.x;
   MK_STAMP(c, 0);
-  int* lens = reinterpret_cast<int*>(c.red() + 1024 + 64);  // sequence lengths incl. the new token
+  if (p.debug_flags & 2) {  // measurement aid: the op keeps its barrier and does nothing else
+    op_barrier(c, op);
+    return;
+  }
+  int* lens = reinterpret_cast<int*>(c.red() + 64);  // sequence lengths incl. the new token
 #pragma unroll 1
   for (int r = c.tid; r < T; r += kNumConsumers) {
     const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
@@ -1200,7 +1246,7 @@ __device__ void op_silu_mul(Ctx& c, const OpDesc& op, int T) {
 }
 
 __device__ ArgBest block_argmax(Ctx& c, ArgBest b) {
-  float* scratch = c.red() + 1024 + 32;
+  float* scratch = c.red() + 32;
   b = warp_argmax(b);
   if (c.lane == 0) {
     scratch[c.warp * 2] = b.v;
@@ -1595,7 +1641,8 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
   volatile int* fl = c.flags();
   int s = 0;
   uint32_t empty_parity = 1;
-  unsigned lin_seq = 0, issued = 0;
+  unsigned lin_seq = 0;
+  unsigned issued_mask = 0, xphase = 0;  // per stage: boxes issued; parity of the stage's next box phase
   const uint32_t bar_x0 = c.xfull_bar(0), bar_empty0 = c.empty_bar(0);
   const uint32_t x_sub = (uint32_t)p.x_rows * 128u;
   for (int iter = 1;; ++iter) {
@@ -1637,6 +1684,7 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
         int spins = 0;
         while ((unsigned)fl[4] < lin_seq) {
           if (fl[0] < 0) { dead = true; break; }
+          __nanosleep(64);  // a hot spin would take issue slots from the consumer warps of this scheduler
           if (((++spins) & 1023) == 0) {
             if (aborted(c)) { dead = true; break; }
             const unsigned long long now = globaltimer();
@@ -1660,8 +1708,8 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
           mbar_arrive_expect_tx(full, 2 * x_sub);
           tma_load_2d(dst, op.tmap_x, full, lc.kt * kTileK, g * op.aux3);
           tma_load_2d(dst + x_sub, op.tmap_x, full, lc.kt * kTileK + kBoxK, g * op.aux3);
-          issued += 1;
-          fl[5] = (int)issued;
+          issued_mask |= 1u << s;
+          xphase ^= 1u << s;
           if (++s == S) { s = 0; empty_parity ^= 1u; }
           if (++lc.kt == lc.nkt) { lc.kt = 0; lc.blk += 1; }
         }
@@ -1669,6 +1717,9 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
     }
     if (dead || p.mode == MODE_ONEPASS) break;
   }
+  // no copy of this thread may still be in flight when the CTA exits
+  for (int i = 0; i < S; ++i)
+    if (issued_mask & (1u << i)) mbar_wait(c, bar_x0 + 8 * i, ((xphase >> i) & 1u) ^ 1u, ST_TIMEOUT_FULL);
 }
 
 // ------------------------------------------------------------------------------------
@@ -1684,6 +1735,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.smem_addr = raw_addr + pad;
   c.epoch = 0;
   c.cons_idx = 0;
+  c.xphase = 0;
   c.tid = threadIdx.x;
   c.lane = threadIdx.x & 31;
   c.warp = threadIdx.x >> 5;
@@ -1824,9 +1876,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     const unsigned issued = (unsigned)fl[1];
     for (unsigned i = c.cons_idx; i < issued; ++i)
       mbar_wait(c, c.full_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
-    const unsigned xissued = (unsigned)fl[5];  // wide batches: every stage also carries activation boxes
-    for (unsigned i = c.cons_idx; i < xissued; ++i)
-      mbar_wait(c, c.xfull_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
     if (p.mode == MODE_OFFLINE && blockIdx.x == 0 && c.iter - 1 < p.max_step_times) {
       // closing timestamp
     }

@@ -179,7 +179,7 @@ class PersistentKernel:
         cfg.timeout_ms = int(timeout_ms)
         cfg.device = -1
         cfg.trace_op = int(trace_op) + 1
-        cfg.debug_flags = int(debug_flags)
+        cfg.debug_flags = int(debug_flags) | int(os.environ.get("B200MK_DEBUG_FLAGS", "0"))
         cfg.max_stages = int(os.environ.get("B200MK_MAX_STAGES", "0"))
         cfg.prefetch_kb = int(os.environ.get("B200MK_PREFETCH_KB", "0"))
         self._h = self._lib.mk_create(C.byref(cfg))

@@ -54,8 +54,10 @@ def test_linear_with_residual(T, N, K, numerics):
 
 @pytest.mark.parametrize("numerics", ["mpk", "torch"])
 @pytest.mark.parametrize("fuse", [True, False])
-def test_rmsnorm_then_linear(fuse, numerics):
-    T, N, K = 3, 768, 1024
+@pytest.mark.parametrize("T", [2, 3])
+def test_rmsnorm_then_linear(fuse, numerics, T):
+    # the planner folds the norm into the linear for one or two batched tokens only
+    N, K = 768, 1024
     x, wn, w = _rand((T, K), 6), (1 + 0.3 * _rand((K,), 7).float()).to(BF), _rand((N, K), 8, 0.05)
     k, meta, _ = onepass_kernel(T, fuse=fuse, numerics=numerics)
     od = torch.zeros(T, N, dtype=BF, device="cuda")
@@ -64,11 +66,31 @@ def test_rmsnorm_then_linear(fuse, numerics):
                     grid_dim=(T, 1, 1), block_dim=(128, 1, 1))
     k.linear_layer(input=mid, weight=k.attach_input(w.cuda(), "w"), output=k.attach_input(od, "o"),
                    grid_dim=(N // 64, 1, 1), block_dim=(128, 1, 1))
-    assert len(k.plan().strip().splitlines()) == (1 if fuse else 2)
+    assert len(k.plan().strip().splitlines()) == (1 if fuse and T <= 2 else 2)
     k.compile()
     k()
     xn = O.mpk_rmsnorm(x, wn) if numerics == "mpk" else O.ref_rmsnorm(x, wn)
     bf16_close(od, O.mpk_linear(xn, w), 1e-2, "rmsnorm+linear")
+    k.finalize()
+
+
+@pytest.mark.parametrize("numerics", ["mpk", "torch"])
+@pytest.mark.parametrize("T,N,K", [(1, 768, 4096), (2, 640, 4096), (5, 768, 4096), (8, 256, 1024), (7, 384, 12288)])
+def test_rmsnorm_linear_layer(T, N, K, numerics):
+    # the reference's fused layer called directly (persistent_kernel.py:566): every CTA stages
+    # and normalises the token rows itself; more rows than fit beside the weight ring take
+    # several passes over the weights
+    x, wn, w = _rand((T, K), 16), (1 + 0.3 * _rand((K,), 17).float()).to(BF), _rand((N, K), 18, 0.05)
+    k, meta, _ = onepass_kernel(T, numerics=numerics)
+    od = torch.zeros(T, N, dtype=BF, device="cuda")
+    k.rmsnorm_linear_layer(input=k.attach_input(x.cuda(), "x"), weight_norm=k.attach_input(wn.cuda(), "wn"),
+                           weight_linear=k.attach_input(w.cuda(), "w"), output=k.attach_input(od, "o"),
+                           grid_dim=(N // 64, 1, 1), block_dim=(128, 1, 1))
+    assert len(k.plan().strip().splitlines()) == 1
+    k.compile()
+    k()
+    xn = O.mpk_rmsnorm(x, wn) if numerics == "mpk" else O.ref_rmsnorm(x, wn)
+    bf16_close(od, O.mpk_linear(xn, w), 1e-2, "rmsnorm_linear")
     k.finalize()
 
 
@@ -100,7 +122,7 @@ def test_gate_up_silu_mul(fuse):
     k.linear_layer(input=k.attach_input(x.cuda(), "x"), weight=wgu, output=mid, grid_dim=(2 * I // 64, 1, 1),
                    block_dim=(128, 1, 1))
     k.silu_mul_layer(input=mid, output=k.attach_input(od, "o"), grid_dim=(groups, 1, 1), block_dim=(128, 1, 1))
-    assert len(k.plan().strip().splitlines()) == (1 if fuse else 2)
+    assert len(k.plan().strip().splitlines()) == (1 if fuse and T <= 2 else 2)
     k.compile()
     k()
     ref = O.mpk_silu_mul(O.mpk_linear(x, wg), O.mpk_linear(x, wu))
