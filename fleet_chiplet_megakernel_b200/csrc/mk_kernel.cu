@@ -812,13 +812,184 @@ __device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0
   c.cons_idx += consumed;
 }
 
+// ------------------------------------------------------------------------------------
+// Row-owner linear (F_ROWS): for one or two tokens the cross-CTA finish of a k-split costs
+// more than the whole weight stream of a small layer, so every CTA takes whole output rows
+// instead: a contiguous range of 8-row units, walked in chunks of up to 32 rows over the
+// full K.  The token rows are resident in shared memory (stage_x, fused norm included).
+// Inside a chunk the 8 warps split k: warp w multiplies the w-th 64-wide k slice of every
+// 512-wide stage, tokens on the M side of the mma and 8 weight rows on the N side, and the
+// eight partial sums of an output meet in shared memory when the chunk ends.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void rows_range(const OpDesc& op, int& row0, int& row1, bool& any) {
+  const unsigned U = (unsigned)(op.n + kUnitRows - 1) / kUnitRows;
+  const unsigned G = min((unsigned)gridDim.x, U);
+  any = blockIdx.x < G;
+  row0 = any ? (int)tile_begin(blockIdx.x, U, G) * kUnitRows : 0;
+  row1 = any ? (int)tile_begin(blockIdx.x + 1, U, G) * kUnitRows : 0;
+}
+// The CTA's rows are walked in chunks of at most 32 rows, sized as evenly as whole 8-row units
+// allow (40 rows are 24 + 16, not 32 + 8: small chunks mean small stages and few bytes in
+// flight).  Chunk ci of nch covers rows [rows_chunk_begin(ci), rows_chunk_begin(ci + 1)).
+__device__ __forceinline__ int rows_num_chunks(int row0, int row1) { return (row1 - row0 + kChunkRows - 1) / kChunkRows; }
+__device__ __forceinline__ int rows_chunk_begin(int row0, int row1, int nch, int ci) {
+  return row0 + kUnitRows * (ci * ((row1 - row0) / kUnitRows) / nch);
+}
+// weight stages of this CTA in one pass of the op
+__device__ __forceinline__ unsigned rows_stage_count(const OpDesc& op) {
+  int row0, row1;
+  bool any;
+  rows_range(op, row0, row1, any);
+  return (unsigned)((row1 - row0 + kChunkRows - 1) / kChunkRows) * (unsigned)op.nkt;
+}
+
+__device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0, int T, const uint4* pre_w) {
+  const KParams& p = c.p;
+  const int nks = op.nkt;
+  const int kp = nks * kRowsStageK;
+  const int ntok = min(op.aux3, T - tok0);
+  MK_STAMP(c, 0);
+  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
+  MK_STAMP(c, 1);
+  int row0, row1;
+  bool any;
+  rows_range(op, row0, row1, any);
+  if (!any) return;
+  const int S = p.num_stages;
+  const int lane = c.lane, warp = c.warp;
+  const bool arith = !(p.debug_flags & 1);
+  // A operand (tokens x k): lane l addresses token (l & 7), 16-byte chunk (l >> 3) of a 32-wide k step
+  const int pitch_b = (kp + 8) * 2;
+  const uint32_t xs0 = c.smem_addr + p.x_off;
+  const bool a_real = (lane & 7) < ntok;
+  const uint32_t a_row = a_real ? xs0 + (uint32_t)((lane & 7) * pitch_b + (lane >> 3) * 16 + warp * 128)
+                                : xs0 + (uint32_t)(ntok * pitch_b);  // the zero chunk
+  // B operand (8 weight rows x k): lane l addresses row (l & 7), chunk 4*h + (l >> 3) of the warp's box
+  const uint32_t b_row = (uint32_t)((lane & 7) * 128);
+  const uint32_t b_xor = (uint32_t)(lane & 7);
+  const uint32_t b_hi = (uint32_t)(lane >> 3);
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
+  const int TP = p.sums_stride;  // token slots of the sums block: [warp][32 rows][TP]
+  float* sums = c.sums();
+  const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
+  const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  // epilogue role of this thread: output (row e & 31, token e >> 5) of the chunk
+  const int e_row = c.tid & 31, e_tok = c.tid >> 5;
+  ArgBest best;  // F_ARGMAX: lane 0 of warp t keeps the running best of token t over the CTA's rows
+  best.v = -INFINITY;
+  best.i = 0x7fffffff;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+  const int nch = rows_num_chunks(row0, row1);
+#pragma unroll 1
+  for (int ci = 0; ci < nch; ++ci) {
+    const int r0 = rows_chunk_begin(row0, row1, nch, ci);
+    const int R = rows_chunk_begin(row0, row1, nch, ci + 1) - r0;
+    const int ntile = R >> 3;
+    // the residual of this thread's output is requested a whole chunk ahead of its use
+    float res0 = 0.f;
+    const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
+    if (with_res && e_live) res0 = __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
+    float acc[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    const uint32_t box_bytes = (uint32_t)R * 128u;
+#pragma unroll 1
+    for (int ks = 0; ks < nks; ++ks) {
+      if (ks == 0 && ci == 0) MK_STAMP(c, 2);
+      mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+      if (arith) {
+        const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes;
+        const uint32_t xa = a_row + (a_real ? (uint32_t)(ks * kRowsStageK * 2) : 0u);
+        uint32_t a[2][4];  // a[h]: k chunks 4h .. 4h+3 of tokens 0..7 (rows 8..15 of the mma are zero)
+        ldmatrix_x4(xa, a[0][0], a[0][1], a[0][2], a[0][3]);
+        ldmatrix_x4(xa + (a_real ? 64u : 0u), a[1][0], a[1][1], a[1][2], a[1][3]);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          if (t < ntile) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t b0, b1, b2, b3;
+              ldmatrix_x4(wb + (uint32_t)t * 1024u + b_row + ((((uint32_t)(4 * h) + b_hi) ^ b_xor) << 4), b0, b1, b2, b3);
+              mma_bf16(acc[t], a[h][0], 0u, a[h][1], 0u, b0, b1);
+              mma_bf16(acc[t], a[h][2], 0u, a[h][3], 0u, b2, b3);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty0 + 8 * s);
+      ++consumed;
+      if (++s == S) {
+        s = 0;
+        parity ^= 1u;
+      }
+    }
+    if (ci == nch - 1) MK_STAMP(c, 3);
+    // the chunk's partial sums of this warp: token lane >> 2, rows 8t + 2 * (lane & 3) + {0, 1}
+    {
+      const int tk = lane >> 2;
+      if (tk < TP) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float* d = sums + ((warp * kChunkRows + 8 * t + 2 * (lane & 3)) * TP + tk);
+          d[0] = acc[t][0];
+          d[TP] = acc[t][1];
+        }
+      }
+    }
+    consumer_sync();
+    if (op.flags & F_SILU_MUL) {
+      // units are [4 gate rows | 4 up rows]: the thread of a gate row also adds up its partner
+      if ((e_row & 7) < 4 && e_live) {
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNumConsumerWarps; ++w) {
+          g += sums[(w * kChunkRows + e_row) * TP + e_tok];
+          u += sums[(w * kChunkRows + e_row + 4) * TP + e_tok];
+        }
+        g = rbf(g);  // the linear output is bf16 before the activation
+        u = rbf(u);
+        const float sv = rbf(__fdividef(g, 1.0f + __expf(-g)));
+        const int col = ((r0 + e_row) >> 3) * 4 + (e_row & 3);
+        if (col < (op.n >> 1)) out[(size_t)(tok0 + e_tok) * op.ld_out + col] = __float2bfloat16_rn(sv * u);
+      }
+    } else {
+      float v = 0.f;
+      if (e_live) {
+#pragma unroll
+        for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + e_tok];
+        if (with_res) v = (p.numerics == NUM_TORCH) ? rbf(v) + res0 : v + res0;
+        out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
+      }
+      if (op.flags & F_ARGMAX) {
+        ArgBest b;
+        b.v = e_live ? rbf(v) : -INFINITY;
+        b.i = e_live ? r0 + e_row : 0x7fffffff;
+        b = warp_argmax(b);
+        best = arg_better(best, b);
+      }
+    }
+    consumer_sync();  // the sums block is free again
+  }
+  if ((op.flags & F_ARGMAX) && lane == 0 && e_tok < ntok) {
+    op.amax_val[(size_t)(tok0 + e_tok) * op.amax_n + blockIdx.x] = best.v;
+    op.amax_idx[(size_t)(tok0 + e_tok) * op.amax_n + blockIdx.x] = best.i;
+  }
+  MK_STAMP(c, 4);
+  c.cons_idx += consumed;
+}
+
 __device__ __forceinline__ int p_x_rows(const Ctx& c) { return c.p.x_rows; }
 
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   // the norm weights do not depend on other CTAs: fetched ahead of the barrier
   uint4 pre_w[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
   const int wpr0 = stage_warps_per_row(min(op.aux3, T));
-  const bool pre = (op.flags & F_NORM_IN) && op.nkt * (kTileK >> 3) <= 128 * wpr0;
+  const int kvec_pad = op.nkt * (((op.flags & F_ROWS) ? kRowsStageK : kTileK) >> 3);  // padded row, in 16-byte vectors
+  const bool pre = (op.flags & F_NORM_IN) && kvec_pad <= 128 * wpr0;
   if (pre) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -830,6 +1001,10 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   c.lin_seq += 1;
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the activation producer may now read this op's input
   const int passes = linear_passes(op, T);
+  if (op.flags & F_ROWS) {
+    for (int g = 0; g < passes; ++g) linear_pass_rows(c, op, g * op.aux3, T, (pre && g == 0) ? pre_w : nullptr);
+    return;
+  }
   if (op.flags & F_XTILE) {
     for (int g = 0; g < passes; ++g) {
       if (p_x_rows(c) == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
@@ -1515,7 +1690,7 @@ struct TileCursor {
 // Open the CTA's range of linear op `oi`; false if the op is not linear or gives this CTA nothing.
 __device__ __forceinline__ bool cursor_open(const KParams& p, TileCursor& tc, int oi) {
   const OpDesc& op = p.ops[oi];
-  if (op.type != OP_LINEAR) return false;
+  if (op.type != OP_LINEAR || (op.flags & F_ROWS)) return false;
   const unsigned total = (unsigned)op.nblk * (unsigned)op.nkt;
   const int G = (int)min(gridDim.x, total);
   if ((int)blockIdx.x >= G) return false;
@@ -1544,6 +1719,77 @@ __device__ __forceinline__ void cursor_advance_wrap(const KParams& p, TileCursor
     if (cursor_open(p, tc, oi)) return;
   }
   tc.valid = false;
+}
+
+// Position in this CTA's sequence of row-owner stages (op, chunk, k stage), used by the L2
+// look-ahead of the producer; wraps from the last linear op to the first.
+struct RowsCursor {
+  int oi, row0, row1, nch, ci, ks, nks;
+  bool valid;
+};
+__device__ __forceinline__ bool rows_cursor_open(const KParams& p, RowsCursor& rc, int oi) {
+  const OpDesc& op = p.ops[oi];
+  if (op.type != OP_LINEAR || !(op.flags & F_ROWS)) return false;
+  int row0, row1;
+  bool any;
+  rows_range(op, row0, row1, any);
+  if (!any || row0 >= row1) return false;
+  rc.oi = oi;
+  rc.row0 = row0;
+  rc.row1 = row1;
+  rc.nch = rows_num_chunks(row0, row1);
+  rc.ci = 0;
+  rc.ks = 0;
+  rc.nks = op.nkt;
+  return true;
+}
+__device__ __forceinline__ void rows_cursor_next(const KParams& p, RowsCursor& rc) {
+  if (++rc.ks < rc.nks) return;
+  rc.ks = 0;
+  if (++rc.ci < rc.nch) return;
+  int oi = rc.oi;
+  for (int n = 0; n < p.num_ops; ++n) {
+    oi = (oi + 1 == p.num_ops) ? 0 : oi + 1;
+    if (rows_cursor_open(p, rc, oi)) return;
+  }
+  rc.valid = false;
+}
+// L2 look-ahead of the row-owner weight stream, run by the 32 lanes of the (otherwise idle)
+// activation-producer warp: the stages the ring will load next are requested into L2 line by
+// line with plain prefetch instructions, so that HBM keeps streaming while the consumers sit
+// in a barrier or stage their inputs, and the ring refills from L2 when they come back.
+__device__ __noinline__ void rows_prefetch_loop(Ctx& c) {
+  const KParams& p = c.p;
+  if (p.prefetch_tiles <= 0) return;
+  const unsigned W = (unsigned)p.prefetch_tiles;
+  volatile int* fl = c.flags();
+  RowsCursor rc;
+  rc.valid = false;
+  for (int oi = 0; oi < p.num_ops && !rc.valid; ++oi) rc.valid = rows_cursor_open(p, rc, oi);
+  unsigned pos = 0;  // the cursor's index in this CTA's stage sequence
+  while (rc.valid) {
+    if (fl[0] < 0) break;  // the consumers have left
+    const unsigned issued = (unsigned)fl[1];
+    if (pos >= issued + W) {
+      __nanosleep(200);
+      continue;
+    }
+    if (pos >= issued) {
+      const OpDesc& op = p.ops[rc.oi];
+      const int r0 = rows_chunk_begin(rc.row0, rc.row1, rc.nch, rc.ci);
+      const int R = rows_chunk_begin(rc.row0, rc.row1, rc.nch, rc.ci + 1) - r0;
+      const unsigned char* w = reinterpret_cast<const unsigned char*>(op.w);
+      for (int idx = c.lane; idx < R * 8; idx += 32) {
+        const int row = r0 + (idx >> 3), kk = rc.ks * kRowsStageK + (idx & 7) * 64;
+        if (row < op.n && kk < op.k) {
+          const unsigned char* a = w + ((size_t)row * op.ld_out2 + kk) * 2;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+      }
+    }
+    rows_cursor_next(p, rc);
+    ++pos;
+  }
 }
 
 __device__ __noinline__ void producer_loop(Ctx& c) {
@@ -1587,6 +1833,42 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     const int T = go & 255;
     bool dead = false;
     for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
+      const OpDesc& rop = p.ops[oi];
+      if (rop.type == OP_LINEAR && (rop.flags & F_ROWS)) {
+        // row-owner op: per chunk of up to 32 owned rows, the full K in 512-wide stages of
+        // eight boxes; the tensor map for a chunk of R rows is the (R / 8)-th of the op's four
+        int row0, row1;
+        bool any;
+        rows_range(rop, row0, row1, any);
+        if (!any) continue;
+        const int passes = linear_passes(rop, T);
+        const int nch = rows_num_chunks(row0, row1);
+        for (int g = 0; g < passes && !dead; ++g)
+          for (int ci = 0; ci < nch && !dead; ++ci) {
+            const int r0 = rows_chunk_begin(row0, row1, nch, ci);
+            const int R = rows_chunk_begin(row0, row1, nch, ci + 1) - r0;
+            const void* tmap = reinterpret_cast<const unsigned char*>(rop.tmap_w) + ((R >> 3) - 1) * 128;
+            const uint32_t box_bytes = (uint32_t)R * 128u;
+            for (int ks = 0; ks < rop.nkt; ++ks) {
+              if (!mbar_wait(c, bar_empty0 + 8 * s, empty_parity, ST_TIMEOUT_EMPTY)) {
+                dead = true;
+                break;
+              }
+              const uint32_t full = bar_full0 + 8 * s;
+              const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+              mbar_arrive_expect_tx(full, 8u * box_bytes);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) tma_load_2d(dst + (uint32_t)j * box_bytes, tmap, full, ks * kRowsStageK + j * kBoxK, r0);
+              issued += 1;
+              fl[1] = (int)issued;
+              if (++s == S) {
+                s = 0;
+                empty_parity ^= 1u;
+              }
+            }
+          }
+        continue;
+      }
       TileCursor lc;
       if (!cursor_open(p, lc, oi)) continue;
       const int passes = linear_passes(p.ops[oi], T);
@@ -1669,6 +1951,12 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
       const OpDesc& op = p.ops[oi];
       if (op.type != OP_LINEAR) continue;
       lin_seq += 1;
+      if (op.flags & F_ROWS) {
+        const unsigned n = rows_stage_count(op) * (unsigned)linear_passes(op, T);
+        for (unsigned i = 0; i < n; ++i)
+          if (++s == S) { s = 0; empty_parity ^= 1u; }
+        continue;
+      }
       TileCursor lc;
       if (!cursor_open(p, lc, oi)) continue;
       if (!(op.flags & F_XTILE)) {
@@ -1768,7 +2056,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     if (c.lane == 0) producer_loop(c);
     __syncwarp();
   } else if (c.warp == kNumConsumerWarps + 1) {
-    if (c.lane == 0) xproducer_loop(c);
+    if (p.x_rows == 0) rows_prefetch_loop(c);
+    else if (c.lane == 0) xproducer_loop(c);
     __syncwarp();
   } else {
     for (int iter = 1;; ++iter) {

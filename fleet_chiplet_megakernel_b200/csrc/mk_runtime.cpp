@@ -33,6 +33,9 @@ namespace {
 constexpr int kMaxSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
 constexpr int kRedBytes = 2048;    // small scratch (reductions, argmax, sequence lengths)
 constexpr int kFastSmem = 166912;  // 164 KB carve-out minus the 1 KB the system reserves per CTA
+constexpr int kRowsSumsBytes = mk::kNumConsumerWarps * mk::kChunkRows * 2 * 4;  // [warp][32 rows][2 tokens] floats
+// token rows a row-owner CTA may keep resident beside three 32 KB weight stages
+constexpr int kRowsXBudget = kFastSmem - 2048 - kRedBytes - kRowsSumsBytes - 3 * mk::kStageBytes;
 constexpr int kAttnMaxChunks = 32;
 constexpr int kMaxStepTimes = 16384;
 
@@ -55,7 +58,7 @@ struct Tensor {
   bool user = false;        // attached by the caller: contents are observable
   std::vector<int> src;     // shuffle/fuse sources
   int groups = 0;
-  bool interleave64 = false;  // two sources laid out as [64 rows of src0 | 64 rows of src1] per tile
+  int interleave = 0;  // > 0: two sources laid out as [g rows of src0 | g rows of src1] repeating (g = 64 or 4)
   int readers = 0;
   int64_t numel() const {
     int64_t n = 1;
@@ -97,6 +100,7 @@ struct mk_handle {
   std::vector<RecOp> ops;
   std::vector<PlanOp> plan;
   bool planned = false, compiled = false, meta_set = false;
+  bool rows_mode = false;  // linear layers run row-owner (F_ROWS)
   std::string err;
   void* meta[10] = {};
   int64_t total_requests = 0;
@@ -184,7 +188,7 @@ int plan_graph(mk_handle* h) {
   const mk_config& cfg = h->cfg;
   for (auto& t : h->tensors) {
     t.readers = 0;
-    t.interleave64 = false;
+    t.interleave = 0;
   }
   // operand positions that are read (everything except each layer's outputs)
   auto n_outputs = [](const RecOp& op) {
@@ -205,6 +209,18 @@ int plan_graph(mk_handle* h) {
   // would push the CTA past the small shared-memory carve-out and a separate rmsnorm task
   // with the linear reading activation boxes is faster.
   const bool fuse_norm = fuse && cfg.max_num_batched_tokens <= 2;
+  // One or two tokens: linear layers run row-owner (every CTA owns whole output rows and keeps
+  // the token rows resident in shared memory), provided the widest input still leaves room
+  // for three weight stages inside the small carve-out.
+  bool rows_mode = cfg.max_num_batched_tokens <= 2;
+  for (const RecOp& op : h->ops) {
+    if (!rows_mode || !is_linear(op.name)) continue;
+    const int wi = op.name == "rmsnorm_linear" ? 2 : 1;
+    if ((int)op.t.size() <= wi || !valid_tensor(h, op.t[wi]) || h->tensors[op.t[wi]].ndim != 2) continue;
+    const int64_t kpad = (h->tensors[op.t[wi]].dims[1] + mk::kRowsStageK - 1) / mk::kRowsStageK * mk::kRowsStageK;
+    if (cfg.max_num_batched_tokens * (kpad + 8) * 2 + 16 > kRowsXBudget) rows_mode = false;
+  }
+  h->rows_mode = rows_mode;
   const int nops_all = (int)h->ops.size();
   // True when the value layer `i` writes into tensor `tid` is read by layer i+1 only:
   // walk the layers in execution order (wrapping into the next iteration) until the
@@ -276,6 +292,7 @@ int plan_graph(mk_handle* h) {
       if (tw.dims[0] != tout.dims[1]) return h->fail(MK_E_INVALID, "%s: N mismatch (%s vs %s)", nm.c_str(), tw.name.c_str(), tout.name.c_str());
       if (tw.dims[1] % 8 || tw.strides[0] % 8) return h->fail(MK_E_INVALID, "%s: K and the weight pitch must be multiples of 8", nm.c_str());
       po.type = mk::OP_LINEAR;
+      if (rows_mode) po.flags |= mk::F_ROWS;
       po.in = in; po.w = w; po.out = out; po.res = res;
       po.n = (int)tw.dims[0];
       po.k = (int)tw.dims[1];
@@ -307,7 +324,7 @@ int plan_graph(mk_handle* h) {
           po.flags |= mk::F_SILU_MUL;
           po.out = sm.t[1];
           po.note += po.note.empty() ? "silu_mul fused" : ", silu_mul fused";
-          h->tensors[w].interleave64 = true;
+          h->tensors[w].interleave = rows_mode ? 4 : 64;
           ++i;
         }
       }
@@ -476,11 +493,15 @@ int materialise_shuffle(mk_handle* h, Tensor& t) {
     dst_row += nr;
     return e == cudaSuccess ? 0 : h->cuda_fail(e, "shuffle copy");
   };
-  if (t.interleave64) {
-    const Tensor &a = h->tensors[t.src[0]], &b = h->tensors[t.src[1]];
-    for (int64_t r = 0; r < a.dims[0]; r += 64) {
-      if (int e = copy_rows(a, r, 64)) return e;
-      if (int e = copy_rows(b, r, 64)) return e;
+  if (t.interleave > 0) {
+    // one strided copy per source: "rows" of g weight rows each, placed 2g rows apart
+    const int64_t g = t.interleave;
+    for (int which = 0; which < 2; ++which) {
+      const Tensor& s = h->tensors[t.src[which]];
+      if (s.strides[0] != s.dims[1] || s.dims[0] % g) return h->fail(MK_E_UNSUPPORTED, "gate/up weights must be dense with a multiple of %d rows", (int)g);
+      cudaError_t e = cudaMemcpy2DAsync((char*)t.ptr + (size_t)which * g * row_bytes, 2 * g * row_bytes, s.ptr, g * row_bytes,
+                                        g * row_bytes, (size_t)(s.dims[0] / g), cudaMemcpyDeviceToDevice, 0);
+      if (e != cudaSuccess) return h->cuda_fail(e, "gate/up interleave copy");
     }
   } else {
     for (int g = 0; g < t.groups; ++g)
@@ -758,9 +779,10 @@ int mk_compile(mk_handle* h) {
   // block shares the x region.
   const bool wide = cfg.max_num_batched_tokens > mk::kMaxTokGroup;
   const int nt = cfg.max_num_batched_tokens;
-  const int x_rows = nt <= 8 ? 8 : (nt <= 16 ? 16 : (nt <= 32 ? 32 : 64));
+  const bool rows_mode = h->rows_mode;  // row-owner linears: resident token rows, no activation boxes
+  const int x_rows = rows_mode ? 0 : (nt <= 8 ? 8 : (nt <= 16 ? 16 : (nt <= 32 ? 32 : 64)));
   const int stage_bytes = mk::kStageBytes + 2 * x_rows * 128;
-  const int sums_bytes = mk::kTileRows * x_rows * 4;
+  const int sums_bytes = rows_mode ? kRowsSumsBytes : mk::kTileRows * x_rows * 4;
   const int sums_sep = wide ? 0 : sums_bytes;
   const int tb_max = std::min(mk::kMaxTokGroup, nt);
   const int fixed0 = 1024 /*alignment slack*/ + sums_sep + kRedBytes + 1024 /*barriers, flags*/;
@@ -768,14 +790,16 @@ int mk_compile(mk_handle* h) {
   // the 164 KB carve-out leaves 92 KB of the SM's unified array to L1, and the whole kernel
   // runs about 8 % faster than with the next carve-out (196 KB, 60 KB of L1).
   const int want_stages = cfg.max_stages > 0 ? std::min(cfg.max_stages, 16) : 4;
-  int x_budget = kFastSmem - fixed0 - want_stages * stage_bytes;
+  // (row-owner mode prefers two resident token rows and three stages to one row and four)
+  int x_budget = rows_mode ? kRowsXBudget : kFastSmem - fixed0 - want_stages * stage_bytes;
   int x_bytes = std::max(cfg.max_num_pages * 4, wide ? sums_bytes : 0);
-  int max_nblk = 1, n_linear = 0, min_tpp = x_rows;
+  int max_nblk = 1, n_linear = 0, min_tpp = rows_mode ? 2 : x_rows;
+  const int kpad_to = rows_mode ? mk::kRowsStageK : mk::kTileK;  // the staged rows are padded to whole stages
   for (int attempt = 0; attempt < 2; ++attempt) {
     bool fits = true;
     for (PlanOp& p : h->plan) {
-      if (p.type != mk::OP_LINEAR || !(p.flags & mk::F_NORM_IN)) continue;
-      const int kp = (p.k + mk::kTileK - 1) / mk::kTileK * mk::kTileK;
+      if (p.type != mk::OP_LINEAR || !(p.flags & (mk::F_NORM_IN | mk::F_ROWS))) continue;
+      const int kp = (p.k + kpad_to - 1) / kpad_to * kpad_to;
       if ((x_budget - 16) / ((kp + 8) * 2) < 1) fits = false;
     }
     if (fits) break;
@@ -786,16 +810,16 @@ int mk_compile(mk_handle* h) {
       max_nblk = std::max(max_nblk, (p.n + mk::kTileRows - 1) / mk::kTileRows);
       ++n_linear;
       if (wide && (p.flags & mk::F_NORM_IN)) return h->fail(MK_E_UNSUPPORTED, "rmsnorm_linear is only built for up to 8 batched tokens");
-      if (!(p.flags & mk::F_NORM_IN)) {
+      if (!(p.flags & (mk::F_NORM_IN | mk::F_ROWS))) {
         // no fused norm: the input is read straight from the previous task's output, as
         // activation boxes that ride with the weight stages
         p.flags |= mk::F_XTILE;
         p.aux3 = x_rows;
         continue;
       }
-      const int kp = (p.k + mk::kTileK - 1) / mk::kTileK * mk::kTileK;
+      const int kp = (p.k + kpad_to - 1) / kpad_to * kpad_to;
       const int row_bytes = (kp + 8) * 2;
-      int tpp = std::min(tb_max, (x_budget - 16) / row_bytes);
+      int tpp = std::min(rows_mode ? std::min(2, nt) : tb_max, (x_budget - 16) / row_bytes);
       if (tpp < 1) return h->fail(MK_E_UNSUPPORTED, "K=%d is too wide for a fused input norm", p.k);
       p.aux3 = tpp;
       min_tpp = std::min(min_tpp, tpp);
@@ -821,7 +845,7 @@ int mk_compile(mk_handle* h) {
   kp.x_off = stages * stage_bytes;
   kp.x_bytes = x_bytes;
   kp.sums_off = wide ? kp.x_off : kp.x_off + x_bytes;
-  kp.sums_stride = x_rows;
+  kp.sums_stride = rows_mode ? 2 : x_rows;
   kp.red_off = kp.x_off + x_bytes + sums_sep;
   kp.bar_off = kp.red_off + kRedBytes;
   h->smem_bytes = kp.bar_off + 1024 + 1024;
@@ -830,6 +854,14 @@ int mk_compile(mk_handle* h) {
   h->grid = h->num_sms;
   if (cfg.num_workers > 0) h->grid = std::min(h->grid, cfg.num_workers);
   h->max_nblk = max_nblk;
+  // row-owner LM head: one (max, index) partial per CTA that owns rows
+  for (size_t i = 0; i < h->plan.size(); ++i) {
+    PlanOp& po = h->plan[i];
+    if (po.type == mk::OP_LINEAR && (po.flags & mk::F_ROWS) && (po.flags & mk::F_ARGMAX)) {
+      po.amax_n = std::min(h->grid, (po.n + mk::kUnitRows - 1) / mk::kUnitRows);
+      if (i + 1 < h->plan.size() && h->plan[i + 1].type == mk::OP_ARGMAX_REDUCE) h->plan[i + 1].amax_n = po.amax_n;
+    }
+  }
 
   // 3. scratch and state
   const int G = h->grid;
@@ -899,6 +931,36 @@ int mk_compile(mk_handle* h) {
       d.ld_in = (int)h->tensors[po.in].strides[0];
     } else if (po.type == mk::OP_LINEAR) {
       const Tensor& w = h->tensors[po.w];
+      if (po.flags & mk::F_ROWS) {
+        // four maps, for chunks of 8, 16, 24 and 32 rows: box = 64 k-elements x that many rows
+        const int units = (po.n + mk::kUnitRows - 1) / mk::kUnitRows;
+        d.nblk = units;
+        d.ld_out2 = (int)w.strides[0];  // the weight pitch, for the L2 look-ahead
+        d.nkt = (po.k + mk::kRowsStageK - 1) / mk::kRowsStageK;
+        if (((uintptr_t)w.ptr) & 15) return h->fail(MK_E_INVALID, "weight %s is not 16-byte aligned", w.name.c_str());
+        map_of[i] = (int)maps.size();
+        for (int rows = mk::kUnitRows; rows <= mk::kChunkRows; rows += mk::kUnitRows) {
+          CUtensorMap m;
+          cuuint64_t gdim[2] = {(cuuint64_t)po.k, (cuuint64_t)po.n};
+          cuuint64_t gstr[1] = {(cuuint64_t)w.strides[0] * 2};
+          cuuint32_t box[2] = {(cuuint32_t)mk::kBoxK, (cuuint32_t)rows};
+          cuuint32_t estr[2] = {1, 1};
+          CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w.ptr, gdim, gstr, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+          if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %s [%d x %d]", (int)r, w.name.c_str(), po.n, po.k);
+          maps.push_back(m);
+        }
+        h->weight_bytes += (int64_t)units * mk::kUnitRows * d.nkt * mk::kRowsStageK * 2;
+        if (po.flags & mk::F_ARGMAX) {
+          void* q = nullptr;
+          if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+          d.amax_val = last_amax_val = (float*)q;
+          if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+          d.amax_idx = last_amax_idx = (int*)q;
+        }
+        continue;
+      }
       d.nblk = (po.n + mk::kTileRows - 1) / mk::kTileRows;
       d.nkt = (po.k + mk::kTileK - 1) / mk::kTileK;
       CUtensorMap m;
@@ -1002,7 +1064,11 @@ int mk_compile(mk_handle* h) {
   }
   kp.trace_op = -1;
   kp.debug_flags = cfg.debug_flags;
-  kp.prefetch_tiles = cfg.prefetch_kb > 0 ? std::max(1, cfg.prefetch_kb * 1024 / mk::kStageBytes) : 0;
+  // L2 look-ahead of the weight stream, in 32 KB stages: on by default (256 KB per CTA, the
+  // measured optimum) for the row-owner path, off elsewhere (it measured slower there);
+  // prefetch_kb > 0 sets it, < 0 turns it off
+  const int pf_kb = cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 256 : 0);
+  kp.prefetch_tiles = pf_kb > 0 ? std::max(1, pf_kb * 1024 / mk::kStageBytes) : 0;
   if (h->prof_ptr) {
     const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;
     if (h->prof_entries < need) return h->fail(MK_E_INVALID, "profiler buffer has %lld words, the trace needs %lld", (long long)h->prof_entries, (long long)need);

@@ -24,6 +24,12 @@ constexpr int kNumConsumers = kNumConsumerWarps * 32;
 constexpr int kNumThreads = kNumConsumers + 64;  // + the weight producer warp and the activation producer warp
 constexpr int kMaxTokGroup = 8;                  // tokens per pass of a linear op (one mma n-tile)
 constexpr int kHeadDim = 128;
+// Row-owner linear (one or two batched tokens): a CTA owns a contiguous range of 8-row units
+// and walks it in chunks of up to 32 rows; a stage holds a chunk's rows for 512 k-elements
+// as eight TMA boxes of 64 k-elements (32 KB for a full chunk).
+constexpr int kUnitRows = 8;
+constexpr int kChunkRows = 32;
+constexpr int kRowsStageK = 512;
 
 enum OpType : int {
   OP_EMBED = 1,
@@ -47,7 +53,8 @@ enum OpFlags : int {
   F_ROPE = 1 << 7,          // attention
   F_WRITE_NORM = 1 << 8,    // linear with F_NORM_IN: CTA 0 also stores the normalised rows
   F_RES_RANK0 = 1 << 9,     // residual only contributed when rank == 0 (row-parallel TP)
-  F_XTILE = 1 << 10,        // linear: input rows arrive per stage by TMA (batches above 8 tokens)
+  F_XTILE = 1 << 10,        // linear: input rows arrive per stage by TMA as activation boxes
+  F_ROWS = 1 << 11,         // linear: every CTA owns whole output rows (no split over k between CTAs)
 };
 
 enum Numerics : int {
@@ -76,7 +83,7 @@ struct alignas(16) OpDesc {
   int n;        // linear: output features; rmsnorm/silu: columns; argmax: vocab
   int k;        // linear: input features
   int ld_in, ld_out, ld_res, ld_out2;  // row pitches in elements
-  int nblk, nkt;                       // linear: row tiles, k tiles
+  int nblk, nkt;                       // linear: row tiles, k tiles (F_ROWS: nkt = 512-wide k stages)
   int aux0, aux1, aux2, aux3;          // per-type small ints (see mk_kernel.cu)
   const void* in;
   const void* w;       // linear weight / embedding table / rmsnorm weight
