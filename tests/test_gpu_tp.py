@@ -65,8 +65,14 @@ def test_tp2_matches_reference_fixture(fixture):
     l0, t0 = ret[0]
     l1, t1 = ret[1]
     assert torch.equal(l0, l1) and t0 == t1, "ranks disagree on logits or tokens"
+    # Against the single-GPU PyTorch fixture the tensor-parallel run carries one more bf16
+    # rounding per row-parallel linear (the partial sums cross NVLink as bf16, as the
+    # reference's allreduce on bf16 task outputs does), on top of a comparison whose noise
+    # floor is already 0.0196: the fixture's own model re-run with fp64 linears.  Hence
+    # 2.5e-2 here instead of the single-GPU tests' 2e-2; the tokens are still held to the
+    # fixture wherever its top-2 margin exceeds 2e-2.
     err = O.max_rel_err(l0, fx["logits"][:n_new])
-    assert err <= 2e-2, err
+    assert err <= 2.5e-2, err
     P = len(fx["prompt"])
     scale = fx["logits"][:n_new].float().abs().amax(-1)
     margin = O.top2_margin(fx["logits"][:n_new])
