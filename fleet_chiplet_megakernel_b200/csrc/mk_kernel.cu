@@ -100,6 +100,8 @@ struct Ctx {
   unsigned epoch;     // grid barriers passed
   unsigned cons_idx;  // weight stages consumed
   unsigned xphase;    // per stage: parity of the next activation-box phase (only some ops use the boxes)
+  bool arrived;       // this CTA has already arrived at the coming grid barrier
+  int attn_iter;      // iteration whose attention metadata is cached in shared memory
   int tid, lane, warp;
   int iter, cur_op;
   unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
@@ -145,6 +147,9 @@ __device__ __forceinline__ bool aborted(const Ctx& c) { return *(volatile int*)c
 // Bounded wait on an mbarrier phase.  Returns false after raising the abort flag.
 // The clock is only consulted every few thousand failed polls: reading %globaltimer
 // is slow enough to throttle the weight stream if it sits on the per-tile path.
+// Time limits are tiered so that the record names the root cause: a wait on another GPU gives
+// up after timeout_ns, waits on other CTAs or on the producer after twice that, the producers'
+// own waits (on the consumers) after four times.
 __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
   unsigned long long t0 = 0;
   unsigned polls = 0;
@@ -155,7 +160,7 @@ __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t
       const unsigned long long now = globaltimer();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > c.p.timeout_ns) {
+      } else if (now - t0 > c.p.timeout_ns * (code == ST_TIMEOUT_EMPTY ? 4ull : 2ull)) {
         raise_abort(c, code, (int)bar, (int)parity);
         return false;
       }
@@ -186,12 +191,20 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t p
 
 // Grid-wide barrier of the consumer warps.  The counter only grows within a
 // launch: barrier number e is passed when it reaches e * gridDim.x.
-__device__ __noinline__ void grid_sync(Ctx& c) {
+// The arrival half on its own: an op that has loads to issue which do not depend on other
+// CTAs arrives first and issues them while the others catch up.
+__device__ __forceinline__ void grid_arrive(Ctx& c) {
   consumer_sync();
+  c.epoch += 1;
+  c.arrived = true;
+  // arrive with a release reduction: nothing comes back, polling can start at once
+  if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
+}
+// The waiting half.  Inlined where values loaded ahead of the barrier must stay in registers
+// (a call would spill them, and a spill waits for the load).
+__device__ __forceinline__ void grid_wait(Ctx& c) {
+  c.arrived = false;
   if (c.tid == 0) {
-    c.epoch += 1;
-    // arrive with a release reduction: nothing comes back, polling starts at once
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
     const unsigned target = c.epoch * gridDim.x;
     unsigned long long t0 = 0;
     unsigned spins = 0;
@@ -201,7 +214,7 @@ __device__ __noinline__ void grid_sync(Ctx& c) {
         const unsigned long long now = globaltimer();
         if (t0 == 0) {
           t0 = now;
-        } else if (now - t0 > c.p.timeout_ns) {
+        } else if (now - t0 > 2 * c.p.timeout_ns) {
           raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
           break;
         }
@@ -209,10 +222,12 @@ __device__ __noinline__ void grid_sync(Ctx& c) {
     }
     __threadfence();
     c.flags()[3] = aborted(c) ? 1 : 0;
-  } else {
-    c.epoch += 1;
   }
   consumer_sync();
+}
+__device__ __noinline__ void grid_sync(Ctx& c) {
+  if (!c.arrived) grid_arrive(c);
+  grid_wait(c);
 }
 
 // Every op calls this once, after whatever it can fetch ahead of its dependencies:
@@ -553,7 +568,7 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
           const unsigned long long now = globaltimer();
           if (t0 == 0) {
             t0 = now;
-          } else if (now - t0 > c.p.timeout_ns) {
+          } else if (now - t0 > 2 * c.p.timeout_ns) {
             raise_abort(c, ST_TIMEOUT_PEER, blk, (int)ld_acquire_u32(cnt));
             break;
           }
@@ -1090,14 +1105,19 @@ struct AttnTask {
   uint4 kr[4], vr[4];
 };
 
+constexpr int kAttnLensMax = 128;  // requests (the host admits at most 128 batched tokens)
+
 struct AttnPlan {
   int HKV, qpk, CS, nch_max, ntasks;
   int gi, ngroups;  // this half-warp's position group and the number of groups
 };
 
 // rows of positions p0 + (it0 + u) * ngroups + gi, u = 0..3
+// `pgc`: this half-warp's four cached page numbers (the metadata of an iteration is the same
+// for all layers, so only the first attention op of an iteration looks them up: `fill`).
 __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a,
-                                                int it0, int l16, uint4* kr, uint4* vr) {
+                                                int it0, int l16, uint4* kr, uint4* vr, int* pgc = nullptr,
+                                                bool fill = false) {
   const int PS = c.p.page_size;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
@@ -1105,7 +1125,13 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
     kr[u] = make_uint4(0, 0, 0, 0);
     vr[u] = make_uint4(0, 0, 0, 0);
     if (j < a.p1 && j != a.L - 1) {
-      const int pg = __ldcg(c.p.kv_indices + a.kv_base + j / PS);
+      int pg;
+      if (pgc != nullptr && !fill) {
+        pg = pgc[u];
+      } else {
+        pg = __ldcg(c.p.kv_indices + a.kv_base + j / PS);
+        if (pgc != nullptr) pgc[u] = pg;  // all 16 lanes store the same number
+      }
       const size_t src = (((size_t)pg * PS + j % PS) * pl.HKV + a.h) * kHeadDim;
       kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src) + l16);
       vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src) + l16);
@@ -1114,7 +1140,7 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
 }
 
 __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int task,
-                                          int l16, AttnTask& a) {
+                                          int l16, AttnTask& a, int* pgc = nullptr, bool fill = false) {
   a.valid = false;
   if (task >= pl.ntasks) return;
   a.ch = task % pl.nch_max;
@@ -1126,14 +1152,19 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
   a.valid = true;
   a.p1 = min(a.L, a.p0 + pl.CS);
   a.nch = (a.L + pl.CS - 1) / pl.CS;
-  a.kv_base = __ldcg(c.p.kv_indptr + a.t);
+  a.kv_base = lens[kAttnLensMax + a.t];
   const int pos = min(a.L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
   a.wq = __ldg(reinterpret_cast<const uint4*>(op.q_norm_w) + l16);
   a.wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
   a.cs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
   a.sn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
-  a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + (a.L - 1) / c.p.page_size) : 0;
-  attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr);
+  if (pgc != nullptr && !fill) {
+    a.new_page = pgc[4];
+  } else {
+    a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + (a.L - 1) / c.p.page_size) : 0;
+    if (pgc != nullptr) pgc[4] = a.new_page;
+  }
+  attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr, pgc, fill);
 }
 
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
@@ -1146,13 +1177,27 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     op_barrier(c, op);
     return;
   }
-  int* lens = reinterpret_cast<int*>(c.red() + 64);  // sequence lengths incl. the new token
+  // arrive at the op's barrier first: everything up to the wait below is independent of other CTAs
+  if (op.flags & F_SYNC_BEFORE) grid_arrive(c);
+  // Per-iteration cache in the scratch region (nothing else touches these bytes): sequence
+  // lengths incl. the new token [128], page-table offsets [128], then per half-warp the page
+  // numbers of its first four rows and of the new token [16][8].  The metadata only changes
+  // between iterations, so the first attention op of an iteration fills it and the other
+  // layers start their K/V row loads without any dependent look-up.
+  int* lens = reinterpret_cast<int*>(c.red() + 64);
+  int* pgc = lens + 2 * kAttnLensMax + (c.tid >> 4) * 8;
+  const int key = (c.iter << 8) ^ (op.aux0 * 16 + op.aux1);  // iteration and head geometry
+  const bool fill = c.attn_iter != key;
+  c.attn_iter = key;
+  if (fill) {
 #pragma unroll 1
-  for (int r = c.tid; r < T; r += kNumConsumers) {
-    const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
-    lens[r] = (last - first - 1) * p.page_size + __ldcg(p.kv_last_page_len + r);
+    for (int r = c.tid; r < T; r += kNumConsumers) {
+      const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
+      lens[r] = (last - first - 1) * p.page_size + __ldcg(p.kv_last_page_len + r);
+      lens[kAttnLensMax + r] = first;
+    }
+    consumer_sync();
   }
-  consumer_sync();
   int Lmax = 1;
 #pragma unroll 1
   for (int r = 0; r < T; ++r) Lmax = max(Lmax, lens[r]);
@@ -1167,52 +1212,82 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   pl.nch_max = (nb_max + bpc - 1) / bpc;
   pl.ntasks = T * pl.HKV * pl.nch_max;
   const int l16 = c.lane & 15;
-  const int qh = c.warp % pl.qpk;                           // this warp's q head within the group
-  pl.ngroups = 2 * (kNumConsumerWarps / pl.qpk);
-  pl.gi = 2 * (c.warp / pl.qpk) + (c.lane >> 4);
-  const int hw = c.tid >> 4;                                // half-warp slot in the combine buffers
+  // A half-warp serves up to four q heads of the group at once (one K/V row load feeds all of
+  // them); with eight q heads per kv head the warps alternate between the two head quads.
+  const int hq = min(pl.qpk, 4);
+  const int nquads = pl.qpk / hq;
+  const int quad = c.warp % nquads;
+  pl.ngroups = 2 * (kNumConsumerWarps / nquads);
+  pl.gi = 2 * (c.warp / nquads) + (c.lane >> 4);
   const int part_stride = pl.qpk * (kHeadDim + 2);
   const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
-  float* sm_o = reinterpret_cast<float*>(c.smem + p.x_off);     // [16 half-warps][128]
-  float* sm_m = sm_o + 16 * kHeadDim;                           // [16]
+  uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off);     // [8 heads][16 lanes]: q after norm and RoPE
+  uint4* sm_k = sm_q + 8 * 16;                                  // [16 lanes]: the new k
+  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [4 slots][4 heads][128]
+  float* sm_m = sm_o + 4 * 4 * kHeadDim;                        // [4 slots][4 heads]
   float* sm_l = sm_m + 16;
   const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
+  const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
 
   bool first = true;
 #pragma unroll 1
   for (int task = blockIdx.x;; task += G) {
     AttnTask a;
-    attn_prepare(c, op, pl, lens, task, l16, a);
+    attn_prepare(c, op, pl, lens, task, l16, a, first ? pgc : nullptr, fill);
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;
       MK_STAMP(c, 1);
-      if (op_barrier(c, op)) return;
+      if (op.flags & F_SYNC_BEFORE) {  // op_barrier, with the wait inlined
+        grid_wait(c);
+        if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+        c.dead = c.flags()[3] != 0;
+        if (c.dead) return;
+      } else if (op_barrier(c, op)) {
+        return;
+      }
     }
     if (task >= pl.ntasks) break;
     if (!a.valid) continue;
     const int L = a.L;
     const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
                                (size_t)a.h * (pl.qpk + 2) * kHeadDim;
-    // one batch of loads: this warp's q head, the new k and v
-    const uint4 rq = __ldcg(reinterpret_cast<const uint4*>(row + qh * kHeadDim) + l16);
-    const uint4 rk = __ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16);
     const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
-    F8 q, kf;
-    unpack8(rq, q.v);
-    unpack8(rk, kf.v);
-    q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
-    kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
-    const uint4 knew = pack8(kf.v);
-    if (a.p1 == L && hw == 0) {  // the last chunk appends the new token's K and V to the cache
-      const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
-      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = knew;
-      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+    // norm + RoPE once per CTA: warp w < qpk prepares q head w, one warp the new k
+    if (c.warp < pl.qpk) {
+      F8 q;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
+      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+      if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
     }
-    MK_STAMP(c, 2);
-    float m = -INFINITY, l = 0.f, o[8];
+    if (c.warp == kw) {
+      F8 kf;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
+      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+      const uint4 kn = pack8(kf.v);
+      if (c.lane < 16) {
+        sm_k[l16] = kn;
+        if (a.p1 == L) {  // the last chunk appends the new token's K and V to the cache
+          const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+        }
+      }
+    }
+    consumer_sync();
+    uint4 qv[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    for (int h = 0; h < 4; ++h) qv[h] = (h < hq) ? sm_q[(quad * 4 + h) * 16 + l16] : make_uint4(0, 0, 0, 0);
+    const uint4 knew = sm_k[l16];
+    MK_STAMP(c, 2);
+    float m[4], l[4], o[4][8];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      m[h] = -INFINITY;
+      l[h] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
+    }
     const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
 #pragma unroll 1
     for (int it = 0; it < niter; it += 4) {
@@ -1220,39 +1295,38 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       uint4 nk[4], nv[4];
       const bool more = it + 4 < niter;
       if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
-      float s[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
-        const bool ok = j < a.p1;
+        const bool ok = j < a.p1;  // may differ between the two halves of a warp
+        if (!__any_sync(0xffffffffu, ok)) continue;  // neither half has a row here: skip it together
         if (ok && j == L - 1) {
           a.kr[u] = knew;
           a.vr[u] = vnew;
         }
-        float kk[8];
+        float kk[8], vf[8];
         unpack8(a.kr[u], kk);
-        float d = 0.f;
+        unpack8(a.vr[u], vf);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) d = fmaf(q.v[i], kk[i], d);
+        for (int h = 0; h < 4; ++h) {
+          if (h < hq) {  // uniform
+            float qf[8];
+            unpack8(qv[h], qf);
+            float d = 0.f;
 #pragma unroll
-        for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-        s[u] = ok ? d * sc : -INFINITY;
-      }
-      const float mn = fmaxf(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])), m);
-      if (mn != -INFINITY) {
-        const float alpha = exp2f(m - mn);
-        l *= alpha;
+            for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] *= alpha;
-        m = mn;
+            for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+            if (ok) {
+              const float sv = d * sc;
+              const float mn = fmaxf(m[h], sv);
+              const float alpha = exp2f(m[h] - mn), pr = exp2f(sv - mn);
+              l[h] = l[h] * alpha + pr;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float pr = exp2f(s[u] - mn);
-          l += pr;
-          float vf[8];
-          unpack8(a.vr[u], vf);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i]);
+              for (int i = 0; i < 8; ++i) o[h][i] = fmaf(pr, vf[i], o[h][i] * alpha);
+              m[h] = mn;
+            }
+          }
         }
       }
       if (more) {
@@ -1264,37 +1338,81 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     MK_STAMP(c, 3);
-    // combine the position groups of each head
-    {
-      float* dst = sm_o + hw * kHeadDim + l16 * 8;
-      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
-      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
-      if (l16 == 0) {
-        sm_m[hw] = m;
-        sm_l[hw] = l;
+    // combine the position groups: the two halves of a warp by shuffle, warps 4-7 into warps
+    // 0-3 through shared memory, then every output element over the remaining four slots
+    const int slot = c.warp & 3;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (h < hq) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m[h], 16), l2 = __shfl_xor_sync(0xffffffffu, l[h], 16);
+        const float M = fmaxf(m[h], m2);
+        const float f1 = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M), f2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - M);
+        l[h] = f1 * l[h] + f2 * l2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[h][i] = f1 * o[h][i] + f2 * __shfl_xor_sync(0xffffffffu, o[h][i], 16);
+        m[h] = M;
+        if (c.warp >= 4 && c.lane < 16) {
+          float* dst = sm_o + (slot * 4 + h) * kHeadDim + l16 * 8;
+          reinterpret_cast<float4*>(dst)[0] = make_float4(o[h][0], o[h][1], o[h][2], o[h][3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(o[h][4], o[h][5], o[h][6], o[h][7]);
+          if (l16 == 0) {
+            sm_m[slot * 4 + h] = M;
+            sm_l[slot * 4 + h] = l[h];
+          }
+        }
+      }
+    }
+    consumer_sync();
+    if (c.warp < 4 && c.lane < 16) {
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (h < hq) {
+          const float m2 = sm_m[slot * 4 + h], l2 = sm_l[slot * 4 + h];
+          const float M = fmaxf(m[h], m2);
+          const float f1 = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M), f2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - M);
+          float* buf = sm_o + (slot * 4 + h) * kHeadDim + l16 * 8;  // read the partner's values, leave the sum
+          const float4 s0 = reinterpret_cast<const float4*>(buf)[0], s1 = reinterpret_cast<const float4*>(buf)[1];
+          reinterpret_cast<float4*>(buf)[0] = make_float4(f1 * o[h][0] + f2 * s0.x, f1 * o[h][1] + f2 * s0.y,
+                                                          f1 * o[h][2] + f2 * s0.z, f1 * o[h][3] + f2 * s0.w);
+          reinterpret_cast<float4*>(buf)[1] = make_float4(f1 * o[h][4] + f2 * s1.x, f1 * o[h][5] + f2 * s1.y,
+                                                          f1 * o[h][6] + f2 * s1.z, f1 * o[h][7] + f2 * s1.w);
+          if (l16 == 0) {
+            sm_m[slot * 4 + h] = M;
+            sm_l[slot * 4 + h] = f1 * l[h] + f2 * l2;
+          }
+        }
       }
     }
     consumer_sync();
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
+    // per head: the overall max and sum, and each slot's weight, computed once by one thread
+    float* sm_f = sm_l + 16;   // [4 slots][4 heads] weights
+    float* sm_M = sm_f + 16;   // [8 heads] max, then [8 heads] sum
+    if (c.tid < pl.qpk) {
+      const int qd = c.tid / hq, h = c.tid % hq;  // slots w with w % nquads == qd hold this head
+      float M = -INFINITY;
+      for (int w = qd; w < 4; w += nquads) M = fmaxf(M, sm_m[w * 4 + h]);
+      float Ls = 0.f;
+      for (int w = qd; w < 4; w += nquads) {
+        const float mw = sm_m[w * 4 + h];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        sm_f[w * 4 + h] = f;
+        Ls += f * sm_l[w * 4 + h];
+      }
+      sm_M[c.tid] = M;
+      sm_M[8 + c.tid] = Ls;
+    }
+    consumer_sync();
 #pragma unroll 1
     for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
       const int eh = e >> 7, d = e & 127;
-      float M = -INFINITY;
+      const int qd = eh / hq, h = eh % hq;
+      const float M = sm_M[eh], Ls = sm_M[8 + eh];
+      float O = 0.f;
 #pragma unroll 1
-      for (int w = eh; w < kNumConsumerWarps; w += pl.qpk) M = fmaxf(M, fmaxf(sm_m[2 * w], sm_m[2 * w + 1]));
-      float Ls = 0.f, O = 0.f;
-#pragma unroll 1
-      for (int w = eh; w < kNumConsumerWarps; w += pl.qpk) {
-#pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          const float mw = sm_m[2 * w + h2];
-          const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-          Ls += f * sm_l[2 * w + h2];
-          O += f * sm_o[(2 * w + h2) * kHeadDim + d];
-        }
-      }
+      for (int w = qd; w < 4; w += nquads) O += sm_f[w * 4 + h] * sm_o[(w * 4 + h) * kHeadDim + d];
       if (a.nch == 1) {
         out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
       } else {
@@ -1327,7 +1445,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
 #define MK_MERGE_BATCH 8
 #endif
         const int nout = pl.qpk * kHeadDim;
-        float* sm_pm = sm_l + 16;                        // [chunks][qpk]
+        float* sm_pm = sm_l + 16 + 32;                   // [chunks][qpk]
         float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
 #pragma unroll 1
         for (int i = c.tid; i < a.nch * pl.qpk; i += kNumConsumers) {
@@ -1821,7 +1939,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           if (aborted(c)) { go = -1; break; }
           const unsigned long long now = globaltimer();
           if (t0 == 0) t0 = now;
-          if (now - t0 > c.p.timeout_ns) {
+          if (now - t0 > 4 * c.p.timeout_ns) {
             raise_abort(c, ST_TIMEOUT_GO, iter, go);
             go = -1;
             break;
@@ -1940,7 +2058,7 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
           if (aborted(c)) { go = -1; break; }
           const unsigned long long now = globaltimer();
           if (t0 == 0) t0 = now;
-          if (now - t0 > c.p.timeout_ns) { go = -1; break; }
+          if (now - t0 > 4 * c.p.timeout_ns) { go = -1; break; }
         }
       }
     }
@@ -1977,7 +2095,7 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
             if (aborted(c)) { dead = true; break; }
             const unsigned long long now = globaltimer();
             if (t0 == 0) t0 = now;
-            if (now - t0 > c.p.timeout_ns) { dead = true; break; }
+            if (now - t0 > 4 * c.p.timeout_ns) { dead = true; break; }
           }
         }
       }
@@ -2024,6 +2142,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.epoch = 0;
   c.cons_idx = 0;
   c.xphase = 0;
+  c.arrived = false;
+  c.attn_iter = -1;
   c.tid = threadIdx.x;
   c.lane = threadIdx.x & 31;
   c.warp = threadIdx.x >> 5;

@@ -827,7 +827,8 @@ int mk_compile(mk_handle* h) {
     } else if (p.type == mk::OP_RMSNORM) {
       x_bytes = std::max(x_bytes, ((p.n + 63) / 64 * 64 + 8) * 2 + 16);
     } else if (p.type == mk::OP_ATTN) {
-      x_bytes = std::max(x_bytes, 16 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 256);
+      // q heads and the new k (bf16), four combine slots of 4 heads x 128 floats, (max, sum) pairs, merge scratch
+      x_bytes = std::max(x_bytes, 9 * 256 + 4 * 4 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 256);
     }
   }
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
