@@ -59,9 +59,13 @@ def main():
           f"(batch {args.batch}, context ~{iters}, {args.layers} layers, grid {dec.mpk.grid_size()})")
     tr = dec.mpk.op_trace().double()  # [ops + 1, grid, 4]
     n = tr.shape[0] - 1
-    names = ["embed"] + ["qkv", "attention", "o_proj", "gate_up", "down"] * args.layers + ["lm_head", "argmax"]
-    if len(names) != n:
-        names = [f"op{i}" for i in range(n)]
+    # label every device op by its kind and shape, e.g. "linear 6144x4096" (QKV), "attention"
+    names = []
+    for line in dec.mpk.describe().strip().splitlines():
+        f = line.split()
+        kv = dict(x.split("=", 1) for x in f[2:] if "=" in x)
+        names.append(f"{f[1]} {kv['n']}x{kv['k']}" if f[1] == "linear" else f[1])
+    assert len(names) == n, (len(names), n)
     agg = collections.OrderedDict()
     for i in range(n):
         reach, passed, done = tr[i, :, 0], tr[i, :, 1], tr[i, :, 2]
@@ -71,11 +75,11 @@ def main():
         a[2] += float(passed.max() - reach.max())   # last CTA at the barrier -> barrier open
         a[3] += float((done - passed).mean())
         a[4] += float((done - passed).max())
-    print(f"{'op':10s} {'count':>5s} {'first arrival -> open':>22s} {'last arrival -> open':>21s} {'body mean':>10s} {'body max':>9s}   (us per op)")
+    print(f"{'op':20s} {'count':>5s} {'first arrival -> open':>22s} {'last arrival -> open':>21s} {'body mean':>10s} {'body max':>9s}   (us per op)")
     total = 0.0
     for k, a in agg.items():
         c = a[0]
-        print(f"{k:10s} {c:5d} {a[1] / c / 1e3:22.2f} {a[2] / c / 1e3:21.2f} {a[3] / c / 1e3:10.2f} {a[4] / c / 1e3:9.2f}")
+        print(f"{k:20s} {c:5d} {a[1] / c / 1e3:22.2f} {a[2] / c / 1e3:21.2f} {a[3] / c / 1e3:10.2f} {a[4] / c / 1e3:9.2f}")
         total += a[2] + a[4]
     print(f"sum of (last arrival -> open) + (slowest body): {total / 1e6:.3f} ms per iteration")
     dec.finalize()

@@ -397,6 +397,12 @@ class PersistentKernel:
         self._check(self._lib.mk_describe(self._h, buf, 1 << 20), "describe")
         return buf.value.decode()
 
+    def describe(self) -> str:
+        """The device-op list of a planned or compiled graph, one line per op."""
+        buf = C.create_string_buffer(1 << 20)
+        self._check(self._lib.mk_describe(self._h, buf, 1 << 20), "describe")
+        return buf.value.decode()
+
     def compile(self, output_dir: str = None, **kwargs):
         assert not self._is_compiled
         if not torch.cuda.is_available():
