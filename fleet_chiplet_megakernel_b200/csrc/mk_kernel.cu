@@ -102,6 +102,9 @@ struct Ctx {
   unsigned xphase;    // per stage: parity of the next activation-box phase (only some ops use the boxes)
   bool arrived;       // this CTA has already arrived at the coming grid barrier
   int attn_iter;      // iteration whose attention metadata is cached in shared memory
+  uint32_t tmem;      // base address of the CTA's tensor-memory columns
+  bool has_tmem;
+  unsigned done_phase;  // phases of the accumulator-ready mbarrier consumed so far
   int tid, lane, warp;
   int iter, cur_op;
   unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
@@ -114,6 +117,9 @@ struct Ctx {
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
   __device__ uint32_t xfull_bar(int s) const { return smem_addr + p.bar_off + 8 * (2 * p.num_stages + s); }
   __device__ volatile int* flags() const { return (volatile int*)(smem + p.bar_off + 24 * p.num_stages); }
+  // behind the flags: the accumulator-ready mbarrier of the tcgen05 path and the word tcgen05.alloc writes
+  __device__ uint32_t done_bar() const { return smem_addr + p.bar_off + 24 * p.num_stages + 64; }
+  __device__ uint32_t tmem_slot() const { return smem_addr + p.bar_off + 24 * p.num_stages + 72; }
   __device__ float* sums() const { return (float*)(smem + p.sums_off); }
   __device__ float* red() const { return (float*)(smem + p.red_off); }  // small scratch: reductions, lengths
 };
@@ -487,38 +493,27 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     }
   }
   if (op.flags & F_ARGMAX) {
-    float* scratch = c.red() + 32;
-    for (int tb = 0; tb < ntok; ++tb) {
+    // one warp per token: the tile's 128 bf16 logits of the token, four per lane
+#pragma unroll 1
+    for (int tb = c.warp; tb < ntok; tb += kNumConsumerWarps) {
       ArgBest b;
       b.v = -INFINITY;
       b.i = 0x7fffffff;
-      if (c.tid < kTileRows) {
-        const int col = blk * kTileRows + c.tid;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int row = c.lane + 32 * q, col = blk * kTileRows + row;
         if (col < op.n) {
-          b.v = rbf(red[c.tid * kRedStride + tb]);
-          b.i = col;
+          ArgBest x;
+          x.v = rbf(red[row * kRedStride + tb]);
+          x.i = col;
+          b = arg_better(b, x);
         }
       }
       b = warp_argmax(b);
-      if (c.lane == 0 && c.warp < 4) {
-        scratch[c.warp * 2] = b.v;
-        scratch[c.warp * 2 + 1] = __int_as_float(b.i);
+      if (c.lane == 0) {
+        op.amax_val[(size_t)(tok0 + tb) * op.amax_n + blk] = b.v;
+        op.amax_idx[(size_t)(tok0 + tb) * op.amax_n + blk] = b.i;
       }
-      consumer_sync();
-      if (c.tid == 0) {
-        ArgBest a;
-        a.v = scratch[0];
-        a.i = __float_as_int(scratch[1]);
-        for (int w = 1; w < 4; ++w) {
-          ArgBest x;
-          x.v = scratch[w * 2];
-          x.i = __float_as_int(scratch[w * 2 + 1]);
-          a = arg_better(a, x);
-        }
-        op.amax_val[(size_t)(tok0 + tb) * op.amax_n + blk] = a.v;
-        op.amax_idx[(size_t)(tok0 + tb) * op.amax_n + blk] = a.i;
-      }
-      consumer_sync();
     }
   }
 }
@@ -828,6 +823,157 @@ __device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0
 }
 
 // ------------------------------------------------------------------------------------
+// Stream-K tiles on the 5th-generation tensor cores (17-64 tokens).  With mma.sync every warp
+// re-reads the activation boxes of a stage (at 64 tokens: 160 KB of ldmatrix traffic per
+// 32 KB weight tile, the SM's shared-memory bandwidth is the limit).  tcgen05.mma reads both
+// operands from shared memory once: A = the weight tile (M = 128 rows), B = the activation
+// box (N = 32 or 64 token rows), both K-major with the 128-byte swizzle TMA left them in;
+// D = 128 lanes x N columns of fp32 in tensor memory.  One thread issues the 8 MMAs of a
+// stage (2 boxes x 4 k-steps of 16) and commits them to the stage's "empty" mbarrier; when a
+// run of tiles ends, a commit to the "done" mbarrier tells all warps to fetch the
+// accumulators (tcgen05.ld, warp w reads lanes 32 * (w & 3) .. + 31) into the sums block,
+// from where the usual split-k finish and epilogue take over.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+  // start address >> 4 | leading offset (unused for swizzled K-major) 1 | stride between 8-row
+  // groups 1024 B >> 4 | descriptor version 1 | layout 2 = 128-byte swizzle
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __noinline__ void linear_pass_umma(Ctx& c, const OpDesc& op, int tok0, int T, int group) {
+  const KParams& p = c.p;
+  const int nkt = op.nkt;
+  const int ntok = min(op.aux3, T - tok0);
+  const int N = p.x_rows;  // 32 or 64 token rows per activation box
+  const unsigned total = (unsigned)op.nblk * (unsigned)nkt;
+  const int G = (int)min(gridDim.x, total);
+  if ((int)blockIdx.x >= G) return;
+  const unsigned t0 = tile_begin(blockIdx.x, total, G);
+  const unsigned t1 = tile_begin(blockIdx.x + 1, total, G);
+  const int S = p.num_stages;
+  const int lane = c.lane, warp = c.warp;
+  const uint32_t x_sub = (uint32_t)N * 128u;  // bytes of one activation box
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0), bar_x0 = c.xfull_bar(0);
+  // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+  const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
+  const __nv_bfloat16* res_ptr = reinterpret_cast<const __nv_bfloat16*>(op.res) +
+                                 (size_t)(tok0 + (c.tid >> 7)) * op.ld_res + (c.tid & 127);
+  const bool res_tok = with_res && (c.tid >> 7) < ntok;
+  int blk = (int)(t0 / (unsigned)nkt);
+  int kt = (int)(t0 - (unsigned)blk * (unsigned)nkt);
+  int kt_first = kt;
+  bool first_of_cta = true;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+  float res0 = 0.f;
+  bool new_blk = true;
+  bool fresh = true;  // the next MMA starts a run: it overwrites the accumulators
+  for (unsigned tile = t0; tile < t1; ++tile) {
+    if (new_blk) {
+      new_blk = false;
+      res0 = 0.f;
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+    }
+    // every warp follows the ring (one arrival per warp and phase keeps the "empty" count
+    // exact); warp 0's arrival is the commit of the stage's MMAs
+    bool ok = mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+    if (warp == 0) {
+      ok = mbar_wait(c, bar_x0 + 8 * s, (c.xphase >> s) & 1u, ST_TIMEOUT_FULL) && ok;
+      if (lane == 0) {
+        if (ok) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+          const uint32_t xt = st + kStageBytes;
+#pragma unroll
+          for (int sub = 0; sub < kSubTiles; ++sub) {
+            const uint64_t ad = umma_smem_desc(st + (uint32_t)sub * kSubBytes);
+            const uint64_t bd = umma_smem_desc(xt + (uint32_t)sub * x_sub);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16) {
+              // 16 k-elements = 32 bytes further inside the 128-byte swizzle span: +2 in the address field
+              umma_bf16(c.tmem, ad + (uint64_t)(2 * k16), bd + (uint64_t)(2 * k16), idesc, (fresh && sub == 0 && k16 == 0) ? 0u : 1u);
+            }
+          }
+          umma_commit(bar_empty0 + 8 * s);
+        } else {
+          mbar_arrive(bar_empty0 + 8 * s);  // aborting: keep the count exact, the body is skipped
+        }
+      }
+      __syncwarp();
+    } else if (lane == 0) {
+      mbar_arrive(bar_empty0 + 8 * s);
+    }
+    c.xphase ^= 1u << s;
+    fresh = false;
+    ++consumed;
+    if (++s == S) {
+      s = 0;
+      parity ^= 1u;
+    }
+    const bool end_blk = (kt == nkt - 1);
+    if (end_blk || tile == t1 - 1) {
+      // accumulators complete -> sums block [row][token]
+      if (warp == 0 && lane == 0) umma_commit(c.done_bar());
+      __syncwarp();
+      mbar_wait(c, c.done_bar(), c.done_phase & 1u, ST_TIMEOUT_FULL);
+      c.done_phase += 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      __syncwarp();
+      {
+        const int q = warp & 3, half = warp >> 2;  // lane quadrant, column half
+        const int row = 32 * q + lane;
+        const int ncol = N >> 1;  // columns of this warp: 16 or 32
+        float* dst = c.sums() + row * p.sums_stride + half * ncol;
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncol; c0 += 16) {
+          float v[16];
+          tmem_ld16(c.tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(half * ncol + c0), v);
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(dst + c0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      linear_finish_piece(c, op, blk, kt_first, kt, first_of_cta, tok0, ntok, group, res0);
+      first_of_cta = false;
+      kt_first = 0;
+      fresh = true;
+    }
+    if (end_blk) {
+      kt = 0;
+      blk += 1;
+      new_blk = true;
+    } else {
+      kt += 1;
+    }
+  }
+  c.cons_idx += consumed;
+}
+
+// ------------------------------------------------------------------------------------
 // Row-owner linear (F_ROWS): for one or two tokens the cross-CTA finish of a k-split costs
 // more than the whole weight stream of a small layer, so every CTA takes whole output rows
 // instead: a contiguous range of 8-row units, walked in chunks of up to 32 rows over the
@@ -1024,6 +1170,7 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
     for (int g = 0; g < passes; ++g) {
       if (p_x_rows(c) == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
       else if (p_x_rows(c) == 16) linear_pass_wide<2>(c, op, g * op.aux3, T, g);
+      else if (c.has_tmem && !(c.p.debug_flags & 4)) linear_pass_umma(c, op, g * op.aux3, T, g);
       else if (p_x_rows(c) == 32) linear_pass_wide<4>(c, op, g * op.aux3, T, g);
       else linear_pass_wide<8>(c, op, g * op.aux3, T, g);
     }
@@ -1167,6 +1314,71 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
   attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr, pgc, fill);
 }
 
+// The half-warp's pass over its positions of the task: for up to four q heads of the kv-head
+// group, running (max, sum, output) per head.  Rows are consumed four at a time while the next
+// four are in flight; `a.kr/a.vr` hold the first batch (loaded ahead of the op's barrier).
+__device__ __forceinline__ void attn_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, AttnTask& a, int l16, int hq,
+                                          const uint4* qv, uint4 knew, uint4 vnew, float sc, float* m, float* l,
+                                          float (*o)[8]) {
+  const int L = a.L;
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
+  }
+  const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
+#pragma unroll 1
+  for (int it = 0; it < niter; it += 4) {
+    // the next four rows are requested before this batch is used
+    uint4 nk[4], nv[4];
+    const bool more = it + 4 < niter;
+    if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
+      const bool ok = j < a.p1;  // may differ between the two halves of a warp
+      if (!__any_sync(0xffffffffu, ok)) continue;  // neither half has a row here: skip it together
+      if (ok && j == L - 1) {
+        a.kr[u] = knew;
+        a.vr[u] = vnew;
+      }
+      float kk[8], vf[8];
+      unpack8(a.kr[u], kk);
+      unpack8(a.vr[u], vf);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (h < hq) {  // uniform
+          float qf[8];
+          unpack8(qv[h], qf);
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
+#pragma unroll
+          for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+          if (ok) {
+            const float sv = d * sc;
+            const float mn = fmaxf(m[h], sv);
+            const float alpha = exp2f(m[h] - mn), pr = exp2f(sv - mn);
+            l[h] = l[h] * alpha + pr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[h][i] = fmaf(pr, vf[i], o[h][i] * alpha);
+            m[h] = mn;
+          }
+        }
+      }
+    }
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a.kr[u] = nk[u];
+        a.vr[u] = nv[u];
+      }
+    }
+  }
+}
+
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
 // request, token t == request slot t.
 __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
@@ -1281,62 +1493,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     const uint4 knew = sm_k[l16];
     MK_STAMP(c, 2);
     float m[4], l[4], o[4][8];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      m[h] = -INFINITY;
-      l[h] = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[h][i] = 0.f;
-    }
-    const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
-#pragma unroll 1
-    for (int it = 0; it < niter; it += 4) {
-      // the next four rows are requested before this batch is used
-      uint4 nk[4], nv[4];
-      const bool more = it + 4 < niter;
-      if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
-        const bool ok = j < a.p1;  // may differ between the two halves of a warp
-        if (!__any_sync(0xffffffffu, ok)) continue;  // neither half has a row here: skip it together
-        if (ok && j == L - 1) {
-          a.kr[u] = knew;
-          a.vr[u] = vnew;
-        }
-        float kk[8], vf[8];
-        unpack8(a.kr[u], kk);
-        unpack8(a.vr[u], vf);
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          if (h < hq) {  // uniform
-            float qf[8];
-            unpack8(qv[h], qf);
-            float d = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
-#pragma unroll
-            for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-            if (ok) {
-              const float sv = d * sc;
-              const float mn = fmaxf(m[h], sv);
-              const float alpha = exp2f(m[h] - mn), pr = exp2f(sv - mn);
-              l[h] = l[h] * alpha + pr;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[h][i] = fmaf(pr, vf[i], o[h][i] * alpha);
-              m[h] = mn;
-            }
-          }
-        }
-      }
-      if (more) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          a.kr[u] = nk[u];
-          a.vr[u] = nv[u];
-        }
-      }
-    }
+    attn_rows(c, op, pl, a, l16, hq, qv, knew, vnew, sc, m, l, o);
     MK_STAMP(c, 3);
     // combine the position groups: the two halves of a warp by shuffle, warps 4-7 into warps
     // 0-3 through shared memory, then every output element over the remaining four slots
@@ -1585,9 +1742,14 @@ __device__ void op_argmax_partial(Ctx& c, const OpDesc& op, int T) {
 }
 
 // partial pairs -> int64 token per row; CTA 0 only
+// Up to 8 tokens CTA 0 reduces them all: it also runs the bookkeeping that reads the result,
+// so nothing has to cross CTAs.  Larger batches are spread over the grid (one token per CTA
+// at a time) and pay one more grid barrier so that CTA 0 sees every token.
 __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
   long long* out = reinterpret_cast<long long*>(op.out);
-  for (int tok = 0; tok < T; ++tok) {
+  const bool spread = T > 8;
+  if (!spread && blockIdx.x != 0) return;
+  for (int tok = spread ? blockIdx.x : 0; tok < T; tok += spread ? gridDim.x : 1) {
     ArgBest b;
     b.v = -INFINITY;
     b.i = 0x7fffffff;
@@ -1600,6 +1762,7 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
     b = block_argmax(c, b);
     if (c.tid == 0) out[(size_t)tok * op.ld_out] = (b.i == 0x7fffffff) ? -1 : (long long)b.i;
   }
+  if (spread) grid_sync(c);
 }
 
 // ------------------------------------------------------------------------------------
@@ -2144,6 +2307,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.xphase = 0;
   c.arrived = false;
   c.attn_iter = -1;
+  c.tmem = 0u;
+  c.has_tmem = false;
+  c.done_phase = 0;
   c.tid = threadIdx.x;
   c.lane = threadIdx.x & 31;
   c.warp = threadIdx.x >> 5;
@@ -2161,6 +2327,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       mbar_init(c.empty_bar(s), kNumConsumerWarps);
       mbar_init(c.xfull_bar(s), 1);
     }
+    mbar_init(c.done_bar(), 1);
     fl[0] = 0;
     fl[1] = 0;
     fl[2] = 0;
@@ -2171,6 +2338,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  // Tensor memory for the tcgen05 linears (32 or 64 token rows per box): x_rows columns of fp32
+  // accumulators, allocated once by warp 0 and freed by it when the CTA leaves.
+  const bool use_tmem = p.x_rows >= 32;
+  if (use_tmem) {
+    if (c.warp == 0) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(c.tmem_slot()), "r"((uint32_t)p.x_rows) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    c.tmem = *reinterpret_cast<volatile uint32_t*>(c.smem + p.bar_off + 24 * p.num_stages + 72);
+    c.has_tmem = true;
+  }
 
   if (c.warp == kNumConsumerWarps) {
     if (c.lane == 0) producer_loop(c);
@@ -2285,11 +2466,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     const unsigned issued = (unsigned)fl[1];
     for (unsigned i = c.cons_idx; i < issued; ++i)
       mbar_wait(c, c.full_bar(i % p.num_stages), (i / p.num_stages) & 1, ST_TIMEOUT_FULL);
-    if (p.mode == MODE_OFFLINE && blockIdx.x == 0 && c.iter - 1 < p.max_step_times) {
-      // closing timestamp
-    }
   }
   __syncthreads();
+  if (use_tmem && c.warp == 0) {
+    // every tensor-core operation of this CTA has completed before its columns are given back:
+    // one more commit collects whatever an aborted pass left in flight (bounded wait)
+    if (c.lane == 0) {
+      umma_commit(c.done_bar());
+      mbar_wait(c, c.done_bar(), c.done_phase & 1u, ST_TIMEOUT_FULL);
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c.tmem), "r"((uint32_t)p.x_rows) : "memory");
+  }
 }
 
 __global__ void init_state_kernel(KParams p) {

@@ -337,7 +337,7 @@ int plan_graph(mk_handle* h) {
         h->plan.push_back(po);
         PlanOp rd;
         rd.type = mk::OP_ARGMAX_REDUCE;
-        rd.flags = mk::F_CTA0_ONLY;
+        rd.flags = 0;  // CTA 0 alone up to 8 tokens, the whole grid beyond (decided on the device)
         rd.out = h->ops[i + 2].t.back();
         rd.amax_n = po.amax_n;
         rd.in = -2;  // reads the previous op's partials
@@ -405,7 +405,7 @@ int plan_graph(mk_handle* h) {
       h->plan.push_back(po);
       PlanOp rd;
       rd.type = mk::OP_ARGMAX_REDUCE;
-      rd.flags = mk::F_CTA0_ONLY;
+      rd.flags = 0;  // CTA 0 alone up to 8 tokens, the whole grid beyond (decided on the device)
       rd.out = out;
       rd.amax_n = po.amax_n;
       rd.in = -2;

@@ -286,7 +286,11 @@ def _attention_case(seq_lens, n_q, n_kv, page_size, numerics, seed):
 @pytest.mark.parametrize("numerics", ["mpk", "torch"])
 @pytest.mark.parametrize("seq_lens,n_q,n_kv,page", [([1], 4, 2, 16), ([65], 32, 8, 64), ([1025], 32, 8, 64),
                                                     ([64, 1, 17, 200], 8, 2, 16), ([1200], 32, 8, 64),
-                                                    ([300, 299, 301], 4, 1, 32), ([128], 16, 2, 64)])
+                                                    ([300, 299, 301], 4, 1, 32), ([128], 16, 2, 64),
+                                                    # more (request, kv head) pairs than SMs: several rounds of tasks
+                                                    ([3 + (i * 7) % 60 for i in range(40)], 32, 8, 16),
+                                                    ([1 + (i * 13) % 90 for i in range(24)], 16, 8, 32),
+                                                    ([5 + i for i in range(64)], 8, 8, 64)])
 def test_paged_attention(seq_lens, n_q, n_kv, page, numerics):
     _attention_case(seq_lens, n_q, n_kv, page, numerics, seed=100 + len(seq_lens) + n_q)
 
