@@ -229,6 +229,9 @@ def run_ours(args):
     first = PROMPT_LEN - 1 + W
     step_ns = t[first + 1: first + K + 1] - t[first: first + K]
     tpot_ms = float(step_ns.sum() / K / 1e6)
+    import numpy as _np
+    tpot_median_ms = float(_np.median(step_ns) / 1e6)
+    tpot_first_ms, tpot_last_ms = float(step_ns[: max(1, K // 10)].mean() / 1e6), float(step_ns[-max(1, K // 10):].mean() / 1e6)
     # end to end through the public API: pinned host prompts in, host tokens out
     host_prompts = [p.pin_memory() for p in prompts]
     torch.cuda.synchronize()
@@ -272,6 +275,8 @@ def run_ours(args):
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
                    "launch_ms_total": launch_ms, "iterations": iters},
         "tokens_per_s": B * 1e3 / tpot_ms,
+        "tpot_median_ms": tpot_median_ms,
+        "tpot_first_tenth_ms": tpot_first_ms, "tpot_last_tenth_ms": tpot_last_ms,  # context grows during the run
         "clocks": clocks,
         "e2e": {"value": e2e_ms, "unit": "ms/token", "h2d_bytes_per_step": B * PROMPT_LEN * 8 / (W + K),
                 "d2h_bytes_per_step": B * (PROMPT_LEN + W + K) * 8 / (W + K),
