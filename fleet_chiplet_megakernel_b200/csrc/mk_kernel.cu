@@ -173,25 +173,11 @@ __device__ __noinline__ bool mbar_wait_slow(const Ctx& c, uint32_t bar, uint32_t
     }
   }
 }
-#ifndef MK_WAIT_STYLE
-#define MK_WAIT_STYLE 0
-#endif
+// Fast path: a few hundred polls without touching the clock; then the bounded slow path.
 __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t parity, int code) {
-#if MK_WAIT_STYLE == 0
 #pragma unroll 1
   for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-#elif MK_WAIT_STYLE == 1
-  for (int i = 0; i < 16; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  (void)globaltimer();
-#elif MK_WAIT_STYLE == 2
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(32);
-  }
-#endif
   return mbar_wait_slow(c, bar, parity, code);
 }
 
@@ -1379,6 +1365,128 @@ __device__ __forceinline__ void attn_rows(const Ctx& c, const OpDesc& op, const 
   }
 }
 
+// Larger batches: with more (request, kv head) pairs than CTAs and sequences short enough to
+// need no split, a CTA runs 2 or 4 pairs side by side instead of one after the other: its 8
+// warps form groups of 4 or 2, every group is a small copy of the CTA-wide scheme (its warps
+// split the positions, a half-warp serves all q heads of the pair, the group meets on a
+// named barrier of its own).  The fixed latencies of a pair (q path, row fetches, combine)
+// are then paid once per round of `groups` pairs.
+__device__ __forceinline__ void group_sync(int g, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(2 + g), "r"(nthreads) : "memory");
+}
+__device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const AttnPlan& pl0, const int* lens, int wpg) {
+  const KParams& p = c.p;
+  const int G = gridDim.x;
+  AttnPlan pl = pl0;
+  const int ngrp = kNumConsumerWarps / wpg;
+  const int g = c.warp / wpg, lw = c.warp % wpg;
+  const int gthreads = wpg * 32, gtid = lw * 32 + c.lane;
+  const int l16 = c.lane & 15;
+  const int hq = pl.qpk;  // at most 4 here
+  pl.ngroups = 2 * wpg;
+  pl.gi = 2 * lw + (c.lane >> 4);
+  const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+  const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
+  // per group: q heads [4][16] + new k [16] (bf16 x 8 per entry); per warp: 4 heads x 128 floats, (max, sum) x 4
+  uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off) + g * 80;
+  uint4* sm_k = sm_q + 64;
+  float* sm_o = reinterpret_cast<float*>(reinterpret_cast<uint4*>(c.smem + p.x_off) + 4 * 80) + c.warp * 4 * kHeadDim;
+  float* sm_ml = reinterpret_cast<float*>(reinterpret_cast<uint4*>(c.smem + p.x_off) + 4 * 80) + kNumConsumerWarps * 4 * kHeadDim;
+  bool first = true;
+#pragma unroll 1
+  for (int task = blockIdx.x + G * g;; task += G * ngrp) {
+    AttnTask a;
+    attn_prepare(c, op, pl, lens, task, l16, a);
+    if (first) {
+      first = false;
+      if (op.flags & F_SYNC_BEFORE) {  // op_barrier with the wait inlined: the prefetched rows stay in registers
+        grid_wait(c);
+        if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+        c.dead = c.flags()[3] != 0;
+        if (c.dead) return;
+      } else if (op_barrier(c, op)) {
+        return;
+      }
+    }
+    if (task >= pl.ntasks) break;   // uniform within the group
+    if (!a.valid) continue;
+    const int L = a.L;
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
+                               (size_t)a.h * (pl.qpk + 2) * kHeadDim;
+    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+#pragma unroll 1
+    for (int h = lw; h < hq; h += wpg) {  // this warp's share of the q heads
+      F8 q;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + h * kHeadDim) + l16), q.v);
+      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+      if (c.lane < 16) sm_q[h * 16 + l16] = pack8(q.v);
+    }
+    if (lw == wpg - 1) {  // the group's last warp also prepares the new k
+      F8 kf;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
+      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+      const uint4 kn = pack8(kf.v);
+      if (c.lane < 16) {
+        sm_k[l16] = kn;
+        if (a.p1 == L) {  // append the new token's K and V to the cache
+          const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+        }
+      }
+    }
+    group_sync(g, gthreads);
+    uint4 qv[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) qv[h] = (h < hq) ? sm_q[h * 16 + l16] : make_uint4(0, 0, 0, 0);
+    const uint4 knew = sm_k[l16];
+    float m[4], l[4], o[4][8];
+    attn_rows(c, op, pl, a, l16, hq, qv, knew, vnew, sc, m, l, o);
+    // the two halves of a warp by shuffle, then the group's warps through shared memory
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (h < hq) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m[h], 16), l2 = __shfl_xor_sync(0xffffffffu, l[h], 16);
+        const float M = fmaxf(m[h], m2);
+        const float f1 = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M), f2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - M);
+        const float lsum = f1 * l[h] + f2 * l2;
+        float r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = f1 * o[h][i] + f2 * __shfl_xor_sync(0xffffffffu, o[h][i], 16);
+        if (c.lane < 16) {
+          float* dst = sm_o + h * kHeadDim + l16 * 8;
+          reinterpret_cast<float4*>(dst)[0] = make_float4(r[0], r[1], r[2], r[3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(r[4], r[5], r[6], r[7]);
+          if (l16 == 0) {
+            sm_ml[(c.warp * 4 + h) * 2] = M;
+            sm_ml[(c.warp * 4 + h) * 2 + 1] = lsum;
+          }
+        }
+      }
+    }
+    group_sync(g, gthreads);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
+                         (size_t)a.h * pl.qpk * kHeadDim;
+    const float* go = reinterpret_cast<const float*>(reinterpret_cast<const uint4*>(c.smem + p.x_off) + 4 * 80) +
+                      (size_t)(g * wpg) * 4 * kHeadDim;  // the group's first warp slot
+#pragma unroll 1
+    for (int e = gtid; e < hq * kHeadDim; e += gthreads) {
+      const int h = e >> 7, d = e & 127;
+      float M = -INFINITY;
+      for (int w = 0; w < wpg; ++w) M = fmaxf(M, sm_ml[((g * wpg + w) * 4 + h) * 2]);
+      float Ls = 0.f, O = 0.f;
+      for (int w = 0; w < wpg; ++w) {
+        const float mw = sm_ml[((g * wpg + w) * 4 + h) * 2];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += f * sm_ml[((g * wpg + w) * 4 + h) * 2 + 1];
+        O += f * go[(w * 4 + h) * kHeadDim + d];
+      }
+      out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
+    }
+    group_sync(g, gthreads);  // the group's buffers are free again
+  }
+}
+
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
 // request, token t == request slot t.
 __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
@@ -1423,6 +1531,11 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   pl.CS = bpc * 16;
   pl.nch_max = (nb_max + bpc - 1) / bpc;
   pl.ntasks = T * pl.HKV * pl.nch_max;
+  // More (request, kv head) pairs than CTAs and no sequence that needs splitting: several pairs per CTA at a time.
+  if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4 && p.x_rows >= 32) {
+    attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4);
+    return;
+  }
   const int l16 = c.lane & 15;
   // A half-warp serves up to four q heads of the group at once (one K/V row load feeds all of
   // them); with eight q heads per kv head the warps alternate between the two head quads.
@@ -1598,9 +1711,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
         // The (max, sum) pairs of all chunks go through shared memory; the values are read in
         // small batches: more than a few dozen loads in flight per thread slowed the merge down.
-#ifndef MK_MERGE_BATCH
-#define MK_MERGE_BATCH 8
-#endif
+        constexpr int kMergeBatch = 8;
         const int nout = pl.qpk * kHeadDim;
         float* sm_pm = sm_l + 16 + 32;                   // [chunks][qpk]
         float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
@@ -1619,13 +1730,13 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
           for (int cc = 0; cc < a.nch; ++cc) M = fmaxf(M, sm_pm[cc * pl.qpk + eh]);
           float Ls = 0.f, O = 0.f;
 #pragma unroll 1
-          for (int c0 = 0; c0 < a.nch; c0 += MK_MERGE_BATCH) {
-            float v[MK_MERGE_BATCH];
+          for (int c0 = 0; c0 < a.nch; c0 += kMergeBatch) {
+            float v[kMergeBatch];
 #pragma unroll
-            for (int u = 0; u < MK_MERGE_BATCH; ++u)
+            for (int u = 0; u < kMergeBatch; ++u)
               v[u] = (c0 + u < a.nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
 #pragma unroll
-            for (int u = 0; u < MK_MERGE_BATCH; ++u) {
+            for (int u = 0; u < kMergeBatch; ++u) {
               if (c0 + u < a.nch) {
                 const float f = exp2f(sm_pm[(c0 + u) * pl.qpk + eh] - M);
                 Ls += f * sm_pl[(c0 + u) * pl.qpk + eh];
@@ -1667,8 +1778,20 @@ __device__ void op_embed(Ctx& c, const OpDesc& op, int T) {
 
 __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   const int kp = ((op.n + 63) / 64) * 64;
+  // the norm weights do not depend on other CTAs: a CTA that has a row fetches them ahead of the barrier
+  uint4 pre_w[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  const bool pre = (kp >> 3) <= 4 * kNumConsumers;
+  if (pre && (int)blockIdx.x < T) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int v = c.tid + kNumConsumers * i;
+      if (v < (op.n >> 3)) pre_w[i] = __ldg(reinterpret_cast<const uint4*>(op.w) + v);
+    }
+  }
+  if (op_barrier(c, op)) return;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1, nullptr);
+    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1,
+            pre ? pre_w : nullptr);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out);
     for (int v = c.tid; v < (op.n >> 3); v += kNumConsumers) dst[v] = xs[v];
@@ -2437,7 +2560,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
         }
         switch (op.type) {
           case OP_EMBED: if (!op_barrier(c, op)) op_embed(c, op, T); break;
-          case OP_RMSNORM: if (!op_barrier(c, op)) op_rmsnorm(c, op, T); break;
+          case OP_RMSNORM: op_rmsnorm(c, op, T); break;
           case OP_LINEAR: op_linear(c, op, T); break;
           case OP_ATTN:
             op_attention(c, op, T);

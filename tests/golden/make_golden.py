@@ -203,7 +203,9 @@ def config1_inputs():
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <root of the reference checkout>")
+    ref_root = sys.argv[1]
     torch.manual_seed(0)
     gen_generate_fixture(ref_root, O.TINY, "tiny_generate.pt", prompt_len=8, n_new=40, max_seq=64, norm_jitter=0.25)
     gen_generate_fixture(ref_root, O.SMALL, "small_generate.pt", prompt_len=16, n_new=40, max_seq=96, norm_jitter=0.0)
