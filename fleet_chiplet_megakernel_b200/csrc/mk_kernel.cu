@@ -1129,40 +1129,41 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   c.cons_idx += consumed;
 }
 
-__device__ __forceinline__ int p_x_rows(const Ctx& c) { return c.p.x_rows; }
-
+template <int PATH>
 __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   // the norm weights do not depend on other CTAs: fetched ahead of the barrier
   uint4 pre_w[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-  const int wpr0 = stage_warps_per_row(min(op.aux3, T));
-  const int kvec_pad = op.nkt * (((op.flags & F_ROWS) ? kRowsStageK : kTileK) >> 3);  // padded row, in 16-byte vectors
-  const bool pre = (op.flags & F_NORM_IN) && kvec_pad <= 128 * wpr0;
-  if (pre) {
+  bool pre = false;
+  if constexpr (PATH != PATH_UMMA) {
+    const int wpr0 = stage_warps_per_row(min(op.aux3, T));
+    const int kvec_pad = op.nkt * ((PATH == PATH_ROWS ? kRowsStageK : kTileK) >> 3);  // padded row, in 16-byte vectors
+    pre = (op.flags & F_NORM_IN) && kvec_pad <= 128 * wpr0;
+    if (pre) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int v = (c.warp % wpr0) * 32 + c.lane + 32 * wpr0 * i;
-      if (v < (op.k >> 3)) pre_w[i] = __ldg(reinterpret_cast<const uint4*>(op.norm_w) + v);
+      for (int i = 0; i < 4; ++i) {
+        const int v = (c.warp % wpr0) * 32 + c.lane + 32 * wpr0 * i;
+        if (v < (op.k >> 3)) pre_w[i] = __ldg(reinterpret_cast<const uint4*>(op.norm_w) + v);
+      }
     }
   }
   if (op_barrier(c, op)) return;
   c.lin_seq += 1;
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the activation producer may now read this op's input
   const int passes = linear_passes(op, T);
-  if (op.flags & F_ROWS) {
+  if constexpr (PATH == PATH_ROWS) {
     for (int g = 0; g < passes; ++g) linear_pass_rows(c, op, g * op.aux3, T, (pre && g == 0) ? pre_w : nullptr);
-    return;
-  }
-  if (op.flags & F_XTILE) {
-    for (int g = 0; g < passes; ++g) {
-      if (p_x_rows(c) == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
-      else if (p_x_rows(c) == 16) linear_pass_wide<2>(c, op, g * op.aux3, T, g);
-      else if (c.has_tmem && !(c.p.debug_flags & 4)) linear_pass_umma(c, op, g * op.aux3, T, g);
-      else if (p_x_rows(c) == 32) linear_pass_wide<4>(c, op, g * op.aux3, T, g);
-      else linear_pass_wide<8>(c, op, g * op.aux3, T, g);
+  } else if constexpr (PATH == PATH_UMMA) {
+    for (int g = 0; g < passes; ++g) linear_pass_umma(c, op, g * op.aux3, T, g);
+  } else {
+    if (op.flags & F_XTILE) {
+      for (int g = 0; g < passes; ++g) {
+        if (c.p.x_rows == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
+        else linear_pass_wide<2>(c, op, g * op.aux3, T, g);
+      }
+      return;
     }
-    return;
+    for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
   }
-  for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
 }
 
 // ------------------------------------------------------------------------------------
@@ -1251,7 +1252,7 @@ struct AttnPlan {
 __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a,
                                                 int it0, int l16, uint4* kr, uint4* vr, int* pgc = nullptr,
                                                 bool fill = false) {
-  const int PS = c.p.page_size;
+  const int psh = c.p.page_shift, pmask = c.p.page_size - 1;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int j = a.p0 + (it0 + u) * pl.ngroups + pl.gi;
@@ -1262,10 +1263,10 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
       if (pgc != nullptr && !fill) {
         pg = pgc[u];
       } else {
-        pg = __ldcg(c.p.kv_indices + a.kv_base + j / PS);
+        pg = __ldcg(c.p.kv_indices + a.kv_base + (j >> psh));
         if (pgc != nullptr) pgc[u] = pg;  // all 16 lanes store the same number
       }
-      const size_t src = (((size_t)pg * PS + j % PS) * pl.HKV + a.h) * kHeadDim;
+      const size_t src = ((((size_t)pg << psh) + (j & pmask)) * pl.HKV + a.h) * kHeadDim;
       kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src) + l16);
       vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src) + l16);
     }
@@ -1294,10 +1295,50 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
   if (pgc != nullptr && !fill) {
     a.new_page = pgc[4];
   } else {
-    a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + (a.L - 1) / c.p.page_size) : 0;
+    a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + ((a.L - 1) >> c.p.page_shift)) : 0;
     if (pgc != nullptr) pgc[4] = a.new_page;
   }
   attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr, pgc, fill);
+}
+
+// Merge of a (request, kv head)'s chunks by the CTA that arrived last: kept out of line, only a
+// handful of CTAs per layer ever run it.  `scratch`: [chunks][8] weights, then [8] sums.
+__device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride,
+                                        float* scratch) {
+  const int nout = qpk * kHeadDim;
+  float* sm_w = scratch;                              // [chunks][8]: exp2(max_chunk - max) per head
+  float* sm_s = scratch + c.p.attn_max_chunks * 8;    // [8]: the merged sum per head
+  if (c.tid < qpk) {
+    // one thread per head: the chunks' (max, sum) pairs, eight loads in flight at a time
+    const float* pm = base + nout + c.tid;
+    float M = -INFINITY;
+    for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, __ldcg(pm + (size_t)cc * part_stride));
+    float Ls = 0.f;
+    for (int cc = 0; cc < nch; ++cc) {
+      const float f = exp2f(__ldcg(pm + (size_t)cc * part_stride) - M);
+      sm_w[cc * 8 + c.tid] = f;
+      Ls += f * __ldcg(pm + (size_t)cc * part_stride + qpk);
+    }
+    sm_s[c.tid] = Ls;
+  }
+  consumer_sync();
+  // more than a few dozen loads in flight per thread slowed the merge down: batches of eight
+  constexpr int kMergeBatch = 8;
+#pragma unroll 1
+  for (int e = c.tid; e < nout; e += kNumConsumers) {
+    const int eh = e >> 7;
+    float O = 0.f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < nch; c0 += kMergeBatch) {
+      float v[kMergeBatch];
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u) v[u] = (c0 + u < nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u)
+        if (c0 + u < nch) O += sm_w[(c0 + u) * 8 + eh] * v[u];
+    }
+    out[e] = __float2bfloat16_rn(__fdividef(O, sm_s[eh]));
+  }
 }
 
 // The half-warp's pass over its positions of the task: for up to four q heads of the kv-head
@@ -1321,39 +1362,46 @@ __device__ __forceinline__ void attn_rows(const Ctx& c, const OpDesc& op, const 
     uint4 nk[4], nv[4];
     const bool more = it + 4 < niter;
     if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
-#pragma unroll
+    // The row loop stays rolled (this code runs once per layer out of a cold instruction
+    // cache; its size is its cost): the batch's rows are rotated through slot 0 instead of
+    // being indexed.
+#pragma unroll 1
     for (int u = 0; u < 4; ++u) {
       const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
-      const bool ok = j < a.p1;  // may differ between the two halves of a warp
-      if (!__any_sync(0xffffffffu, ok)) continue;  // neither half has a row here: skip it together
-      if (ok && j == L - 1) {
-        a.kr[u] = knew;
-        a.vr[u] = vnew;
-      }
-      float kk[8], vf[8];
-      unpack8(a.kr[u], kk);
-      unpack8(a.vr[u], vf);
+      const bool ok = j < a.p1;  // may differ between the two halves of a warp: no shuffle may depend on it
+      if (__any_sync(0xffffffffu, ok)) {
+        uint4 kr = a.kr[0], vr = a.vr[0];
+        if (ok && j == L - 1) {
+          kr = knew;
+          vr = vnew;
+        }
+        float kk[8], vf[8];
+        unpack8(kr, kk);
+        unpack8(vr, vf);
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        if (h < hq) {  // uniform
-          float qf[8];
-          unpack8(qv[h], qf);
-          float d = 0.f;
+        for (int h = 0; h < 4; ++h) {
+          if (h < hq) {  // uniform
+            float qf[8];
+            unpack8(qv[h], qf);
+            float d = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
+            for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
 #pragma unroll
-          for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-          if (ok) {
-            const float sv = d * sc;
-            const float mn = fmaxf(m[h], sv);
-            const float alpha = exp2f(m[h] - mn), pr = exp2f(sv - mn);
-            l[h] = l[h] * alpha + pr;
+            for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+            if (ok) {
+              const float sv = d * sc;
+              const float mn = fmaxf(m[h], sv);
+              const float alpha = exp2f(m[h] - mn), pr = exp2f(sv - mn);
+              l[h] = l[h] * alpha + pr;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[h][i] = fmaf(pr, vf[i], o[h][i] * alpha);
-            m[h] = mn;
+              for (int i = 0; i < 8; ++i) o[h][i] = fmaf(pr, vf[i], o[h][i] * alpha);
+              m[h] = mn;
+            }
           }
         }
       }
+      a.kr[0] = a.kr[1]; a.kr[1] = a.kr[2]; a.kr[2] = a.kr[3];
+      a.vr[0] = a.vr[1]; a.vr[1] = a.vr[2]; a.vr[2] = a.vr[3];
     }
     if (more) {
 #pragma unroll
@@ -1429,7 +1477,7 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
       if (c.lane < 16) {
         sm_k[l16] = kn;
         if (a.p1 == L) {  // append the new token's K and V to the cache
-          const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
+          const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
         }
@@ -1489,6 +1537,7 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
 
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
 // request, token t == request slot t.
+template <int PATH>
 __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
   const int G = gridDim.x;
@@ -1532,9 +1581,11 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   pl.nch_max = (nb_max + bpc - 1) / bpc;
   pl.ntasks = T * pl.HKV * pl.nch_max;
   // More (request, kv head) pairs than CTAs and no sequence that needs splitting: several pairs per CTA at a time.
-  if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4 && p.x_rows >= 32) {
-    attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4);
-    return;
+  if constexpr (PATH == PATH_UMMA) {
+    if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4) {
+      attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4);
+      return;
+    }
   }
   const int l16 = c.lane & 15;
   // A half-warp serves up to four q heads of the group at once (one K/V row load feeds all of
@@ -1593,7 +1644,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       if (c.lane < 16) {
         sm_k[l16] = kn;
         if (a.p1 == L) {  // the last chunk appends the new token's K and V to the cache
-          const size_t dst = (((size_t)a.new_page * p.page_size + (L - 1) % p.page_size) * pl.HKV + a.h) * kHeadDim;
+          const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
         }
@@ -1709,43 +1760,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       if (fl[2] != 0) {  // the chunk that arrives last merges all of them
         __threadfence();
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
-        // The (max, sum) pairs of all chunks go through shared memory; the values are read in
-        // small batches: more than a few dozen loads in flight per thread slowed the merge down.
-        constexpr int kMergeBatch = 8;
-        const int nout = pl.qpk * kHeadDim;
-        float* sm_pm = sm_l + 16 + 32;                   // [chunks][qpk]
-        float* sm_pl = sm_pm + p.attn_max_chunks * 8;    // [chunks][qpk]
-#pragma unroll 1
-        for (int i = c.tid; i < a.nch * pl.qpk; i += kNumConsumers) {
-          const float* pm = base + (size_t)(i / pl.qpk) * part_stride + nout + (i % pl.qpk);
-          sm_pm[i] = __ldcg(pm);
-          sm_pl[i] = __ldcg(pm + pl.qpk);
-        }
-        consumer_sync();
-#pragma unroll 1
-        for (int e = c.tid; e < nout; e += kNumConsumers) {
-          const int eh = e >> 7;
-          float M = -INFINITY;
-#pragma unroll 1
-          for (int cc = 0; cc < a.nch; ++cc) M = fmaxf(M, sm_pm[cc * pl.qpk + eh]);
-          float Ls = 0.f, O = 0.f;
-#pragma unroll 1
-          for (int c0 = 0; c0 < a.nch; c0 += kMergeBatch) {
-            float v[kMergeBatch];
-#pragma unroll
-            for (int u = 0; u < kMergeBatch; ++u)
-              v[u] = (c0 + u < a.nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
-#pragma unroll
-            for (int u = 0; u < kMergeBatch; ++u) {
-              if (c0 + u < a.nch) {
-                const float f = exp2f(sm_pm[(c0 + u) * pl.qpk + eh] - M);
-                Ls += f * sm_pl[(c0 + u) * pl.qpk + eh];
-                O += f * v[u];
-              }
-            }
-          }
-          out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
-        }
+        attn_merge(c, base, out, a.nch, pl.qpk, part_stride, sm_l + 16 + 32);
         if (c.tid == 0) *cnt = 0u;
       }
     }
@@ -2196,6 +2211,7 @@ __device__ __noinline__ void rows_prefetch_loop(Ctx& c) {
   }
 }
 
+template <int PATH>
 __device__ __noinline__ void producer_loop(Ctx& c) {
   const KParams& p = c.p;
   const int S = p.num_stages;
@@ -2209,7 +2225,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
   TileCursor pc;
   pc.valid = false;
   int ahead = 0;
-  if (p.prefetch_tiles > 0)
+  if (PATH != PATH_ROWS && p.prefetch_tiles > 0)
     for (int oi = 0; oi < p.num_ops && !pc.valid; ++oi) pc.valid = cursor_open(p, pc, oi);
   for (int iter = 1;; ++iter) {
     // wait for the consumers to publish this iteration's token count (or the end)
@@ -2238,7 +2254,8 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     bool dead = false;
     for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
       const OpDesc& rop = p.ops[oi];
-      if (rop.type == OP_LINEAR && (rop.flags & F_ROWS)) {
+      if constexpr (PATH == PATH_ROWS) {
+        if (rop.type != OP_LINEAR) continue;
         // row-owner op: per chunk of up to 32 owned rows, the full K in 512-wide stages of
         // eight boxes; the tensor map for a chunk of R rows is the (R / 8)-th of the op's four
         int row0, row1;
@@ -2272,7 +2289,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
             }
           }
         continue;
-      }
+      } else {
       TileCursor lc;
       if (!cursor_open(p, lc, oi)) continue;
       const int passes = linear_passes(p.ops[oi], T);
@@ -2310,6 +2327,7 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           }
         }
       }
+      }  // stream-K paths
     }
     if (dead || p.mode == MODE_ONEPASS) break;
   }
@@ -2417,6 +2435,7 @@ __device__ __noinline__ void xproducer_loop(Ctx& c) {
 // ------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------
+template <int PATH>
 __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_constant__ KParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Ctx c(p);
@@ -2463,7 +2482,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   __syncthreads();
   // Tensor memory for the tcgen05 linears (32 or 64 token rows per box): x_rows columns of fp32
   // accumulators, allocated once by warp 0 and freed by it when the CTA leaves.
-  const bool use_tmem = p.x_rows >= 32;
+  constexpr bool use_tmem = PATH == PATH_UMMA;
   if (use_tmem) {
     if (c.warp == 0) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(c.tmem_slot()), "r"((uint32_t)p.x_rows) : "memory");
@@ -2477,11 +2496,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   }
 
   if (c.warp == kNumConsumerWarps) {
-    if (c.lane == 0) producer_loop(c);
+    if (c.lane == 0) producer_loop<PATH>(c);
     __syncwarp();
   } else if (c.warp == kNumConsumerWarps + 1) {
-    if (p.x_rows == 0) rows_prefetch_loop(c);
-    else if (c.lane == 0) xproducer_loop(c);
+    if constexpr (PATH == PATH_ROWS) {
+      rows_prefetch_loop(c);
+    } else {
+      if (c.lane == 0) xproducer_loop(c);
+    }
     __syncwarp();
   } else {
     for (int iter = 1;; ++iter) {
@@ -2561,9 +2583,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
         switch (op.type) {
           case OP_EMBED: if (!op_barrier(c, op)) op_embed(c, op, T); break;
           case OP_RMSNORM: op_rmsnorm(c, op, T); break;
-          case OP_LINEAR: op_linear(c, op, T); break;
+          case OP_LINEAR: op_linear<PATH>(c, op, T); break;
           case OP_ATTN:
-            op_attention(c, op, T);
+            op_attention<PATH>(c, op, T);
             break;
           case OP_SILU_MUL: if (!op_barrier(c, op)) op_silu_mul(c, op, T); break;
           case OP_ARGMAX_PARTIAL: if (!op_barrier(c, op)) op_argmax_partial(c, op, T); break;
@@ -2628,19 +2650,30 @@ __global__ void init_state_kernel(KParams p) {
 // ------------------------------------------------------------------------------------
 // host-side launch helpers (called by the runtime in mk_runtime.cpp)
 // ------------------------------------------------------------------------------------
-extern "C" int mk_kernel_max_ctas_per_sm(int smem_bytes) {
+namespace {
+const void* kernel_for_path(int path) {
+  switch (path) {
+    case mk::PATH_ROWS: return (const void*)mk::megakernel<mk::PATH_ROWS>;
+    case mk::PATH_UMMA: return (const void*)mk::megakernel<mk::PATH_UMMA>;
+    default: return (const void*)mk::megakernel<mk::PATH_TILES>;
+  }
+}
+}  // namespace
+
+extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes) {
   int n = 0;
-  if (cudaFuncSetAttribute(mk::megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mk::megakernel, mk::kNumThreads, smem_bytes) != cudaSuccess) return -1;
+  const void* k = kernel_for_path(path);
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, mk::kNumThreads, smem_bytes) != cudaSuccess) return -1;
   return n;
 }
 
 extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream) {
-  cudaError_t e = cudaFuncSetAttribute(mk::megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  const void* k = kernel_for_path(p->path);
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)p};
-  e = cudaLaunchCooperativeKernel((void*)mk::megakernel, dim3(grid), dim3(mk::kNumThreads), args, (size_t)smem_bytes,
-                                  (cudaStream_t)stream);
+  e = cudaLaunchCooperativeKernel(k, dim3(grid), dim3(mk::kNumThreads), args, (size_t)smem_bytes, (cudaStream_t)stream);
   return (int)e;
 }
 

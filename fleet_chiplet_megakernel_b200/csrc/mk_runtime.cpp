@@ -24,7 +24,7 @@
 #include "../../include/b200mk.h"
 #include "mk_types.h"
 
-extern "C" int mk_kernel_max_ctas_per_sm(int smem_bytes);
+extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes);
 extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream);
 extern "C" int mk_kernel_init_state(const mk::KParams* p, void* stream);
 
@@ -691,6 +691,7 @@ int mk_plan(mk_handle* h) {
     return h->fail(MK_E_INVALID, "max_num_batched_tokens must be >= max_num_batched_requests >= 1");
   if (c.max_num_batched_tokens > 128) return h->fail(MK_E_UNSUPPORTED, "at most 128 batched tokens");
   if (c.page_size < 1 || c.max_num_pages < 1 || c.max_seq_length < 2) return h->fail(MK_E_INVALID, "bad paging/sequence limits");
+  if (c.page_size & (c.page_size - 1)) return h->fail(MK_E_UNSUPPORTED, "page_size must be a power of two (got %d)", c.page_size);
   if (c.world_size < 1 || c.rank < 0 || c.rank >= c.world_size) return h->fail(MK_E_INVALID, "bad rank/world_size");
   return plan_graph(h);
 }
@@ -853,7 +854,8 @@ int mk_compile(mk_handle* h) {
   kp.red_off = kp.x_off + x_bytes + sums_sep;
   kp.bar_off = kp.red_off + kRedBytes;
   h->smem_bytes = kp.bar_off + 1024 + 1024;
-  const int per_sm = mk_kernel_max_ctas_per_sm(h->smem_bytes);
+  kp.path = rows_mode ? mk::PATH_ROWS : (x_rows >= 32 ? mk::PATH_UMMA : mk::PATH_TILES);
+  const int per_sm = mk_kernel_max_ctas_per_sm(kp.path, h->smem_bytes);
   if (per_sm < 1) return h->fail(MK_E_CUDA, "the megakernel does not fit on an SM with %d bytes of shared memory", h->smem_bytes);
   h->grid = h->num_sms;
   if (cfg.num_workers > 0) h->grid = std::min(h->grid, cfg.num_workers);
@@ -1055,6 +1057,8 @@ int mk_compile(mk_handle* h) {
   kp.max_tokens = cfg.max_num_batched_tokens;
   kp.max_pages = cfg.max_num_pages;
   kp.page_size = cfg.page_size;
+  kp.page_shift = 0;
+  while ((1 << kp.page_shift) < cfg.page_size) ++kp.page_shift;
   kp.total_requests = (int)h->total_requests;
   kp.eos = cfg.eos_token_id;
   kp.max_iters = cfg.max_iterations;

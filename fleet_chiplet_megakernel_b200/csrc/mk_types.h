@@ -64,6 +64,15 @@ enum Numerics : int {
 
 enum Mode : int { MODE_OFFLINE = 0, MODE_ONEPASS = 1 };
 
+// The kernel is compiled once per linear-layer path, each instance holding only the code its
+// path runs: the whole step executes out of the instruction cache once per layer, and code
+// that is merely present (other paths' loops) measurably slowed the batch-1 step down.
+enum Path : int {
+  PATH_ROWS = 0,   // 1-2 tokens: row-owner linears, resident token rows, L2 look-ahead
+  PATH_TILES = 1,  // 3-16 tokens (and graphs the row-owner path cannot take): stream-K tiles, mma.sync
+  PATH_UMMA = 2,   // 17-64 tokens: stream-K tiles, tcgen05.mma, grouped attention
+};
+
 enum Status : int {
   ST_OK = 0,
   ST_TIMEOUT_GRID = 1,
@@ -111,6 +120,7 @@ struct KParams {
   const OpDesc* ops;
   int num_ops;
   int mode;
+  int path;  // Path: which instance of the kernel the host launches
   int numerics;
   int rank, world;
   // meta tensors of the operator API (caller-owned)
@@ -125,6 +135,7 @@ struct KParams {
   int* kv_indices;
   int* kv_last_page_len;
   int max_seq_len, max_reqs, max_tokens, max_pages, page_size, total_requests;
+  int page_shift;  // log2(page_size): page sizes are powers of two
   long long eos;
   int vocab_limit;  // embedding rows, to refuse out-of-range token ids
   // runtime-owned state
