@@ -1302,22 +1302,30 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
 }
 
 // Merge of a (request, kv head)'s chunks by the CTA that arrived last: kept out of line, only a
-// handful of CTAs per layer ever run it.  `scratch`: [chunks][8] weights, then [8] sums.
+// handful of CTAs per layer ever run it.  `scratch`: [chunks][8] weights, [8] sums, [chunks][8] chunk sums.
 __device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride,
                                         float* scratch) {
   const int nout = qpk * kHeadDim;
   float* sm_w = scratch;                              // [chunks][8]: exp2(max_chunk - max) per head
   float* sm_s = scratch + c.p.attn_max_chunks * 8;    // [8]: the merged sum per head
+  // all (max, sum) pairs in one round of loads, one pair per thread; then one thread per head
+  float* sm_l2 = sm_s + 8;  // [chunks][8]: the chunks' sums
+#pragma unroll 1
+  for (int i = c.tid; i < nch * qpk; i += kNumConsumers) {
+    const int cc = i / qpk, h = i - cc * qpk;
+    const float* pm = base + (size_t)cc * part_stride + nout + h;
+    sm_w[cc * 8 + h] = __ldcg(pm);
+    sm_l2[cc * 8 + h] = __ldcg(pm + qpk);
+  }
+  consumer_sync();
   if (c.tid < qpk) {
-    // one thread per head: the chunks' (max, sum) pairs, eight loads in flight at a time
-    const float* pm = base + nout + c.tid;
     float M = -INFINITY;
-    for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, __ldcg(pm + (size_t)cc * part_stride));
+    for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, sm_w[cc * 8 + c.tid]);
     float Ls = 0.f;
     for (int cc = 0; cc < nch; ++cc) {
-      const float f = exp2f(__ldcg(pm + (size_t)cc * part_stride) - M);
+      const float f = exp2f(sm_w[cc * 8 + c.tid] - M);
       sm_w[cc * 8 + c.tid] = f;
-      Ls += f * __ldcg(pm + (size_t)cc * part_stride + qpk);
+      Ls += f * sm_l2[cc * 8 + c.tid];
     }
     sm_s[c.tid] = Ls;
   }

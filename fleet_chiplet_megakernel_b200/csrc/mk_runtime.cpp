@@ -829,7 +829,7 @@ int mk_compile(mk_handle* h) {
       x_bytes = std::max(x_bytes, ((p.n + 63) / 64 * 64 + 8) * 2 + 16);
     } else if (p.type == mk::OP_ATTN) {
       // q heads and the new k (bf16), four combine slots of 4 heads x 128 floats, (max, sum) pairs, merge scratch
-      x_bytes = std::max(x_bytes, 9 * 256 + 4 * 4 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 256);
+      x_bytes = std::max(x_bytes, 9 * 256 + 4 * 4 * (mk::kHeadDim + 2) * 4 + 2 * kAttnMaxChunks * 8 * 4 + 64 + 256);
       // above 16 tokens several (request, kv head) pairs run side by side in a CTA: q/k per group
       // (4 x 1280 B) and one combine slot per warp (8 x 4 heads x 128 floats + (max, sum) pairs)
       if (x_rows >= 32) x_bytes = std::max(x_bytes, 4 * 1280 + 8 * 4 * mk::kHeadDim * 4 + 8 * 4 * 2 * 4);
