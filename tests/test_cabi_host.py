@@ -132,6 +132,26 @@ def test_error_behaviour_follows_the_reference_api(native_lib):
     k.finalize()
 
 
+def test_lowering_picks_the_path_by_batch(native_lib):
+    """One or two batched tokens fold the norms into the linears (row-owner path); more keep
+    the rmsnorm tasks (activation boxes); page sizes must be powers of two."""
+    for R, fused in ((1, 5), (2, 5), (3, 0), (16, 0)):
+        k = _kernel(fuse=True, R=R, pages=R * 4)
+        keep = _tiny_graph(k, layers=2)
+        plan = k.plan().strip().splitlines()
+        assert sum("rmsnorm fused" in ln for ln in plan) == fused, (R, plan)
+        assert sum(ln.split()[1] == "rmsnorm" for ln in plan) == 5 - fused
+        assert sum("silu_mul fused" in ln for ln in plan) == 2
+        k.finalize()
+        del keep
+    k = _kernel(page=24, pages=8)
+    keep = _tiny_graph(k, layers=1)
+    with pytest.raises(NotImplementedError, match="power of two"):
+        k.plan()
+    k.finalize()
+    del keep
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
 def test_compile_without_a_gpu_fails_loudly(native_lib):
     k = _kernel()
