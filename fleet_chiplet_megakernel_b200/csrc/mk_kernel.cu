@@ -61,6 +61,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// The same with an L2 eviction policy (from createpolicy) attached to the lines it reads.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tmap, uint32_t bar, int x, int y, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "l"(pol)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
 }
@@ -73,6 +80,16 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// barrier counter and abort flag (adjacent words) in one load
+__device__ __forceinline__ uint2 ld_bar_pair(const unsigned* p) {
+  uint2 v;
+#ifdef MK_BAR_RELAXED
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+#else
+  asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+#endif
   return v;
 }
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
@@ -200,20 +217,30 @@ __device__ __forceinline__ void grid_wait(Ctx& c) {
     const unsigned target = c.epoch * gridDim.x;
     unsigned long long t0 = 0;
     unsigned spins = 0;
-    while (ld_acquire_u32(c.p.grid_bar) < target) {
+    // the abort flag is the word behind the counter: one 8-byte load polls both
+    bool dead = false;
+    while (true) {
+      const uint2 v = ld_bar_pair(c.p.grid_bar);
+      if (v.y != 0u) {
+        dead = true;
+        break;
+      }
+      if (v.x >= target) break;
       if (((++spins) & 1023u) == 0) {
-        if (aborted(c)) break;
         const unsigned long long now = globaltimer();
         if (t0 == 0) {
           t0 = now;
         } else if (now - t0 > 2 * c.p.timeout_ns) {
           raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+          dead = true;
           break;
         }
       }
     }
+#ifdef MK_BAR_RELAXED
     __threadfence();
-    c.flags()[3] = aborted(c) ? 1 : 0;
+#endif
+    c.flags()[3] = dead ? 1 : 0;
   }
   consumer_sync();
 }
@@ -1047,6 +1074,9 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     for (int ks = 0; ks < nks; ++ks) {
       if (ks == 0 && ci == 0) MK_STAMP(c, 2);
       mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+#ifdef MK_STAGE_STAMPS
+      if (c.dbg != nullptr && c.tid == 0 && consumed < 11) c.dbg[5 + consumed] = globaltimer();
+#endif
       if (arith) {
         const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes;
         const uint32_t xa = a_row + (a_real ? (uint32_t)(ks * kRowsStageK * 2) : 0u);
@@ -1421,6 +1451,64 @@ __device__ __forceinline__ void attn_rows(const Ctx& c, const OpDesc& op, const 
   }
 }
 
+// The same pass for ONE q head per half-warp (the single-chunk-per-CTA path): running
+// (max, sum, output) of the half-warp's positions of the task.
+__device__ __forceinline__ void attn_rows1(const Ctx& c, const OpDesc& op, const AttnPlan& pl, AttnTask& a, int l16,
+                                           uint4 qv, uint4 knew, uint4 vnew, float sc, float& m, float& l, float* o) {
+  const int L = a.L;
+  m = -INFINITY;
+  l = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = 0.f;
+  float qf[8];
+  unpack8(qv, qf);
+  const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
+#pragma unroll 1
+  for (int it = 0; it < niter; it += 4) {
+    uint4 nk[4], nv[4];  // the next four rows are requested before this batch is used
+    const bool more = it + 4 < niter;
+    if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
+#pragma unroll 1
+    for (int u = 0; u < 4; ++u) {
+      const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
+      const bool ok = j < a.p1;  // may differ between the two halves of a warp: no shuffle may depend on it
+      if (__any_sync(0xffffffffu, ok)) {
+        uint4 kr = a.kr[0], vr = a.vr[0];
+        if (ok && j == L - 1) {
+          kr = knew;
+          vr = vnew;
+        }
+        float kk[8], vf[8];
+        unpack8(kr, kk);
+        unpack8(vr, vf);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
+#pragma unroll
+        for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+        if (ok) {
+          const float sv = d * sc;
+          const float mn = fmaxf(m, sv);
+          const float alpha = exp2f(m - mn), pr = exp2f(sv - mn);
+          l = l * alpha + pr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i] * alpha);
+          m = mn;
+        }
+      }
+      a.kr[0] = a.kr[1]; a.kr[1] = a.kr[2]; a.kr[2] = a.kr[3];
+      a.vr[0] = a.vr[1]; a.vr[1] = a.vr[2]; a.vr[2] = a.vr[3];
+    }
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a.kr[u] = nk[u];
+        a.vr[u] = nv[u];
+      }
+    }
+  }
+}
+
 // Larger batches: with more (request, kv head) pairs than CTAs and sequences short enough to
 // need no split, a CTA runs 2 or 4 pairs side by side instead of one after the other: its 8
 // warps form groups of 4 or 2, every group is a small copy of the CTA-wide scheme (its warps
@@ -1585,6 +1673,8 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   int bpc = (T * pl.HKV * nb_max + G - 1) / G;  // 16-position blocks per chunk: one round of tasks
   bpc = max(bpc, (nb_max + p.attn_max_chunks - 1) / p.attn_max_chunks);
   bpc = max(bpc, 1);
+  // one round of tasks: a chunk count that leaves a few CTAs a second task doubles the op's time
+  while (T * pl.HKV <= G && T * pl.HKV * ((nb_max + bpc - 1) / bpc) > G) ++bpc;
   pl.CS = bpc * 16;
   pl.nch_max = (nb_max + bpc - 1) / bpc;
   pl.ntasks = T * pl.HKV * pl.nch_max;
@@ -1596,19 +1686,20 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     }
   }
   const int l16 = c.lane & 15;
-  // A half-warp serves up to four q heads of the group at once (one K/V row load feeds all of
-  // them); with eight q heads per kv head the warps alternate between the two head quads.
-  const int hq = min(pl.qpk, 4);
-  const int nquads = pl.qpk / hq;
-  const int quad = c.warp % nquads;
-  pl.ngroups = 2 * (kNumConsumerWarps / nquads);
-  pl.gi = 2 * (c.warp / nquads) + (c.lane >> 4);
+  // Half-warp hw serves q head (hw % qpk) of the kv-head group for the positions of group
+  // (hw / qpk): one head per thread keeps the row loop and the combine small (this code runs
+  // once per layer out of a cold instruction cache), and the two halves of a warp read the
+  // same K/V rows, so their loads share a request.
+  const int hw = 2 * c.warp + (c.lane >> 4);
+  const int head = hw % pl.qpk;
+  pl.ngroups = 16 / pl.qpk;
+  pl.gi = hw / pl.qpk;
   const int part_stride = pl.qpk * (kHeadDim + 2);
   const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
   uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off);     // [8 heads][16 lanes]: q after norm and RoPE
   uint4* sm_k = sm_q + 8 * 16;                                  // [16 lanes]: the new k
-  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [4 slots][4 heads][128]
-  float* sm_m = sm_o + 4 * 4 * kHeadDim;                        // [4 slots][4 heads]
+  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [16 half-warps][128]
+  float* sm_m = sm_o + 16 * kHeadDim;                           // [16 half-warps]
   float* sm_l = sm_m + 16;
   const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
   const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
@@ -1659,89 +1750,42 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     consumer_sync();
-    uint4 qv[4];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) qv[h] = (h < hq) ? sm_q[(quad * 4 + h) * 16 + l16] : make_uint4(0, 0, 0, 0);
+    const uint4 qv = sm_q[head * 16 + l16];
     const uint4 knew = sm_k[l16];
     MK_STAMP(c, 2);
-    float m[4], l[4], o[4][8];
-    attn_rows(c, op, pl, a, l16, hq, qv, knew, vnew, sc, m, l, o);
+    float m, l, o[8];
+    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o);
     MK_STAMP(c, 3);
-    // combine the position groups: the two halves of a warp by shuffle, warps 4-7 into warps
-    // 0-3 through shared memory, then every output element over the remaining four slots
-    const int slot = c.warp & 3;
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      if (h < hq) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m[h], 16), l2 = __shfl_xor_sync(0xffffffffu, l[h], 16);
-        const float M = fmaxf(m[h], m2);
-        const float f1 = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M), f2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - M);
-        l[h] = f1 * l[h] + f2 * l2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[h][i] = f1 * o[h][i] + f2 * __shfl_xor_sync(0xffffffffu, o[h][i], 16);
-        m[h] = M;
-        if (c.warp >= 4 && c.lane < 16) {
-          float* dst = sm_o + (slot * 4 + h) * kHeadDim + l16 * 8;
-          reinterpret_cast<float4*>(dst)[0] = make_float4(o[h][0], o[h][1], o[h][2], o[h][3]);
-          reinterpret_cast<float4*>(dst)[1] = make_float4(o[h][4], o[h][5], o[h][6], o[h][7]);
-          if (l16 == 0) {
-            sm_m[slot * 4 + h] = M;
-            sm_l[slot * 4 + h] = l[h];
-          }
-        }
-      }
-    }
-    consumer_sync();
-    if (c.warp < 4 && c.lane < 16) {
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        if (h < hq) {
-          const float m2 = sm_m[slot * 4 + h], l2 = sm_l[slot * 4 + h];
-          const float M = fmaxf(m[h], m2);
-          const float f1 = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M), f2 = (m2 == -INFINITY) ? 0.f : exp2f(m2 - M);
-          float* buf = sm_o + (slot * 4 + h) * kHeadDim + l16 * 8;  // read the partner's values, leave the sum
-          const float4 s0 = reinterpret_cast<const float4*>(buf)[0], s1 = reinterpret_cast<const float4*>(buf)[1];
-          reinterpret_cast<float4*>(buf)[0] = make_float4(f1 * o[h][0] + f2 * s0.x, f1 * o[h][1] + f2 * s0.y,
-                                                          f1 * o[h][2] + f2 * s0.z, f1 * o[h][3] + f2 * s0.w);
-          reinterpret_cast<float4*>(buf)[1] = make_float4(f1 * o[h][4] + f2 * s1.x, f1 * o[h][5] + f2 * s1.y,
-                                                          f1 * o[h][6] + f2 * s1.z, f1 * o[h][7] + f2 * s1.w);
-          if (l16 == 0) {
-            sm_m[slot * 4 + h] = M;
-            sm_l[slot * 4 + h] = f1 * l[h] + f2 * l2;
-          }
-        }
+    // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
+    // elements then combines the position groups of each head
+    {
+      float* dst = sm_o + hw * kHeadDim + l16 * 8;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (l16 == 0) {
+        sm_m[hw] = m;
+        sm_l[hw] = l;
       }
     }
     consumer_sync();
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
-    // per head: the overall max and sum, and each slot's weight, computed once by one thread
-    float* sm_f = sm_l + 16;   // [4 slots][4 heads] weights
-    float* sm_M = sm_f + 16;   // [8 heads] max, then [8 heads] sum
-    if (c.tid < pl.qpk) {
-      const int qd = c.tid / hq, h = c.tid % hq;  // slots w with w % nquads == qd hold this head
-      float M = -INFINITY;
-      for (int w = qd; w < 4; w += nquads) M = fmaxf(M, sm_m[w * 4 + h]);
-      float Ls = 0.f;
-      for (int w = qd; w < 4; w += nquads) {
-        const float mw = sm_m[w * 4 + h];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        sm_f[w * 4 + h] = f;
-        Ls += f * sm_l[w * 4 + h];
-      }
-      sm_M[c.tid] = M;
-      sm_M[8 + c.tid] = Ls;
-    }
-    consumer_sync();
 #pragma unroll 1
     for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
       const int eh = e >> 7, d = e & 127;
-      const int qd = eh / hq, h = eh % hq;
-      const float M = sm_M[eh], Ls = sm_M[8 + eh];
-      float O = 0.f;
+      float M = -INFINITY;
 #pragma unroll 1
-      for (int w = qd; w < 4; w += nquads) O += sm_f[w * 4 + h] * sm_o[(w * 4 + h) * kHeadDim + d];
+      for (int g = 0; g < pl.ngroups; ++g) M = fmaxf(M, sm_m[g * pl.qpk + eh]);
+      float Ls = 0.f, O = 0.f;
+#pragma unroll 1
+      for (int g = 0; g < pl.ngroups; ++g) {
+        const int w = g * pl.qpk + eh;
+        const float mw = sm_m[w];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += f * sm_l[w];
+        O += f * sm_o[w * kHeadDim + d];
+      }
       if (a.nch == 1) {
         out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
       } else {
@@ -2235,6 +2279,10 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
   int ahead = 0;
   if (PATH != PATH_ROWS && p.prefetch_tiles > 0)
     for (int oi = 0; oi < p.num_ops && !pc.valid; ++oi) pc.valid = cursor_open(p, pc, oi);
+  // Weights are read once per step: their lines are marked evict-first on the way through L2, so
+  // that what the look-ahead has fetched (and the KV cache) is not pushed out by bytes already used.
+  uint64_t pol_stream;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_stream));
   for (int iter = 1;; ++iter) {
     // wait for the consumers to publish this iteration's token count (or the end)
     int go;
@@ -2287,7 +2335,8 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
               const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
               mbar_arrive_expect_tx(full, 8u * box_bytes);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) tma_load_2d(dst + (uint32_t)j * box_bytes, tmap, full, ks * kRowsStageK + j * kBoxK, r0);
+              for (int j = 0; j < 8; ++j)
+                tma_load_2d_hint(dst + (uint32_t)j * box_bytes, tmap, full, ks * kRowsStageK + j * kBoxK, r0, pol_stream);
               issued += 1;
               fl[1] = (int)issued;
               if (++s == S) {

@@ -897,7 +897,7 @@ int mk_compile(mk_handle* h) {
   kp.sched = (int*)p;
   kp.grid_bar = (unsigned*)p + 16;
   kp.ctrl = (int*)p + 20;
-  kp.abort_flag = (int*)p + 24;
+  kp.abort_flag = (int*)p + 17;  // beside the barrier counter: one 8-byte load polls both
   kp.status = (int*)p + 32;
   if (int e = h->dmalloc(&p, (size_t)kMaxStepTimes * 16)) return e;
   kp.step_times = (unsigned long long*)p;
@@ -1072,10 +1072,10 @@ int mk_compile(mk_handle* h) {
   }
   kp.trace_op = -1;
   kp.debug_flags = cfg.debug_flags;
-  // L2 look-ahead of the weight stream, in 32 KB stages: on by default (256 KB per CTA, the
-  // measured optimum) for the row-owner path, off elsewhere (it measured slower there);
+  // L2 look-ahead of the weight stream, in 32 KB stages: on by default (512 KB per CTA, the
+  // measured optimum with evict-first weight loads) for the row-owner path, off elsewhere (it measured slower there);
   // prefetch_kb > 0 sets it, < 0 turns it off
-  const int pf_kb = cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 256 : 0);
+  const int pf_kb = cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 512 : 0);
   kp.prefetch_tiles = pf_kb > 0 ? std::max(1, pf_kb * 1024 / mk::kStageBytes) : 0;
   if (h->prof_ptr) {
     const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;
@@ -1119,14 +1119,14 @@ int mk_wait(mk_handle* h, void* stream) {
   if (!h->launched) return h->fail(MK_E_STATE, "nothing launched");
   cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "megakernel");
-  int st[16];
-  ce = cudaMemcpy(st, h->kp.abort_flag, sizeof(int) * 16, cudaMemcpyDeviceToHost);
+  int st[24];
+  ce = cudaMemcpy(st, h->kp.abort_flag, sizeof(int) * 24, cudaMemcpyDeviceToHost);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "status readback");
   if (st[0] != 0) {
     static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
                                   "producer never got the next iteration", "peer never arrived", "token id out of range",
                                   "out of KV pages", "a peer rank never delivered its allreduce share"};
-    const int* s = st + 8;
+    const int* s = st + 15;  // status sits 15 words behind the abort flag
     const int code = s[0];
     return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
                    (code >= 0 && code < 9) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
