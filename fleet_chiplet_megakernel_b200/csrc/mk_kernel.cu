@@ -992,8 +992,8 @@ __device__ __noinline__ void linear_pass_umma(Ctx& c, const OpDesc& op, int tok0
 // instead: a contiguous range of 8-row units, walked in chunks of up to 32 rows over the
 // full K.  The token rows are resident in shared memory (stage_x, fused norm included).
 // Inside a chunk the 8 warps split k: warp w multiplies the w-th 64-wide k slice of every
-// 512-wide stage, tokens on the M side of the mma and 8 weight rows on the N side, and the
-// eight partial sums of an output meet in shared memory when the chunk ends.
+// 512-wide stage, 16 weight rows on the M side of the mma and the tokens on the N side, and
+// the eight partial sums of an output meet in shared memory when the chunk ends.
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ void rows_range(const OpDesc& op, int& row0, int& row1, bool& any) {
   const unsigned U = (unsigned)(op.n + kUnitRows - 1) / kUnitRows;
@@ -1032,16 +1032,19 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int S = p.num_stages;
   const int lane = c.lane, warp = c.warp;
   const bool arith = !(p.debug_flags & 1);
-  // A operand (tokens x k): lane l addresses token (l & 7), 16-byte chunk (l >> 3) of a 32-wide k step
+  // B operand (k x tokens): lane l addresses token (l & 7), 16-byte chunk (l >> 3) of a 32-wide k step
   const int pitch_b = (kp + 8) * 2;
   const uint32_t xs0 = c.smem_addr + p.x_off;
   const bool a_real = (lane & 7) < ntok;
   const uint32_t a_row = a_real ? xs0 + (uint32_t)((lane & 7) * pitch_b + (lane >> 3) * 16 + warp * 128)
                                 : xs0 + (uint32_t)(ntok * pitch_b);  // the zero chunk
-  // B operand (8 weight rows x k): lane l addresses row (l & 7), chunk 4*h + (l >> 3) of the warp's box
-  const uint32_t b_row = (uint32_t)((lane & 7) * 128);
-  const uint32_t b_xor = (uint32_t)(lane & 7);
-  const uint32_t b_hi = (uint32_t)(lane >> 3);
+  // Weights sit on the M side of the mma (16 rows per tile, so a 32-row chunk is two tiles of
+  // four k steps: half the instructions of 8-row tiles on the N side) and the tokens on the N
+  // side.  Lane l addresses row (l & 15) of a tile and the 16-byte chunk 2 * step + (l >> 4)
+  // of the warp's 128-byte-swizzled box.
+  const uint32_t w_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * 128);
+  const uint32_t w_xor = (uint32_t)(lane & 7);
+  const uint32_t w_hi = (uint32_t)(lane >> 4);
   const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
   const int TP = p.sums_stride;  // token slots of the sums block: [warp][32 rows][TP]
   float* sums = c.sums();
@@ -1061,12 +1064,12 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   for (int ci = 0; ci < nch; ++ci) {
     const int r0 = rows_chunk_begin(row0, row1, nch, ci);
     const int R = rows_chunk_begin(row0, row1, nch, ci + 1) - r0;
-    const int ntile = R >> 3;
+    const int ntile = (R + 15) >> 4;  // a ragged last tile reads 8 rows of bytes behind the box: ignored rows
     // the residual of this thread's output is requested a whole chunk ahead of its use
     float res0 = 0.f;
     const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
     if (with_res && e_live) res0 = __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
-    float acc[4][4];
+    float acc[4][4];  // [2 * tile + (k step & 1)]: two chains per tile, added up at the end
 #pragma unroll
     for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
     const uint32_t box_bytes = (uint32_t)R * 128u;
@@ -1074,24 +1077,20 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     for (int ks = 0; ks < nks; ++ks) {
       if (ks == 0 && ci == 0) MK_STAMP(c, 2);
       mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
-#ifdef MK_STAGE_STAMPS
-      if (c.dbg != nullptr && c.tid == 0 && consumed < 11) c.dbg[5 + consumed] = globaltimer();
-#endif
       if (arith) {
-        const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes;
+        const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes + w_off;
         const uint32_t xa = a_row + (a_real ? (uint32_t)(ks * kRowsStageK * 2) : 0u);
-        uint32_t a[2][4];  // a[h]: k chunks 4h .. 4h+3 of tokens 0..7 (rows 8..15 of the mma are zero)
-        ldmatrix_x4(xa, a[0][0], a[0][1], a[0][2], a[0][3]);
-        ldmatrix_x4(xa + (a_real ? 64u : 0u), a[1][0], a[1][1], a[1][2], a[1][3]);
+        uint32_t x[2][4];  // x[h]: k chunks 4h .. 4h+3 of tokens 0..7: the B fragments of k steps 2h and 2h+1
+        ldmatrix_x4(xa, x[0][0], x[0][1], x[0][2], x[0][3]);
+        ldmatrix_x4(xa + (a_real ? 64u : 0u), x[1][0], x[1][1], x[1][2], x[1][3]);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
+        for (int t = 0; t < 2; ++t) {
           if (t < ntile) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t b0, b1, b2, b3;
-              ldmatrix_x4(wb + (uint32_t)t * 1024u + b_row + ((((uint32_t)(4 * h) + b_hi) ^ b_xor) << 4), b0, b1, b2, b3);
-              mma_bf16(acc[t], a[h][0], 0u, a[h][1], 0u, b0, b1);
-              mma_bf16(acc[t], a[h][2], 0u, a[h][3], 0u, b2, b3);
+            for (int st = 0; st < 4; ++st) {
+              uint32_t w0, w1, w2, w3;
+              ldmatrix_x4(wb + (uint32_t)t * 2048u + ((((uint32_t)(2 * st) + w_hi) ^ w_xor) << 4), w0, w1, w2, w3);
+              mma_bf16(acc[2 * t + (st & 1)], w0, w1, w2, w3, x[st >> 1][2 * (st & 1)], x[st >> 1][2 * (st & 1) + 1]);
             }
           }
         }
@@ -1105,15 +1104,19 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
       }
     }
     if (ci == nch - 1) MK_STAMP(c, 3);
-    // the chunk's partial sums of this warp: token lane >> 2, rows 8t + 2 * (lane & 3) + {0, 1}
+    // the chunk's partial sums of this warp: rows 16t + (lane >> 2) and + 8, tokens 2 * (lane & 3) + {0, 1}
     {
-      const int tk = lane >> 2;
+      const int tk = 2 * (lane & 3);
       if (tk < TP) {
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float* d = sums + ((warp * kChunkRows + 8 * t + 2 * (lane & 3)) * TP + tk);
-          d[0] = acc[t][0];
-          d[TP] = acc[t][1];
+        for (int t = 0; t < 2; ++t) {
+          float* d = sums + ((warp * kChunkRows + 16 * t + (lane >> 2)) * TP + tk);
+          d[0] = acc[2 * t][0] + acc[2 * t + 1][0];
+          d[8 * TP] = acc[2 * t][2] + acc[2 * t + 1][2];
+          if (tk + 1 < TP) {
+            d[1] = acc[2 * t][1] + acc[2 * t + 1][1];
+            d[8 * TP + 1] = acc[2 * t][3] + acc[2 * t + 1][3];
+          }
         }
       }
     }
@@ -1332,50 +1335,42 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
 }
 
 // Merge of a (request, kv head)'s chunks by the CTA that arrived last: kept out of line, only a
-// handful of CTAs per layer ever run it.  `scratch`: [chunks][8] weights, [8] sums, [chunks][8] chunk sums.
-__device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride,
-                                        float* scratch) {
+// handful of CTAs per layer ever run it.  One round of loads: every thread fetches, for its
+// output elements, the chunks' values together with their (max, sum) pairs and rescales as it
+// goes, eight chunks at a time (more loads in flight per thread measured slower).
+__device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride) {
   const int nout = qpk * kHeadDim;
-  float* sm_w = scratch;                              // [chunks][8]: exp2(max_chunk - max) per head
-  float* sm_s = scratch + c.p.attn_max_chunks * 8;    // [8]: the merged sum per head
-  // all (max, sum) pairs in one round of loads, one pair per thread; then one thread per head
-  float* sm_l2 = sm_s + 8;  // [chunks][8]: the chunks' sums
-#pragma unroll 1
-  for (int i = c.tid; i < nch * qpk; i += kNumConsumers) {
-    const int cc = i / qpk, h = i - cc * qpk;
-    const float* pm = base + (size_t)cc * part_stride + nout + h;
-    sm_w[cc * 8 + h] = __ldcg(pm);
-    sm_l2[cc * 8 + h] = __ldcg(pm + qpk);
-  }
-  consumer_sync();
-  if (c.tid < qpk) {
-    float M = -INFINITY;
-    for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, sm_w[cc * 8 + c.tid]);
-    float Ls = 0.f;
-    for (int cc = 0; cc < nch; ++cc) {
-      const float f = exp2f(sm_w[cc * 8 + c.tid] - M);
-      sm_w[cc * 8 + c.tid] = f;
-      Ls += f * sm_l2[cc * 8 + c.tid];
-    }
-    sm_s[c.tid] = Ls;
-  }
-  consumer_sync();
-  // more than a few dozen loads in flight per thread slowed the merge down: batches of eight
   constexpr int kMergeBatch = 8;
 #pragma unroll 1
   for (int e = c.tid; e < nout; e += kNumConsumers) {
-    const int eh = e >> 7;
-    float O = 0.f;
+    const float* pm = base + nout + (e >> 7);
+    float M = -INFINITY, Ls = 0.f, O = 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < nch; c0 += kMergeBatch) {
-      float v[kMergeBatch];
+      float v[kMergeBatch], mm[kMergeBatch], ll[kMergeBatch];
 #pragma unroll
-      for (int u = 0; u < kMergeBatch; ++u) v[u] = (c0 + u < nch) ? __ldcg(base + (size_t)(c0 + u) * part_stride + e) : 0.f;
+      for (int u = 0; u < kMergeBatch; ++u) {
+        const bool ok = c0 + u < nch;
+        const size_t off = (size_t)(c0 + u) * part_stride;
+        v[u] = ok ? __ldcg(base + off + e) : 0.f;
+        mm[u] = ok ? __ldcg(pm + off) : -INFINITY;
+        ll[u] = ok ? __ldcg(pm + off + qpk) : 0.f;
+      }
+      float Mb = M;
 #pragma unroll
-      for (int u = 0; u < kMergeBatch; ++u)
-        if (c0 + u < nch) O += sm_w[(c0 + u) * 8 + eh] * v[u];
+      for (int u = 0; u < kMergeBatch; ++u) Mb = fmaxf(Mb, mm[u]);
+      const float r = exp2f(M - Mb);  // 0 for the first batch (every chunk holds at least one position)
+      O *= r;
+      Ls *= r;
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u) {
+        const float f = exp2f(mm[u] - Mb);
+        O = fmaf(f, v[u], O);
+        Ls = fmaf(f, ll[u], Ls);
+      }
+      M = Mb;
     }
-    out[e] = __float2bfloat16_rn(__fdividef(O, sm_s[eh]));
+    out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
   }
 }
 
@@ -1798,21 +1793,20 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     }
     MK_STAMP(c, 4);
     if (a.nch > 1) {
-      __threadfence();
-      consumer_sync();
+      consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
       MK_STAMP(c, 5);
       volatile int* fl = c.flags();
       unsigned* cnt = p.attn_count + (size_t)a.t * pl.HKV + a.h;
       if (c.tid == 0) {
-        const unsigned old = atomicAdd(cnt, 1u);
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
         fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
       }
       consumer_sync();
       MK_STAMP(c, 6);
       if (fl[2] != 0) {  // the chunk that arrives last merges all of them
-        __threadfence();
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
-        attn_merge(c, base, out, a.nch, pl.qpk, part_stride, sm_l + 16 + 32);
+        attn_merge(c, base, out, a.nch, pl.qpk, part_stride);
         if (c.tid == 0) *cnt = 0u;
       }
     }
