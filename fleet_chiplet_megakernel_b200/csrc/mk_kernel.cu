@@ -153,6 +153,19 @@ struct Ctx {
   } while (0)
 #endif
 
+#ifdef MK_CLK_STAMPS
+#define MK_CLK(c, k)                                                                  \
+  do {                                                                               \
+    if ((c).dbg != nullptr && (c).tid == 0) {                                         \
+      long long t_;                                                                  \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_)::"memory");                   \
+      (c).dbg[k] = (unsigned long long)t_;                                           \
+    }                                                                                \
+  } while (0)
+#else
+#define MK_CLK(c, k) do {} while (0)
+#endif
+
 __device__ __noinline__ void raise_abort(const Ctx& c, int code, int d0, int d1) {
   if (atomicCAS(c.p.abort_flag, 0, 1) == 0) {
     c.p.status[0] = code;
@@ -1717,6 +1730,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         return;
       }
     }
+    MK_CLK(c, 8);
     if (task >= pl.ntasks) break;
     if (!a.valid) continue;
     const int L = a.L;
@@ -1729,6 +1743,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
       q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
       if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
+      MK_CLK(c, 9);
     }
     if (c.warp == kw) {
       F8 kf;
@@ -1747,9 +1762,11 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     consumer_sync();
     const uint4 qv = sm_q[head * 16 + l16];
     const uint4 knew = sm_k[l16];
+    MK_CLK(c, 10);
     MK_STAMP(c, 2);
     float m, l, o[8];
     attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o);
+    MK_CLK(c, 11);
     MK_STAMP(c, 3);
     // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
     // elements then combines the position groups of each head
@@ -1763,6 +1780,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     consumer_sync();
+    MK_CLK(c, 12);
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
@@ -1791,6 +1809,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         }
       }
     }
+    MK_CLK(c, 13);
     MK_STAMP(c, 4);
     if (a.nch > 1) {
       consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
@@ -1803,6 +1822,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
       }
       consumer_sync();
+      MK_CLK(c, 14);
       MK_STAMP(c, 6);
       if (fl[2] != 0) {  // the chunk that arrives last merges all of them
         const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
@@ -1811,6 +1831,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     consumer_sync();
+    MK_CLK(c, 15);
     MK_STAMP(c, 7);
   }
 }
@@ -2364,8 +2385,8 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           const uint32_t full = bar_full0 + 8 * s;
           const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
           mbar_arrive_expect_tx(full, kStageBytes);
-          tma_load_2d(dst, lc.tmap, full, lc.kt * kTileK, lc.blk * kTileRows);
-          tma_load_2d(dst + kSubBytes, lc.tmap, full, lc.kt * kTileK + kBoxK, lc.blk * kTileRows);
+          tma_load_2d_hint(dst, lc.tmap, full, lc.kt * kTileK, lc.blk * kTileRows, pol_stream);
+          tma_load_2d_hint(dst + kSubBytes, lc.tmap, full, lc.kt * kTileK + kBoxK, lc.blk * kTileRows, pol_stream);
           issued += 1;
           fl[1] = (int)issued;
           if (++s == S) {
