@@ -1295,9 +1295,11 @@ struct AttnPlan {
 // rows of positions p0 + (it0 + u) * ngroups + gi, u = 0..3
 // `pgc`: this half-warp's four cached page numbers (the metadata of an iteration is the same
 // for all layers, so only the first attention op of an iteration looks them up: `fill`).
+// `pgs`: when not null, the page numbers of page slots (a.p0 >> page_shift) + 0..15 of the request,
+// cached in shared memory (the row loop would otherwise wait for a page look-up before every load).
 __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a,
                                                 int it0, int l16, uint4* kr, uint4* vr, int* pgc = nullptr,
-                                                bool fill = false) {
+                                                bool fill = false, const int* pgs = nullptr) {
   const int psh = c.p.page_shift, pmask = c.p.page_size - 1;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
@@ -1306,8 +1308,11 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
     vr[u] = make_uint4(0, 0, 0, 0);
     if (j < a.p1 && j != a.L - 1) {
       int pg;
+      const int slot = (j >> psh) - (a.p0 >> psh);
       if (pgc != nullptr && !fill) {
         pg = pgc[u];
+      } else if (pgs != nullptr && slot < 16) {
+        pg = pgs[slot];
       } else {
         pg = __ldcg(c.p.kv_indices + a.kv_base + (j >> psh));
         if (pgc != nullptr) pgc[u] = pg;  // all 16 lanes store the same number
@@ -1460,9 +1465,13 @@ __device__ __forceinline__ void attn_rows(const Ctx& c, const OpDesc& op, const 
 }
 
 // The same pass for ONE q head per half-warp (the single-chunk-per-CTA path): running
-// (max, sum, output) of the half-warp's positions of the task.
+// (max, sum, output) of the half-warp's positions of the task.  Four rows are handled as one
+// batch: their dot products and the four shuffle trees run side by side, and the running
+// maximum is updated once per batch, so the dependent chain of a batch is about as long as
+// that of a single row.  `pgs`: see attn_fetch_rows.
 __device__ __forceinline__ void attn_rows1(const Ctx& c, const OpDesc& op, const AttnPlan& pl, AttnTask& a, int l16,
-                                           uint4 qv, uint4 knew, uint4 vnew, float sc, float& m, float& l, float* o) {
+                                           uint4 qv, uint4 knew, uint4 vnew, float sc, float& m, float& l, float* o,
+                                           const int* pgs) {
   const int L = a.L;
   m = -INFINITY;
   l = 0.f;
@@ -1475,37 +1484,51 @@ __device__ __forceinline__ void attn_rows1(const Ctx& c, const OpDesc& op, const
   for (int it = 0; it < niter; it += 4) {
     uint4 nk[4], nv[4];  // the next four rows are requested before this batch is used
     const bool more = it + 4 < niter;
-    if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv);
-#pragma unroll 1
+    if (more) attn_fetch_rows(c, op, pl, a, it + 4, l16, nk, nv, nullptr, false, pgs);
+    float sv[4];
+    bool ok[4];
+#pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int j = a.p0 + (it + u) * pl.ngroups + pl.gi;
-      const bool ok = j < a.p1;  // may differ between the two halves of a warp: no shuffle may depend on it
-      if (__any_sync(0xffffffffu, ok)) {
-        uint4 kr = a.kr[0], vr = a.vr[0];
-        if (ok && j == L - 1) {
-          kr = knew;
-          vr = vnew;
-        }
-        float kk[8], vf[8];
-        unpack8(kr, kk);
-        unpack8(vr, vf);
-        float d = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
-#pragma unroll
-        for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-        if (ok) {
-          const float sv = d * sc;
-          const float mn = fmaxf(m, sv);
-          const float alpha = exp2f(m - mn), pr = exp2f(sv - mn);
-          l = l * alpha + pr;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i] * alpha);
-          m = mn;
-        }
+      ok[u] = j < a.p1;  // may differ between the two halves of a warp: the shuffles below do not depend on it
+      if (ok[u] && j == L - 1) {
+        a.kr[u] = knew;
+        a.vr[u] = vnew;
       }
-      a.kr[0] = a.kr[1]; a.kr[1] = a.kr[2]; a.kr[2] = a.kr[3];
-      a.vr[0] = a.vr[1]; a.vr[1] = a.vr[2]; a.vr[2] = a.vr[3];
+      float kk[8];
+      unpack8(a.kr[u], kk);
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kk[i], d);
+      sv[u] = d;
+    }
+#pragma unroll
+    for (int x = 8; x > 0; x >>= 1) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sv[u] += __shfl_xor_sync(0xffffffffu, sv[u], x);
+    }
+    float mn = m;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      sv[u] = ok[u] ? sv[u] * sc : -INFINITY;
+      mn = fmaxf(mn, sv[u]);
+    }
+    if (mn != -INFINITY) {  // (a batch without a position of this half-warp leaves everything as it is)
+      const float alpha = exp2f(m - mn);
+      float pr[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) pr[u] = exp2f(sv[u] - mn);
+      l = l * alpha + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] *= alpha;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float vf[8];
+        unpack8(a.vr[u], vf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = fmaf(pr[u], vf[i], o[i]);
+      }
+      m = mn;
     }
     if (more) {
 #pragma unroll
@@ -1513,6 +1536,30 @@ __device__ __forceinline__ void attn_rows1(const Ctx& c, const OpDesc& op, const
         a.kr[u] = nk[u];
         a.vr[u] = nv[u];
       }
+    }
+  }
+}
+
+// Rows of the task beyond the first four per half-warp (those are loaded into registers) are
+// requested into L2 ahead of the op's barrier, one row per lane, so that the row loop's own
+// loads find them there.
+__device__ __forceinline__ void attn_l2_ahead(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a, int l16,
+                                              const int* pgs) {
+  const int psh = c.p.page_shift, pmask = c.p.page_size - 1;
+  const int niter = (a.p1 - a.p0 + pl.ngroups - 1) / pl.ngroups;
+#pragma unroll 1
+  for (int r = 4 + l16; r < niter; r += 16) {
+    const int j = a.p0 + r * pl.ngroups + pl.gi;
+    if (j < a.p1 && j != a.L - 1) {
+      const int slot = (j >> psh) - (a.p0 >> psh);
+      const int pg = (pgs != nullptr && slot < 16) ? pgs[slot] : __ldcg(c.p.kv_indices + a.kv_base + (j >> psh));
+      const size_t src = ((((size_t)pg << psh) + (j & pmask)) * pl.HKV + a.h) * kHeadDim;
+      const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(op.k_cache) + src;
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(op.v_cache) + src;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(kp));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(kp + 64));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(vp));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(vp + 64));
     }
   }
 }
@@ -1659,6 +1706,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   // layers start their K/V row loads without any dependent look-up.
   int* lens = reinterpret_cast<int*>(c.red() + 64);
   int* pgc = lens + 2 * kAttnLensMax + (c.tid >> 4) * 8;
+  int* pgs = lens + 2 * kAttnLensMax + 16 * 8;  // [16]: page numbers of the first task's chunk, from its first page on
   const int key = (c.iter << 8) ^ (op.aux0 * 16 + op.aux1);  // iteration and head geometry
   const bool fill = c.attn_iter != key;
   c.attn_iter = key;
@@ -1720,6 +1768,13 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;
+      if (a.valid) {
+        if (fill && c.tid < 16) {  // (read only after the barrier's CTA-wide sync)
+          const int slot = (a.p0 >> p.page_shift) + c.tid;
+          if ((slot << p.page_shift) < a.p1) pgs[c.tid] = __ldcg(p.kv_indices + a.kv_base + slot);
+        }
+        attn_l2_ahead(c, op, pl, a, l16, fill ? nullptr : pgs);
+      }
       MK_STAMP(c, 1);
       if (op.flags & F_SYNC_BEFORE) {  // op_barrier, with the wait inlined
         grid_wait(c);
@@ -1730,7 +1785,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         return;
       }
     }
-    MK_CLK(c, 8);
+    if (task == (int)blockIdx.x) MK_CLK(c, 8);
     if (task >= pl.ntasks) break;
     if (!a.valid) continue;
     const int L = a.L;
@@ -1765,7 +1820,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     MK_CLK(c, 10);
     MK_STAMP(c, 2);
     float m, l, o[8];
-    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o);
+    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, task == (int)blockIdx.x ? pgs : nullptr);
     MK_CLK(c, 11);
     MK_STAMP(c, 3);
     // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
