@@ -574,8 +574,7 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
           p.partial + (((size_t)group * GS + blockIdx.x) * 2 + (first_of_cta ? 0 : 1)) * slot_elems);
 #pragma unroll 1
       for (int i = c.tid; i < nvec4; i += kNumConsumers) mine[i] = red4[i];
-      __threadfence();
-      consumer_sync();
+      consumer_sync();  // thread 0's release covers what the CTA wrote before this sync
       if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
       return;
     }
@@ -1871,6 +1870,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       MK_STAMP(c, 5);
       volatile int* fl = c.flags();
       unsigned* cnt = p.attn_count + (size_t)a.t * pl.HKV + a.h;
+      const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
       if (c.tid == 0) {
         unsigned old;
         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
@@ -1879,8 +1879,9 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       consumer_sync();
       MK_CLK(c, 14);
       MK_STAMP(c, 6);
-      if (fl[2] != 0) {  // the chunk that arrives last merges all of them
-        const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
+      // The chunk that arrives last merges all of them.  (A fixed merger per kv head, polling the
+      // counter, measured slower: the last arriver knows at once that it is the last.)
+      if (fl[2] != 0) {
         attn_merge(c, base, out, a.nch, pl.qpk, part_stride);
         if (c.tid == 0) *cnt = 0u;
       }

@@ -119,6 +119,7 @@ struct mk_handle {
   bool xchg_ready = false;
   int xchg_tokens = 0, xchg_cols = 0, xchg_units = 0;
   unsigned launches = 0;
+  size_t attn_count_bytes = 0;  // the attention chunk counters, cleared before every launch
 
   int fail(int code, const char* fmt, ...) {
     char buf[1024];
@@ -887,7 +888,8 @@ int mk_compile(mk_handle* h) {
   kp.attn_max_chunks = kAttnMaxChunks;
   if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_tokens * max_hkv * kAttnMaxChunks * max_qpk * (mk::kHeadDim + 2) * 4)) return e;
   kp.attn_part = (float*)p;
-  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_tokens * max_hkv * 4)) return e;
+  h->attn_count_bytes = (size_t)cfg.max_num_batched_tokens * max_hkv * 4;
+  if (int e = h->dmalloc(&p, h->attn_count_bytes)) return e;
   kp.attn_count = (unsigned*)p;
   if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_requests * 4)) return e;
   kp.request_ids = (int*)p;
@@ -1105,6 +1107,9 @@ int mk_launch_async(mk_handle* h, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   // grid barrier, control word, abort flag and status live in one 256-byte block behind sched[0..15]
   cudaError_t ce = cudaMemsetAsync((char*)h->kp.sched + 64, 0, 192, s);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  // (a launch that aborted may have left chunk counters of its attention ops half-way)
+  ce = cudaMemsetAsync(h->kp.attn_count, 0, h->attn_count_bytes, s);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
   h->launches += 1;
   h->kp.xchg_seq_base = h->launches << 20;  // exchange sequence numbers keep growing across launches
