@@ -440,6 +440,39 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
   consumer_sync();
 }
 
+// Staging for a row-owner linear WITHOUT a fused norm (one or two token rows, at most 24 stages
+// of 512 k): warp w multiplies only the w-th 64-wide slice of every stage, so it stages exactly
+// those slices of the row itself, all in one round of loads, and needs no CTA-wide sync before
+// its first tile.  Lane l takes the 16-byte chunk (l & 7) of the slices of stages (l >> 3) + 4 i.
+// (The same scheme with the norm fused in was 0.36 ms per step SLOWER: its unrolled scaling code
+// is several KB that every op would run once, out of a cold instruction cache.)
+__device__ __noinline__ void stage_x_rows(Ctx& c, const void* in, int ld_in, int K, int kp, int tok0, int rows, int T) {
+  constexpr int kMaxV = 6;  // 24 stages / 4 per round
+  uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
+  const int pitch = (kp >> 3) + 1;  // uint4 per row
+  const int v0 = ((c.lane >> 3) * kRowsStageK + c.warp * 64 + (c.lane & 7) * 8) >> 3;  // vector of round 0
+  constexpr int vstep = 4 * kRowsStageK / 8;                                           // vectors per round
+  const int kvec = K >> 3, nvec = kp >> 3;
+  if (c.lane == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);  // the chunk absent tokens point at (every warp writes the same zeros)
+#pragma unroll 1
+  for (int t = 0; t < rows; ++t) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(in) + (size_t)(tok0 + t) * ld_in);
+    const bool live = tok0 + t < T;
+    uint4 raw[kMaxV];
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = v0 + i * vstep;
+      raw[i] = (live && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = v0 + i * vstep;
+      if (v < nvec) xs[t * pitch + v] = raw[i];
+    }
+  }
+  __syncwarp();
+}
+
 // ------------------------------------------------------------------------------------
 // linear layer: weight tiles from the TMA ring x activations from shared memory on the
 // warp-level tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate)
@@ -1035,7 +1068,8 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int kp = nks * kRowsStageK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
+  if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
+  else stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
   MK_STAMP(c, 1);
   int row0, row1;
   bool any;
