@@ -1358,19 +1358,35 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
 }
 
 __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int task,
-                                          int l16, AttnTask& a, int* pgc = nullptr, bool fill = false) {
-  a.valid = false;
-  if (task >= pl.ntasks) return;
-  a.ch = task % pl.nch_max;
-  a.h = (task / pl.nch_max) % pl.HKV;
-  a.t = task / (pl.nch_max * pl.HKV);
-  a.L = lens[a.t];
-  a.p0 = a.ch * pl.CS;
-  if (a.p0 >= a.L || a.L <= 0) return;
-  a.valid = true;
-  a.p1 = min(a.L, a.p0 + pl.CS);
-  a.nch = (a.L + pl.CS - 1) / pl.CS;
-  a.kv_base = lens[kAttnLensMax + a.t];
+                                          int l16, AttnTask& a, int* pgc = nullptr, bool fill = false,
+                                          int* geom = nullptr) {
+  // `geom`: the task's geometry as the iteration's first attention op worked it out
+  // ([0] valid, then t, h, ch, L, p0, p1, nch, kv_base): the other layers skip the divisions.
+  if (geom != nullptr && !fill) {
+    a.valid = geom[0] != 0;
+    if (!a.valid) return;
+    a.t = geom[1]; a.h = geom[2]; a.ch = geom[3]; a.L = geom[4];
+    a.p0 = geom[5]; a.p1 = geom[6]; a.nch = geom[7]; a.kv_base = geom[8];
+  } else {
+    a.valid = false;
+    if (geom != nullptr && c.tid == 0) geom[0] = 0;
+    if (task >= pl.ntasks) return;
+    a.ch = task % pl.nch_max;
+    a.h = (task / pl.nch_max) % pl.HKV;
+    a.t = task / (pl.nch_max * pl.HKV);
+    a.L = lens[a.t];
+    a.p0 = a.ch * pl.CS;
+    if (a.p0 >= a.L || a.L <= 0) return;
+    a.valid = true;
+    a.p1 = min(a.L, a.p0 + pl.CS);
+    a.nch = (a.L + pl.CS - 1) / pl.CS;
+    a.kv_base = lens[kAttnLensMax + a.t];
+    if (geom != nullptr && c.tid == 0) {
+      geom[0] = 1;
+      geom[1] = a.t; geom[2] = a.h; geom[3] = a.ch; geom[4] = a.L;
+      geom[5] = a.p0; geom[6] = a.p1; geom[7] = a.nch; geom[8] = a.kv_base;
+    }
+  }
   const int pos = min(a.L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
   a.wq = __ldg(reinterpret_cast<const uint4*>(op.q_norm_w) + l16);
   a.wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
@@ -1752,21 +1768,34 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     }
     consumer_sync();
   }
-  int Lmax = 1;
-#pragma unroll 1
-  for (int r = 0; r < T; ++r) Lmax = max(Lmax, lens[r]);
   AttnPlan pl;
   pl.HKV = op.aux0;
   pl.qpk = op.aux1 / op.aux0;
-  const int nb_max = (Lmax + 15) >> 4;
-  int bpc = (T * pl.HKV * nb_max + G - 1) / G;  // 16-position blocks per chunk: one round of tasks
-  bpc = max(bpc, (nb_max + p.attn_max_chunks - 1) / p.attn_max_chunks);
-  bpc = max(bpc, 1);
-  // one round of tasks: a chunk count that leaves a few CTAs a second task doubles the op's time
-  while (T * pl.HKV <= G && T * pl.HKV * ((nb_max + bpc - 1) / bpc) > G) ++bpc;
-  pl.CS = bpc * 16;
-  pl.nch_max = (nb_max + bpc - 1) / bpc;
-  pl.ntasks = T * pl.HKV * pl.nch_max;
+  int* plan = pgs + 16;   // [0] chunk size, [1] chunks of the longest request, [2] tasks: the same in every layer of an iteration
+  int* geom = plan + 3;   // [9]: the CTA's first task, see attn_prepare
+  if (fill) {
+    int Lmax = 1;
+#pragma unroll 1
+    for (int r = 0; r < T; ++r) Lmax = max(Lmax, lens[r]);
+    const int nb_max = (Lmax + 15) >> 4;
+    int bpc = (T * pl.HKV * nb_max + G - 1) / G;  // 16-position blocks per chunk: one round of tasks
+    bpc = max(bpc, (nb_max + p.attn_max_chunks - 1) / p.attn_max_chunks);
+    bpc = max(bpc, 1);
+    // one round of tasks: a chunk count that leaves a few CTAs a second task doubles the op's time
+    while (T * pl.HKV <= G && T * pl.HKV * ((nb_max + bpc - 1) / bpc) > G) ++bpc;
+    pl.CS = bpc * 16;
+    pl.nch_max = (nb_max + bpc - 1) / bpc;
+    pl.ntasks = T * pl.HKV * pl.nch_max;
+    if (c.tid == 0) {
+      plan[0] = pl.CS;
+      plan[1] = pl.nch_max;
+      plan[2] = pl.ntasks;
+    }
+  } else {
+    pl.CS = plan[0];
+    pl.nch_max = plan[1];
+    pl.ntasks = plan[2];
+  }
   // More (request, kv head) pairs than CTAs and no sequence that needs splitting: several pairs per CTA at a time.
   if constexpr (PATH == PATH_UMMA) {
     if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4) {
@@ -1797,7 +1826,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
 #pragma unroll 1
   for (int task = blockIdx.x;; task += G) {
     AttnTask a;
-    attn_prepare(c, op, pl, lens, task, l16, a, first ? pgc : nullptr, fill);
+    attn_prepare(c, op, pl, lens, task, l16, a, first ? pgc : nullptr, fill, first ? geom : nullptr);
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;

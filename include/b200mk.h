@@ -55,7 +55,7 @@ typedef struct mk_config {
   int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer, -1 = none (stored +1: 0 = none) */
   int32_t debug_flags;              /* measurement aids. bit 0: linear tasks skip the arithmetic (weight-stream timing only); bit 1: attention tasks keep their barrier and do nothing else */
   int32_t max_stages;               /* cap on the weight ring depth, 0 = as many 16 KB stages as fit */
-  int32_t prefetch_kb;              /* KB of weights per CTA requested into L2 ahead of the shared-memory ring; 0 = default (256 for one or two batched tokens, off otherwise), < 0 = off */
+  int32_t prefetch_kb;              /* KB of weights per CTA requested into L2 ahead of the shared-memory ring; 0 = default (512 for one or two batched tokens, off otherwise), < 0 = off */
   int32_t reserved[3];
 } mk_config;
 
