@@ -19,7 +19,8 @@ class MkConfig(C.Structure):
         ("max_num_batched_tokens", C.c_int32), ("max_num_pages", C.c_int32), ("page_size", C.c_int32),
         ("numerics", C.c_int32), ("eos_token_id", C.c_int64), ("fuse", C.c_int32),
         ("max_iterations", C.c_int32), ("timeout_ms", C.c_int64), ("device", C.c_int32),
-        ("trace_op", C.c_int32), ("debug_flags", C.c_int32), ("max_stages", C.c_int32), ("prefetch_kb", C.c_int32), ("reserved", C.c_int32 * 3),
+        ("trace_op", C.c_int32), ("debug_flags", C.c_int32), ("max_stages", C.c_int32), ("prefetch_kb", C.c_int32),
+        ("cluster_size", C.c_int32), ("test_barrier_epoch", C.c_uint32), ("reserved", C.c_int32 * 2),
     ]
 
 
@@ -49,6 +50,9 @@ SIGNATURES = {
     "mk_grid_size": (C.c_int, [C.c_void_p]),
     "mk_weight_bytes_per_step": (C.c_int64, [C.c_void_p]),
     "mk_debug_partition": (C.c_int, [C.c_int64, C.c_int64, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int)]),
+    "mk_debug_exchange_sequence": (C.c_int, [C.c_uint32, C.c_uint32, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint32),
+                                             C.POINTER(C.c_int64), C.POINTER(C.c_int)]),
+    "mk_barrier_target_reached": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "mk_tensor_ptr": (C.c_void_p, [C.c_void_p, C.c_int]),
     "mk_tensor_read": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64]),
     "mk_linear_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),

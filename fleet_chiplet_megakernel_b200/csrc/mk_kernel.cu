@@ -85,11 +85,7 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 // barrier counter and abort flag (adjacent words) in one load
 __device__ __forceinline__ uint2 ld_bar_pair(const unsigned* p) {
   uint2 v;
-#ifdef MK_BAR_RELAXED
-  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-#else
   asm volatile("ld.acquire.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-#endif
   return v;
 }
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
@@ -127,8 +123,10 @@ struct Ctx {
   unsigned long long* dbg;  // inner-phase stamps of the traced op (thread 0), or null
   unsigned long long* pr;   // this op's trace record, or null
   bool dead;                // abort flag seen at the op's barrier (CTA-uniform)
-  unsigned ar_seq;          // allreduce ops executed so far in this launch
+  unsigned ar_seq;          // cross-rank exchanges (allreduce pushes) executed so far in this launch
   unsigned lin_seq;         // linear ops whose barrier has been passed in this launch
+  unsigned nbar;            // grid barriers waited for in this launch (phase of the cluster mbarriers)
+  uint32_t cl_rank, cl_size;  // this CTA's rank in its thread-block cluster, CTAs per cluster (1: no clusters)
   __device__ Ctx(const KParams& p_) : p(p_) {}
   __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
@@ -137,6 +135,10 @@ struct Ctx {
   // behind the flags: the accumulator-ready mbarrier of the tcgen05 path and the word tcgen05.alloc writes
   __device__ uint32_t done_bar() const { return smem_addr + p.bar_off + 24 * p.num_stages + 64; }
   __device__ uint32_t tmem_slot() const { return smem_addr + p.bar_off + 24 * p.num_stages + 72; }
+  // hierarchical grid barrier: arrivals of the cluster (used in its first CTA), release from the first CTA, its abort word
+  __device__ uint32_t cl_arrive_bar() const { return smem_addr + p.bar_off + 24 * p.num_stages + 80; }
+  __device__ uint32_t cl_open_bar() const { return smem_addr + p.bar_off + 24 * p.num_stages + 88; }
+  __device__ uint32_t cl_dead_word() const { return smem_addr + p.bar_off + 24 * p.num_stages + 96; }
   __device__ float* sums() const { return (float*)(smem + p.sums_off); }
   __device__ float* red() const { return (float*)(smem + p.red_off); }  // small scratch: reductions, lengths
 };
@@ -144,27 +146,10 @@ struct Ctx {
 //          [1] stages issued by the producer   [2] broadcast slot   [3] dead flag of the op
 //          [4] linear ops whose barrier the consumers have passed   [5] activation stages issued
 
-#ifdef MK_NO_STAMP
-#define MK_STAMP(c, k) do {} while (0)
-#else
 #define MK_STAMP(c, k)                                             \
   do {                                                            \
     if ((c).dbg != nullptr && (c).tid == 0) (c).dbg[k] = globaltimer(); \
   } while (0)
-#endif
-
-#ifdef MK_CLK_STAMPS
-#define MK_CLK(c, k)                                                                  \
-  do {                                                                               \
-    if ((c).dbg != nullptr && (c).tid == 0) {                                         \
-      long long t_;                                                                  \
-      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_)::"memory");                   \
-      (c).dbg[k] = (unsigned long long)t_;                                           \
-    }                                                                                \
-  } while (0)
-#else
-#define MK_CLK(c, k) do {} while (0)
-#endif
 
 __device__ __noinline__ void raise_abort(const Ctx& c, int code, int d0, int d1) {
   if (atomicCAS(c.p.abort_flag, 0, 1) == 0) {
@@ -211,50 +196,119 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t p
   return mbar_wait_slow(c, bar, parity, code);
 }
 
-// Grid-wide barrier of the consumer warps.  The counter only grows within a
-// launch: barrier number e is passed when it reaches e * gridDim.x.
+// Grid-wide barrier of the consumer warps.  The counter only grows within a launch: barrier
+// number e is passed when it reaches e * (arrivals per barrier), compared modulo 2^32 so
+// that a long launch may wrap it.
+//
+// Two shapes, chosen by the host per launch (KParams::cluster):
+//  * flat (cluster = 1): every CTA adds 1 to the counter in L2 and polls it.
+//  * hierarchical (cluster = 2 or 4, the kernel is launched in thread-block clusters): the CTAs
+//    of a cluster first meet on an mbarrier in the shared memory of the cluster's first CTA
+//    (remote arrive over distributed shared memory, release at cluster scope); that CTA alone
+//    adds 1 to the global counter, polls it, and then opens an mbarrier in each of its peers'
+//    shared memory.  The global line sees gridDim.x / cluster arrivals and pollers instead of
+//    gridDim.x.  (The reference's Fleet runtime counts arrivals per XCD before one global release
+//    per XCD, persistent_kernel.cuh:1214-1275; this is the same idea on Blackwell's clusters.)
+//
 // The arrival half on its own: an op that has loads to issue which do not depend on other
 // CTAs arrives first and issues them while the others catch up.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on an mbarrier that CTAs of the same cluster arrive on.
+__device__ __noinline__ bool cluster_bar_wait(const Ctx& c, uint32_t bar, uint32_t parity) {
+  unsigned long long t0 = 0;
+  unsigned polls = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (((++polls) & 1023u) == 0) {
+      if (aborted(c)) return false;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2 * c.p.timeout_ns) {
+        raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, -(int)c.cl_rank - 1);
+        return false;
+      }
+    }
+  }
+}
 __device__ __forceinline__ void grid_arrive(Ctx& c) {
   consumer_sync();
   c.epoch += 1;
   c.arrived = true;
-  // arrive with a release reduction: nothing comes back, polling can start at once
-  if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
+  if (c.tid == 0) {
+    // arrive with a release: nothing comes back, polling can start at once
+    if (c.cl_size == 1) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
+    else mbar_arrive_cluster(cluster_map(c.cl_arrive_bar(), 0));
+  }
 }
 // The waiting half.  Inlined where values loaded ahead of the barrier must stay in registers
 // (a call would spill them, and a spill waits for the load).
 __device__ __forceinline__ void grid_wait(Ctx& c) {
   c.arrived = false;
   if (c.tid == 0) {
-    const unsigned target = c.epoch * gridDim.x;
-    unsigned long long t0 = 0;
-    unsigned spins = 0;
-    // the abort flag is the word behind the counter: one 8-byte load polls both
     bool dead = false;
-    while (true) {
-      const uint2 v = ld_bar_pair(c.p.grid_bar);
-      if (v.y != 0u) {
-        dead = true;
-        break;
+    if (c.cl_rank == 0) {
+      if (c.cl_size > 1) {
+        // the cluster is complete: one arrival for all of it (the release is cumulative over what
+        // the peers published to this thread through the mbarrier)
+        if (cluster_bar_wait(c, c.cl_arrive_bar(), c.nbar & 1u))
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
+        else
+          dead = true;
       }
-      if (v.x >= target) break;
-      if (((++spins) & 1023u) == 0) {
-        const unsigned long long now = globaltimer();
-        if (t0 == 0) {
-          t0 = now;
-        } else if (now - t0 > 2 * c.p.timeout_ns) {
-          raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+      const unsigned target = c.epoch * (gridDim.x / c.cl_size);
+      unsigned long long t0 = 0;
+      unsigned spins = 0;
+      // the abort flag is the word behind the counter: one 8-byte load polls both
+      while (!dead) {
+        const uint2 v = ld_bar_pair(c.p.grid_bar);
+        if (v.y != 0u) {
           dead = true;
           break;
         }
+        if ((int)(v.x - target) >= 0) break;
+        if (((++spins) & 1023u) == 0) {
+          const unsigned long long now = globaltimer();
+          if (t0 == 0) {
+            t0 = now;
+          } else if (now - t0 > 2 * c.p.timeout_ns) {
+            raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+            dead = true;
+            break;
+          }
+        }
       }
+      for (uint32_t r = 1; r < c.cl_size; ++r) {
+        asm volatile("st.relaxed.cluster.shared::cluster.u32 [%0], %1;" ::"r"(cluster_map(c.cl_dead_word(), r)), "r"(dead ? 1u : 0u) : "memory");
+        mbar_arrive_cluster(cluster_map(c.cl_open_bar(), r));
+      }
+    } else {
+      if (!cluster_bar_wait(c, c.cl_open_bar(), c.nbar & 1u)) dead = true;
+      else dead = *reinterpret_cast<volatile uint32_t*>(c.smem + c.p.bar_off + 24 * c.p.num_stages + 96) != 0u;
     }
-#ifdef MK_BAR_RELAXED
-    __threadfence();
-#endif
     c.flags()[3] = dead ? 1 : 0;
   }
+  c.nbar += 1;
   consumer_sync();
 }
 __device__ __noinline__ void grid_sync(Ctx& c) {
@@ -290,6 +344,105 @@ __device__ __forceinline__ float block_sum(Ctx& c, float v) {
   consumer_sync();
   return s;
 }
+
+// ------------------------------------------------------------------------------------
+// tensor-parallel exchange over NVLink peer memory (the two allreduces of a layer)
+// ------------------------------------------------------------------------------------
+// The reference's allreduce is an NVSHMEM put-with-signal allgather followed by a local
+// reduction task (src/kernel/task_register.cc:1606-1687, tasks/ampere/reduction.cuh:139-166).
+// Here every rank stores its fp32 partial sums straight into EVERY rank's exchange region
+// (its own included) with plain stores over NVLink, as 8-byte words {value, exchange number}:
+// a word that carries the awaited number has arrived, so no fence, flag or second round trip
+// is needed, and a reader simply adds the ranks' words up in rank order in fp32 (identical
+// on every rank) and rounds once to bf16.  Data always lands in the reader's own memory; no
+// bulk or tensor copy ever touches a peer's memory.  The halves of a region alternate between
+// consecutive exchanges: a rank can only push exchange s+2 after it has read all of s+1 from
+// every peer, which those peers push after their last read of s.
+__device__ __forceinline__ uint4 ld_sys_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_sys_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_v2(uint2* p, uint32_t a, uint32_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void st_sys_v4(uint4* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// one value of exchange `seq` into every rank's region
+__device__ __forceinline__ void xchg_push1(const KParams& p, unsigned seq, int tok, int col, float v) {
+  const size_t w = xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, p.rank, tok, col);
+#pragma unroll 1
+  for (int r = 0; r < p.world; ++r) st_sys_v2(reinterpret_cast<uint2*>(p.xchg[r]) + w, __float_as_uint(v), seq);
+}
+// A word of a rank that is not there yet: poll it (bounded).  Returns false after raising the abort flag.
+__device__ __noinline__ bool xchg_wait_word(const Ctx& c, const uint2* w, unsigned seq, int src) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    if (xchg_arrived(ld_sys_v2(w).y, seq)) return true;
+    if (((++spins) & 63u) == 0) {
+      if (aborted(c)) return false;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > c.p.timeout_ns) {
+        raise_abort(c, ST_TIMEOUT_RANK, src, (int)seq);
+        return false;
+      }
+    }
+  }
+}
+// 8 consecutive columns (col a multiple of 8) of token row `tok`: the sum over ranks as bf16 x 8
+__device__ __noinline__ uint4 xchg_gather8(const Ctx& c, unsigned seq, int tok, int col) {
+  const KParams& p = c.p;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 1
+  for (int r = 0; r < p.world; ++r) {
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(p.xchg[p.rank]) +
+                                                      xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, r, tok, col));
+    uint4 q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = ld_sys_v4(src + i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (!xchg_arrived(q[i].y, seq) || !xchg_arrived(q[i].w, seq)) {
+        const uint2* w2 = reinterpret_cast<const uint2*>(src + i);
+        if (!xchg_wait_word(c, w2, seq, r) || !xchg_wait_word(c, w2 + 1, seq, r)) return make_uint4(0, 0, 0, 0);
+        q[i] = ld_sys_v4(src + i);
+      }
+      acc[2 * i] += __uint_as_float(q[i].x);
+      acc[2 * i + 1] += __uint_as_float(q[i].z);
+    }
+  }
+  return pack8(acc);
+}
+// one column: the bf16-rounded sum over ranks, as a float
+__device__ __noinline__ float xchg_gather1(const Ctx& c, unsigned seq, int tok, int col) {
+  const KParams& p = c.p;
+  float acc = 0.f;
+#pragma unroll 1
+  for (int r = 0; r < p.world; ++r) {
+    const uint2* w = reinterpret_cast<const uint2*>(p.xchg[p.rank]) + xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, r, tok, col);
+    uint2 q = ld_sys_v2(w);
+    if (!xchg_arrived(q.y, seq)) {
+      if (!xchg_wait_word(c, w, seq, r)) return 0.f;
+      q = ld_sys_v2(w);
+    }
+    acc += __uint_as_float(q.x);
+  }
+  return rbf(acc);
+}
+// number of the latest exchange (the one gathering ops read) and of the one a pushing linear writes
+__device__ __forceinline__ unsigned xchg_cur(const Ctx& c) { return xchg_seq(c.p.xchg_seq_base, c.ar_seq); }
+__device__ __forceinline__ unsigned xchg_next(const Ctx& c) { return xchg_seq(c.p.xchg_seq_base, c.ar_seq + 1u); }
 
 // ------------------------------------------------------------------------------------
 __device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
@@ -353,7 +506,8 @@ __device__ __forceinline__ float row_rms_scale(const float* red, int first, int 
 // squares and the scaling; the norm weights were loaded ahead of the op's barrier.
 template <int NV>
 __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* dst, const uint4* pre_w, int K, int nvec,
-                                               int v0, int vstep, bool active, bool valid, int red_first, int wpr) {
+                                               int v0, int vstep, bool active, bool valid, int red_first, int wpr,
+                                               bool gather, int tok) {
   const int kvec = K >> 3;
   const bool torch_num = c.p.numerics == NUM_TORCH;
   float* red = c.red();
@@ -361,7 +515,8 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int v = v0 + vstep * i;
-    raw[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (valid && v < kvec) raw[i] = gather ? xchg_gather8(c, xchg_cur(c), tok, v * 8) : __ldcg(src + v);
   }
   float ss = 0.f;
 #pragma unroll
@@ -381,8 +536,9 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
   consumer_sync();
 }
 
+// `gather`: the rows are not read from `in` but summed over the ranks' slots of the latest exchange.
 __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0,
-                                     int rows, int T, const uint4* pre_w) {
+                                     int rows, int T, const uint4* pre_w, bool gather = false) {
   uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3, kvec = K >> 3;
@@ -399,8 +555,8 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
   if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);  // the chunk absent tokens point at
   if (active && part == 0 && c.lane == 0) dst[nvec] = make_uint4(0, 0, 0, 0);  // the row's padding vector
   if (wv != nullptr && pre_w != nullptr && nvec <= 4 * vstep) {
-    if (nvec <= 2 * vstep) stage_row_regs<2>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr);
-    else stage_row_regs<4>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr);
+    if (nvec <= 2 * vstep) stage_row_regs<2>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb);
+    else stage_row_regs<4>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb);
     return;
   }
   float ss = 0.f;
@@ -413,7 +569,8 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int v = vb + i * vstep;
-        val[i] = (valid && v < kvec) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+        val[i] = make_uint4(0, 0, 0, 0);
+        if (valid && v < kvec) val[i] = gather ? xchg_gather8(c, xchg_cur(c), tok0 + tb, v * 8) : __ldcg(src + v);
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -538,17 +695,23 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   }
   const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
+  const bool push = (op.flags & F_PUSH) != 0;
 #pragma unroll 1
   for (int e = c.tid; e < kTileRows * ntok; e += kNumConsumers) {
     const int row = e & 127, tb = e >> 7;
     const int tok = tok0 + tb, col = blk * kTileRows + row;
     if (col < op.n) {
       float v = red[row * kRedStride + tb];
+      if (p.numerics == NUM_TORCH && !push) v = rbf(v);  // (pushed partial sums stay fp32: they are rounded once, after the ranks are added up)
       if (with_res) {
-        const float r = (e < kNumConsumers) ? res0 : __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
-        v = (p.numerics == NUM_TORCH) ? rbf(v) + r : v + r;
+        float r;
+        if (e < kNumConsumers) r = res0;
+        else if (op.flags & F_GATHER_RES) r = xchg_gather1(c, xchg_cur(c), tok, col);
+        else r = __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
+        v += r;
       }
-      out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(v);
+      if (push) xchg_push1(p, xchg_next(c), tok, col, v);
+      else out[(size_t)tok * op.ld_out + col] = __float2bfloat16_rn(v);
     }
   }
   if (op.flags & F_ARGMAX) {
@@ -675,7 +838,8 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
   const int kp = nkt * kTileK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
+  stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w,
+          (op.flags & F_GATHER_IN) != 0);
   MK_STAMP(c, 1);
 
   const unsigned total = (unsigned)op.nblk * (unsigned)nkt;
@@ -719,7 +883,9 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
     if (new_blk) {
       new_blk = false;
       res0 = 0.f;
-      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
+        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+                                         : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
     if (tile == t0) MK_STAMP(c, 2);
@@ -821,7 +987,9 @@ __device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0
     if (new_blk) {
       new_blk = false;
       res0 = 0.f;
-      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
+        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+                                         : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
     mbar_wait(c, bar_x0 + 8 * s, (c.xphase >> s) & 1u, ST_TIMEOUT_FULL);
@@ -954,7 +1122,9 @@ __device__ __noinline__ void linear_pass_umma(Ctx& c, const OpDesc& op, int tok0
     if (new_blk) {
       new_blk = false;
       res0 = 0.f;
-      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n) res0 = __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
+      if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
+        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+                                         : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     // every warp follows the ring (one arrival per warp and phase keeps the "empty" count
     // exact); warp 0's arrival is the commit of the stage's MMAs
@@ -1068,8 +1238,9 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int kp = nks * kRowsStageK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
-  else stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w);
+  if (nks <= 24 && ntok <= 2 && !(op.flags & (F_NORM_IN | F_GATHER_IN))) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
+  else stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w,
+               (op.flags & F_GATHER_IN) != 0);
   MK_STAMP(c, 1);
   int row0, row1;
   bool any;
@@ -1114,7 +1285,9 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     // the residual of this thread's output is requested a whole chunk ahead of its use
     float res0 = 0.f;
     const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
-    if (with_res && e_live) res0 = __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
+    if (with_res && e_live)
+      res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
+                                       : __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
     float acc[4][4];  // [2 * tile + (k step & 1)]: two chains per tile, added up at the end
 #pragma unroll
     for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
@@ -1187,8 +1360,9 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
       if (e_live) {
 #pragma unroll
         for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + e_tok];
-        if (with_res) v = (p.numerics == NUM_TORCH) ? rbf(v) + res0 : v + res0;
-        out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
+        if (with_res) v = (p.numerics == NUM_TORCH && !(op.flags & F_PUSH)) ? rbf(v) + res0 : v + res0;
+        if (op.flags & F_PUSH) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
+        else out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
       }
       if (op.flags & F_ARGMAX) {
         ArgBest b;
@@ -1239,10 +1413,11 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
         if (c.p.x_rows == 8) linear_pass_wide<1>(c, op, g * op.aux3, T, g);
         else linear_pass_wide<2>(c, op, g * op.aux3, T, g);
       }
-      return;
+    } else {
+      for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
     }
-    for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
   }
+  if (op.flags & F_PUSH) c.ar_seq += 1;  // every CTA counts the exchange, with or without rows of its own
 }
 
 // ------------------------------------------------------------------------------------
@@ -1847,7 +2022,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         return;
       }
     }
-    if (task == (int)blockIdx.x) MK_CLK(c, 8);
     if (task >= pl.ntasks) break;
     if (!a.valid) continue;
     const int L = a.L;
@@ -1860,7 +2034,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
       q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
       if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
-      MK_CLK(c, 9);
     }
     if (c.warp == kw) {
       F8 kf;
@@ -1879,11 +2052,9 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     consumer_sync();
     const uint4 qv = sm_q[head * 16 + l16];
     const uint4 knew = sm_k[l16];
-    MK_CLK(c, 10);
     MK_STAMP(c, 2);
     float m, l, o[8];
     attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, task == (int)blockIdx.x ? pgs : nullptr);
-    MK_CLK(c, 11);
     MK_STAMP(c, 3);
     // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
     // elements then combines the position groups of each head
@@ -1897,7 +2068,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     consumer_sync();
-    MK_CLK(c, 12);
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
@@ -1926,7 +2096,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         }
       }
     }
-    MK_CLK(c, 13);
     MK_STAMP(c, 4);
     if (a.nch > 1) {
       consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
@@ -1940,7 +2109,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
       }
       consumer_sync();
-      MK_CLK(c, 14);
       MK_STAMP(c, 6);
       // The chunk that arrives last merges all of them.  (A fixed merger per kv head, polling the
       // counter, measured slower: the last arriver knows at once that it is the last.)
@@ -1950,7 +2118,6 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     consumer_sync();
-    MK_CLK(c, 15);
     MK_STAMP(c, 7);
   }
 }
@@ -1991,8 +2158,9 @@ __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   }
   if (op_barrier(c, op)) return;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1,
-            pre ? pre_w : nullptr);
+    if (op.flags & F_GATHER_IN) stage_x(c, nullptr, 0, op.n, kp, op.w, tok, 1, tok + 1, pre ? pre_w : nullptr, true);
+    else stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1,
+                 pre ? pre_w : nullptr);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)tok * op.ld_out);
     for (int v = c.tid; v < (op.n >> 3); v += kNumConsumers) dst[v] = xs[v];
@@ -2090,89 +2258,44 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
 }
 
 // ------------------------------------------------------------------------------------
-// tensor-parallel allreduce over NVLink peer memory
+// stand-alone allreduce layer
 // ------------------------------------------------------------------------------------
-// aux0 = world size, aux1 = this rank.  in: this rank's partial sums [T, n] bf16, out: the
-// sum over ranks [T, n] bf16 (fp32 addition in rank order, one rounding: the reference's
-// reduction task, tasks/ampere/reduction.cuh:139-166).  One-shot push: the CTA that owns a
-// 4 KB unit of the tensor stores it into its slot in every peer's exchange region with
-// plain 16-byte stores, then publishes a sequence number with a system-scope release; the
-// same CTA waits (bounded) for the peers' numbers on its own unit and adds the slots up.
-// Data always lands in the consumer's own memory; no bulk or tensor copy ever reads a
-// peer's memory.  Slots are double-buffered by sequence parity: a rank can be at most one
-// allreduce ahead of a peer on any unit, because finishing one needs that peer's push.
-__device__ __forceinline__ uint4 ld_sys_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
+// aux0 = world size, aux1 = this rank.  in: this rank's partial sums [T, n] bf16, out: the sum over
+// ranks [T, n] bf16 (fp32 addition in rank order, one rounding: the reference's reduction task,
+// tasks/ampere/reduction.cuh:139-166).  The host lowers an allreduce layer to this op only where it
+// cannot fold the exchange into the producing linear's epilogue and the consumers' input staging
+// (F_PUSH / F_GATHER_*).  Same exchange words as there: every unit of 8 columns is pushed to all
+// ranks and then gathered from this rank's own region by the same thread.
 __device__ __noinline__ void op_allreduce(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
   if (op_barrier(c, op)) return;
-  const int world = op.aux0, me = op.aux1;
-  const unsigned seq = p.xchg_seq_base + (++c.ar_seq);
+  const int world = op.aux0;
   const int nvec = op.n >> 3;
-  const int upr = (nvec + kNumConsumers - 1) / kNumConsumers;  // units per row
-  const size_t slot_row = (size_t)p.xchg_cols * 2;             // bytes
-  const size_t slot_rank = slot_row * p.xchg_tokens;
-  const size_t slot_par = slot_rank * world;
-  const size_t flags_off = 2 * slot_par;
-  const size_t par_off = (size_t)(seq & 1u) * slot_par;
+  if (world <= 1) {  // a single rank: the sum is the input
 #pragma unroll 1
-  for (int unit = blockIdx.x; unit < T * upr; unit += gridDim.x) {
-    const int row = unit / upr, v = (unit % upr) * kNumConsumers + c.tid;
-    const bool valid = v < nvec;
-    uint4 mine = make_uint4(0, 0, 0, 0);
-    if (valid) mine = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)row * op.ld_in) + v);
-    if (valid) {
-#pragma unroll 1
-      for (int r = 0; r < world; ++r) {
-        if (r == me) continue;
-        uint4* dst = reinterpret_cast<uint4*>(p.xchg[r] + par_off + (size_t)me * slot_rank + (size_t)row * slot_row) + v;
-        *dst = mine;
-      }
+    for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
+      const int row = u / nvec, v = u % nvec;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)row * op.ld_out)[v] =
+          __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)row * op.ld_in) + v);
     }
-    __threadfence_system();
-    consumer_sync();
-    if (c.tid < world && c.tid != me) {
-      unsigned* theirs = reinterpret_cast<unsigned*>(p.xchg[c.tid] + flags_off) + (size_t)me * p.xchg_units + unit;
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(seq) : "memory");
-      const unsigned* ours = reinterpret_cast<const unsigned*>(p.xchg[me] + flags_off) + (size_t)c.tid * p.xchg_units + unit;
-      unsigned long long t0 = 0;
-      unsigned spins = 0;
-      while (true) {
-        unsigned got;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(ours) : "memory");
-        if ((int)(got - seq) >= 0) break;
-        if (((++spins) & 255u) == 0) {
-          if (aborted(c)) break;
-          const unsigned long long now = globaltimer();
-          if (t0 == 0) {
-            t0 = now;
-          } else if (now - t0 > c.p.timeout_ns) {
-            raise_abort(c, ST_TIMEOUT_RANK, c.tid, (int)got);
-            break;
-          }
-        }
-      }
-    }
-    consumer_sync();
-    if (valid) {
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll 1
-      for (int r = 0; r < world; ++r) {
-        uint4 x = mine;
-        if (r != me) x = ld_sys_v4(reinterpret_cast<const uint4*>(p.xchg[me] + par_off + (size_t)r * slot_rank + (size_t)row * slot_row) + v);
-        float f[8];
-        unpack8(x, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
-      }
-      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)row * op.ld_out)[v] = pack8(acc);
-    }
+    return;
   }
+  const unsigned seq = xchg_next(c);
+#pragma unroll 1
+  for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
+    const int row = u / nvec, v = u % nvec;
+    float f[8];
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)row * op.ld_in) + v), f);
+    const size_t w = xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, p.rank, row, v * 8);
+#pragma unroll 1
+    for (int r = 0; r < world; ++r) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint2*>(p.xchg[r]) + w);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st_sys_v4(dst + i, __float_as_uint(f[2 * i]), seq, __float_as_uint(f[2 * i + 1]), seq);
+    }
+    reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)row * op.ld_out)[v] = xchg_gather8(c, seq, row, v * 8);
+  }
+  c.ar_seq += 1;
 }
 
 // ------------------------------------------------------------------------------------
@@ -2635,7 +2758,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   c.smem = smem_raw + pad;
   c.smem_addr = raw_addr + pad;
-  c.epoch = 0;
+  c.epoch = p.bar_epoch0;
+  c.nbar = 0;
+  c.cl_size = p.cluster > 1 ? (uint32_t)p.cluster : 1u;
+  c.cl_rank = 0;
+  if (c.cl_size > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(c.cl_rank));
   c.cons_idx = 0;
   c.xphase = 0;
   c.arrived = false;
@@ -2661,6 +2788,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       mbar_init(c.xfull_bar(s), 1);
     }
     mbar_init(c.done_bar(), 1);
+    mbar_init(c.cl_arrive_bar(), c.cl_size);
+    mbar_init(c.cl_open_bar(), 1);
     fl[0] = 0;
     fl[1] = 0;
     fl[2] = 0;
@@ -2671,6 +2800,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  if (c.cl_size > 1) {  // no CTA may arrive on a peer's mbarrier before it is initialised
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   // Tensor memory for the tcgen05 linears (32 or 64 token rows per box): x_rows columns of fp32
   // accumulators, allocated once by warp 0 and freed by it when the CTA leaves.
   constexpr bool use_tmem = PATH == PATH_UMMA;
@@ -2794,7 +2927,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     }
     // the producer may be waiting for the next iteration
     consumer_sync();
-    if (c.tid == 0) fl[0] = -1;
+    if (c.tid == 0) {
+      fl[0] = -1;
+      // exchanges executed by this launch: the host advances its running sequence base by it
+      if (blockIdx.x == 0) p.sched[6] = (int)c.ar_seq;
+    }
   }
   __syncthreads();
   // no CTA may exit with a bulk copy still writing its shared memory
@@ -2814,6 +2951,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c.tmem), "r"((uint32_t)p.x_rows) : "memory");
+  }
+  if (c.cl_size > 1) {  // a peer may still be storing into this CTA's shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
 }
 
@@ -2859,12 +3000,54 @@ extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes) {
   return n;
 }
 
+// Clusters of `cluster` CTAs that can be resident at once (the hierarchical barrier needs all of them).
+extern "C" int mk_kernel_max_clusters(int path, int smem_bytes, int cluster, int grid) {
+  const void* k = kernel_for_path(path);
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(mk::kNumThreads);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = cluster;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, k, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return n;
+}
+
 extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream) {
   const void* k = kernel_for_path(p->path);
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)p};
-  e = cudaLaunchCooperativeKernel(k, dim3(grid), dim3(mk::kNumThreads), args, (size_t)smem_bytes, (cudaStream_t)stream);
+  if (p->cluster <= 1) {
+    e = cudaLaunchCooperativeKernel(k, dim3(grid), dim3(mk::kNumThreads), args, (size_t)smem_bytes, (cudaStream_t)stream);
+    return (int)e;
+  }
+  // co-resident grid of thread-block clusters
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(mk::kNumThreads);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = p->cluster;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeCooperative;
+  at[1].val.cooperative = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 2;
+  e = cudaLaunchKernelExC(&cfg, k, args);
   return (int)e;
 }
 

@@ -55,6 +55,10 @@ enum OpFlags : int {
   F_RES_RANK0 = 1 << 9,     // residual only contributed when rank == 0 (row-parallel TP)
   F_XTILE = 1 << 10,        // linear: input rows arrive per stage by TMA as activation boxes
   F_ROWS = 1 << 11,         // linear: every CTA owns whole output rows (no split over k between CTAs)
+  // tensor parallelism: the allreduce behind a row-parallel linear folded into its neighbours
+  F_PUSH = 1 << 12,         // linear: the epilogue stores its fp32 sums into every rank's exchange slots instead of `out`
+  F_GATHER_IN = 1 << 13,    // linear / rmsnorm: the input rows are the rank-order sum of the latest exchange's slots
+  F_GATHER_RES = 1 << 14,   // linear: the residual is the rank-order sum of the latest exchange's slots
 };
 
 enum Numerics : int {
@@ -142,7 +146,10 @@ struct KParams {
   int* request_ids;   // [max_reqs]
   int* page_queue;    // ring of free pages [max_pages]
   int* sched;         // [0]=page head [1]=page tail [2]=next request id [3]=iterations done
+                      // [4]=outputs of the last iteration not appended yet [6]=exchanges executed by the last launch
   unsigned* grid_bar;
+  int cluster;            // CTAs per thread-block cluster of the launch (1 = flat grid barrier)
+  unsigned bar_epoch0;    // barrier epoch the launch starts at (the counter is preset to match; tests start near the wrap)
   int* ctrl;          // [0] = active tokens of the iteration, -1 = terminate
   int* abort_flag;
   int* status;        // [0]=code [1]=cta [2]=op [3]=iter [4..7]=detail
@@ -159,11 +166,13 @@ struct KParams {
   unsigned* attn_count;   // [tokens][kv heads]
   int attn_max_chunks;
   // tensor-parallel exchange: every rank's exchange region mapped into this GPU's address space
-  // (xchg[rank] is the local one).  Layout of a region: slots [2][world][xchg_tokens][xchg_cols] bf16,
-  // then flags [world][xchg_units] u32 (last push sequence number seen from each source rank).
+  // (xchg[rank] is the local one).  A region holds slots [2][world][xchg_tokens][xchg_cols] of 8-byte
+  // words {fp32 value, sequence number}: a word is valid for exchange number s once its second half
+  // equals s, so data and "arrived" flag travel in one store and no fence or separate flag is needed.
+  // Exchange s uses the half of the region selected by s & 1 (see xchg_word).
   unsigned char* xchg[8];
-  int xchg_tokens, xchg_cols, xchg_units;
-  unsigned xchg_seq_base;  // launches so far << 20: sequence numbers grow across launches
+  int xchg_tokens, xchg_cols;
+  unsigned xchg_seq_base;  // exchanges executed by all earlier launches: sequence numbers keep growing (mod 2^32)
   // optional per-op trace of the last iteration: [(op * grid + cta) * 4 + k] globaltimer ns,
   // k = 0 op reached, 1 barrier passed, 2 op done; op == num_ops is the iteration prologue
   unsigned long long* prof;
@@ -180,6 +189,19 @@ struct KParams {
   int red_off;
   int bar_off;
 };
+
+// Exchange sequence arithmetic (shared with the host-side checks).  Exchange k (1-based) of a launch
+// that follows `total_before` completed exchanges has number total_before + k, modulo 2^32; number 0 is
+// skipped by nobody: a word is "arrived" only when it carries exactly the awaited number, and the
+// previous occupants of a slot carry numbers that differ from it by a multiple of 2 up to the region's
+// age, so a collision needs 2^32 exchanges between two uses of one slot.
+__host__ __device__ inline unsigned xchg_seq(unsigned total_before, unsigned k) { return total_before + k; }
+__host__ __device__ inline unsigned xchg_half(unsigned seq) { return seq & 1u; }
+__host__ __device__ inline bool xchg_arrived(unsigned word_seq, unsigned seq) { return word_seq == seq; }
+// index (in 8-byte words) of (exchange seq, source rank, token row, column) in a region
+__host__ __device__ inline size_t xchg_word(unsigned seq, int world, int tokens, int cols, int src, int tok, int col) {
+  return (((size_t)xchg_half(seq) * world + src) * tokens + tok) * cols + col;
+}
 
 // Weight tiles of a linear op are dealt to `grid` CTAs as contiguous ranges
 // [c*total/grid, (c+1)*total/grid); tile_owner is the inverse.  32-bit arithmetic: the

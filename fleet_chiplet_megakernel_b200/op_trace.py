@@ -40,6 +40,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=100, help="tokens in the KV cache at the traced iteration")
+    ap.add_argument("--cluster", type=int, default=0, help="CTAs per cluster for the hierarchical grid barrier (0/1: flat)")
     args = ap.parse_args()
     g = Qwen3Geometry(layers=args.layers)
     dev = torch.device("cuda")
@@ -47,7 +48,7 @@ def main():
     prompt_len = 16
     iters = args.context
     dec = Qwen3Decoder(g, w, max_seq_length=max(1200, iters + 8), max_requests=args.batch, page_size=64,
-                       max_iterations=iters, trace=True)
+                       max_iterations=iters, trace=True, cluster_size=args.cluster)
     gen = torch.Generator().manual_seed(1000)
     prompts = [torch.randint(0, g.vocab, (prompt_len,), generator=gen) for _ in range(args.batch)]
     for _ in range(2):
@@ -56,7 +57,7 @@ def main():
     st = dec.mpk.get_event_timing()[:, 0].astype("float64")
     n_tail = min(20, len(st) - 1)
     print(f"step time with tracing on: {(st[-1] - st[-1 - n_tail]) / n_tail / 1e6:.3f} ms "
-          f"(batch {args.batch}, context ~{iters}, {args.layers} layers, grid {dec.mpk.grid_size()})")
+          f"(batch {args.batch}, context ~{iters}, {args.layers} layers, grid {dec.mpk.grid_size()}, cluster {max(1, args.cluster)})")
     tr = dec.mpk.op_trace().double()  # [ops + 1, grid, 4]
     n = tr.shape[0] - 1
     # label every device op by its kind and shape, e.g. "linear 6144x4096" (QKV), "attention"

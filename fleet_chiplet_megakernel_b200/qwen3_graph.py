@@ -177,7 +177,8 @@ class Qwen3Decoder:
                  total_requests: int | None = None, page_size: int = 64, max_num_pages: int | None = None,
                  device="cuda", numerics=None, fuse=None, keep_logits=False, eos_token_id: int = 0x7FFFFFFF,
                  max_iterations: int = 0, num_layers=None, timeout_ms: int = 0, trace: bool = False,
-                 trace_op: int = -1, debug_flags: int = 0, world_size: int = 1, rank: int = 0):
+                 trace_op: int = -1, debug_flags: int = 0, world_size: int = 1, rank: int = 0, cluster_size: int = 0,
+                 test_barrier_epoch: int = 0, max_num_batched_tokens: int | None = None):
         """``weights`` are this rank's shard (see ``shard_qwen3_weights``) when world_size > 1."""
         self.geom, self.device = geom, torch.device(device)
         R = max_requests
@@ -213,17 +214,29 @@ class Qwen3Decoder:
                           "paged_kv_last_page_len_buffer": self.kv_last_page_len},
             profiler_tensor=self.profiler, trace_name="", spec_decode_config=None, use_cutlass_kernel=True,
             eos_token_id=eos_token_id, numerics=numerics, fuse=fuse, max_iterations=max_iterations,
-            timeout_ms=timeout_ms, trace_op=trace_op, debug_flags=debug_flags)
+            timeout_ms=timeout_ms, trace_op=trace_op, debug_flags=debug_flags, cluster_size=cluster_size,
+            test_barrier_epoch=test_barrier_epoch)
         build_qwen3_graph(self.mpk, geom, weights, self.k_cache, self.v_cache, self.cos, self.sin,
                           self.input_tokens, self.output_tokens, logits=self.logits, num_layers=num_layers)
         self.mpk.compile()
 
     def set_prompts(self, prompts):
-        """prompts: list of 1-D int64 tensors, one per request."""
+        """prompts: list of 1-D int64 tensors, one per request.  Host prompts travel in one copy
+        (a padded [requests, longest] block) plus one for the lengths."""
+        n = len(prompts)
+        lens = [len(p) for p in prompts]
+        width = max(lens)
         self.tokens.zero_()
-        for r, p in enumerate(prompts):
-            self.tokens[r, : len(p)] = p.to(self.device)
-            self.prompt_lengths[r] = len(p)
+        if all(p.device.type == "cpu" for p in prompts):
+            block = torch.zeros(n, width, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else \
+                torch.zeros(n, width, dtype=torch.int64)
+            for r, p in enumerate(prompts):
+                block[r, : lens[r]] = p
+            self.tokens[:n, :width].copy_(block, non_blocking=True)
+        else:
+            for r, p in enumerate(prompts):
+                self.tokens[r, : lens[r]] = p.to(self.device)
+        self.prompt_lengths[:n].copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=False)
         self.mpk.init_requests()
 
     def run(self):

@@ -52,11 +52,15 @@ typedef struct mk_config {
   int32_t max_iterations;           /* 0 = run until every request has finished */
   int64_t timeout_ms;               /* bound of every in-kernel wait; 0 = default (4000) */
   int32_t device;                   /* CUDA device ordinal, -1 = current */
-  int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer, -1 = none (stored +1: 0 = none) */
-  int32_t debug_flags;              /* measurement aids. bit 0: linear tasks skip the arithmetic (weight-stream timing only); bit 1: attention tasks keep their barrier and do nothing else */
-  int32_t max_stages;               /* cap on the weight ring depth, 0 = as many 16 KB stages as fit */
+  /* ---- measurement and test aids: not part of the operator API.  Leave them zero in
+   * production; mk_create warns on stderr when debug_flags is set, because it changes results. */
+  int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer (stored +1: 0 = none) */
+  int32_t debug_flags;              /* bit 0: linear tasks skip the arithmetic (weight-stream timing only); bit 1: attention tasks keep their barrier and do nothing else.  RESULTS ARE WRONG with either bit */
+  int32_t max_stages;               /* cap on the weight ring depth, 0 = default */
   int32_t prefetch_kb;              /* KB of weights per CTA requested into L2 ahead of the shared-memory ring; 0 = default (512 for one or two batched tokens, off otherwise), < 0 = off */
-  int32_t reserved[3];
+  int32_t cluster_size;             /* CTAs per thread-block cluster of the launch: 0 = default, 1 = flat grid barrier, 2 or 4 = hierarchical (cluster-first) grid barrier */
+  uint32_t test_barrier_epoch;      /* tests only: barrier epoch every launch starts at (e.g. just below the 32-bit wrap of the counter) */
+  int32_t reserved[2];
 } mk_config;
 
 /* PersistentKernel.__init__ -> KNGraph(CyKNGraph(...)) (persistent_kernel.py:404). */
@@ -150,6 +154,13 @@ int mk_describe(mk_handle* h, char* buf, int n);       /* one line per device op
 int mk_grid_size(mk_handle* h);
 int64_t mk_weight_bytes_per_step(mk_handle* h);        /* bytes the TMA producer streams per iteration */
 int mk_debug_partition(int64_t nblk, int64_t nkt, int grid, int64_t* begin_out /* grid+1 */, int* owner_check);
+/* The arithmetic of the tensor-parallel exchange and of the grid barrier, as the device does it
+ * (used by the host-side tests).  Exchange k (1-based) of a launch that follows total_before
+ * completed exchanges: its number, the first 8-byte word of its half of a region, and how many of
+ * the numbers a slot may still hold from earlier uses would be taken for "arrived" (must be 0). */
+int mk_debug_exchange_sequence(uint32_t total_before, uint32_t k, int world, int tokens, int cols, uint32_t* seq_out,
+                               int64_t* first_word_out, int* stale_arrived_out);
+int mk_barrier_target_reached(uint32_t counter, uint32_t epoch, uint32_t arrivals_per_barrier);
 void* mk_tensor_ptr(mk_handle* h, int tensor_id);      /* device address after compile (runtime-owned ones too) */
 int mk_tensor_read(mk_handle* h, int tensor_id, void* host_buf, int64_t bytes); /* copy a tensor's bytes to the host */
 
@@ -168,7 +179,8 @@ int mk_tensor_read(mk_handle* h, int tensor_id, void* host_buf, int64_t bytes); 
  * The first call on a device looks up that array's device address; make this first call
  * outside any stream capture.  All calls share the array: calls that overlap on the GPU
  * race on it, so issue them on one stream or otherwise serialise them.  The launch is
- * asynchronous on `stream`; the return value covers argument checks and launch errors. */
+ * asynchronous on `stream`; the return value covers argument checks and launch errors.
+ * Not thread-safe: the per-device address cache and the scratch are shared by all callers. */
 #define MK_STATIC_MAX_TOKENS 8
 #define MK_STATIC_MAX_N 16384
 #define MK_STATIC_MAX_K 32768

@@ -58,6 +58,8 @@ QWEN3_8B = Geometry()
 # Small geometries for fast parity cases (head_dim stays 128, as in every Qwen3).
 TINY = Geometry(hidden=512, n_q=4, n_kv=2, mlp=1024, layers=3, vocab=2048)
 SMALL = Geometry(hidden=1024, n_q=8, n_kv=2, mlp=3072, layers=4, vocab=8192)
+# Eight kv heads, so that the model still splits over 2, 4 and 8 tensor-parallel ranks.
+KV8 = Geometry(hidden=1024, n_q=16, n_kv=8, mlp=3072, layers=3, vocab=8192)
 
 
 # ---------------------------------------------------------------------------

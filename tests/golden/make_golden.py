@@ -16,6 +16,7 @@ reference, checks the oracle's restatement against it, and stores the
 REFERENCE's outputs:
   tiny_generate.pt   TINY geometry: prompt, greedy tokens, per-step logits
   small_generate.pt  SMALL geometry: same
+  kv8_generate.pt    KV8 geometry (16 q / 8 kv heads: splits over 2, 4 and 8 tensor-parallel ranks): same
   config1_layer.pt   one Qwen3-8B-geometry decoder layer, one decode step at
                      position 1024 over a seeded N(0,1) KV cache: output hidden
                      state, plus checksums of the seeded inputs
@@ -209,4 +210,5 @@ if __name__ == "__main__":
     torch.manual_seed(0)
     gen_generate_fixture(ref_root, O.TINY, "tiny_generate.pt", prompt_len=8, n_new=40, max_seq=64, norm_jitter=0.25)
     gen_generate_fixture(ref_root, O.SMALL, "small_generate.pt", prompt_len=16, n_new=40, max_seq=96, norm_jitter=0.0)
+    gen_generate_fixture(ref_root, O.KV8, "kv8_generate.pt", prompt_len=12, n_new=40, max_seq=96, norm_jitter=0.1)
     gen_config1(ref_root)

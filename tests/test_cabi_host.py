@@ -127,7 +127,7 @@ def test_error_behaviour_follows_the_reference_api(native_lib):
     k.finalize()
     k = _kernel()
     with pytest.raises(NotImplementedError, match="unknown layer"):
-        k._op("gang_linear", [k.new_tensor(dims=(2, 64), name="z")])
+        k._op("moe_topk_softmax_sm100", [k.new_tensor(dims=(2, 64), name="z")])
         k.plan()
     k.finalize()
 
@@ -167,3 +167,179 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_cabi, "LIB_PATH", str(tmp_path / "libb200mk.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         _cabi.load()
+
+
+# ---- the reference's other spellings of the same layers -------------------------------------
+def _weights(geom, layers):
+    z = lambda *sh: torch.zeros(*sh, dtype=torch.bfloat16)
+    w = {"embed": z(geom.vocab, geom.hidden), "lm_head": z(geom.vocab, geom.hidden), "norm": z(geom.hidden)}
+    for i in range(layers):
+        w[f"l{i}.q"], w[f"l{i}.k"], w[f"l{i}.v"] = z(geom.n_q * 128, geom.hidden), z(geom.n_kv * 128, geom.hidden), z(geom.n_kv * 128, geom.hidden)
+        w[f"l{i}.o"], w[f"l{i}.gate"], w[f"l{i}.up"] = z(geom.hidden, geom.n_q * 128), z(geom.mlp, geom.hidden), z(geom.mlp, geom.hidden)
+        w[f"l{i}.down"] = z(geom.hidden, geom.mlp)
+        for n, d in (("ln1", geom.hidden), ("ln2", geom.hidden), ("qn", 128), ("kn", 128)):
+            w[f"l{i}.{n}"] = z(d)
+    return w
+
+
+def _variant_graph(k, variant, layers=2):
+    """The layer-call sequence of the reference's model builder with its split-K projections
+    (python/mirage/mpk/models/qwen3/builder.py:560-700, cc-100 branch: splitk_linear_layer
+    accumulating into the residual stream) or of its driver with USE_GANG=1
+    (demo/qwen3/demo.py:560-1170: gang_rmsnorm / gang_linear / gang attention / fused SiLU)."""
+    geom = mk.Qwen3Geometry(hidden=512, n_q=4, n_kv=2, mlp=1024, layers=layers, vocab=2048)
+    w = _weights(geom, layers)
+    T, R, H, D = k.max_num_batched_tokens, k.max_num_batched_requests, geom.hidden, 128
+    qkv_out = (geom.n_q + 2 * geom.n_kv) * D
+    kc = torch.zeros(layers, k.max_num_pages, k.page_size, geom.n_kv, D, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    cos = torch.zeros(k.max_seq_length, D, dtype=torch.bfloat16)
+    sin = cos.clone()
+    keep = [w, kc, vc, cos, sin]
+    gang = variant == "gang"
+    x = k.attach_input(k.meta_tensors["input_tokens"], "input_token")
+    cos_t, sin_t = k.attach_input(cos, "cos"), k.attach_input(sin, "sin")
+    y = k.new_tensor(dims=(T, H), name="embed_out")
+    rms = k.new_tensor(dims=(T, H), name="rmsnorm_out")
+    attn_in = k.new_tensor(dims=(T, qkv_out), name="attn_in")
+    attn_out = k.new_tensor(dims=(T, geom.n_q * D), name="attn_out")
+    attn_proj = k.new_tensor(dims=(T, H), name="attn_proj_out")
+    mlp_mid = k.new_tensor(dims=(T, 2 * geom.mlp), name="mlp_mid")
+    silu_out = k.new_tensor(dims=(T, geom.mlp), name="silu_mul_out")
+    mlp_out = k.new_tensor(dims=(T, H), name="mlp_out")
+    chunks = 2
+    if gang:
+        lse = k.new_tensor(dims=(T, chunks * geom.n_q), dtype=mk.float32, name="lse")
+        tmp = k.new_tensor(dims=(T, chunks * geom.n_q * D), name="attn_out_tmp")
+        qws = k.new_tensor(dims=(T, geom.n_q * D), name="q_ws")
+        ws = k.new_tensor(dims=(4 * T, H), dtype=mk.float32, name="splitk_ws")
+    k.embed_layer(input=x, weight=k.attach_input(w["embed"], "embed"), output=y, grid_dim=(1, 1, 1), block_dim=(128, 1, 1))
+    x = y
+    for i in range(layers):
+        wq, wk, wv = (k.attach_input(w[f"l{i}.{n}"], f"l{i}{n}") for n in "qkv")
+        wqkv = k.shuffle_tensors([wq, wk, wv], 0, geom.n_kv, name=f"l{i}qkv")
+        wn = k.attach_input(w[f"l{i}.ln1"], f"l{i}ln1")
+        if gang:
+            k.gang_rmsnorm_layer(input=x, weight=wn, output=rms)
+            k.gang_linear_layer(input=rms, weight=wqkv, output=attn_in, tile_n=64, output_stride=qkv_out, m_tiles=1, wgm=0)
+        else:
+            k.rmsnorm_layer(input=x, weight=wn, output=rms, grid_dim=(T, 1, 1), block_dim=(128, 1, 1))
+            k.linear_layer(input=rms, weight=wqkv, output=attn_in, grid_dim=(qkv_out // 64, 1, 1), block_dim=(128, 1, 1))
+        qn, kn = k.attach_input(w[f"l{i}.qn"], f"l{i}qn"), k.attach_input(w[f"l{i}.kn"], f"l{i}kn")
+        kct, vct = k.attach_input(kc[i], f"l{i}kc"), k.attach_input(vc[i], f"l{i}vc")
+        if gang:
+            k.gang_paged_attention_split_kv_layer(input=attn_in, k_cache=kct, v_cache=vct, q_norm=qn, k_norm=kn,
+                                                  cos_pos_embed=cos_t, sin_pos_embed=sin_t, lse=lse, output=tmp,
+                                                  q_workspace=qws, attention_params=(geom.n_q, chunks, geom.n_q * D),
+                                                  block_dim=(256, 1, 1))
+            k.gang_paged_attention_split_kv_merge_layer(lse=lse, output_tmp=tmp, output=attn_out,
+                                                        attention_params=(geom.n_q, D, geom.n_kv, chunks), block_dim=(256, 1, 1))
+        else:
+            k.paged_attention_layer(input=attn_in, k_cache=kct, v_cache=vct, q_norm=qn, k_norm=kn, cos_pos_embed=cos_t,
+                                    sin_pos_embed=sin_t, output=attn_out, grid_dim=(R, geom.n_kv, 1), block_dim=(128, 1, 1))
+        wo = k.attach_input(w[f"l{i}.o"], f"l{i}o")
+        if variant == "splitk":
+            k.splitk_linear_layer(input=attn_out, weight=wo, output=x, grid_dim=(H // 128, 128 * 128 // H, 1), block_dim=(256, 1, 1))
+        elif gang:
+            k.gang_linear_with_residual_layer(input=attn_out, weight=wo, residual=x, output=attn_proj, tile_n=64, output_stride=H)
+            x = attn_proj
+        else:
+            k.linear_with_residual_layer(input=attn_out, weight=wo, residual=x, output=attn_proj, grid_dim=(H // 64, 1, 1), block_dim=(128, 1, 1))
+            x = attn_proj
+        wg, wu = k.attach_input(w[f"l{i}.gate"], f"l{i}g"), k.attach_input(w[f"l{i}.up"], f"l{i}u")
+        tasks = 2 * geom.mlp // 64
+        wgu = k.shuffle_tensors([wg, wu], 0, tasks // 2, name=f"l{i}gu")
+        wn2 = k.attach_input(w[f"l{i}.ln2"], f"l{i}ln2")
+        wd = k.attach_input(w[f"l{i}.down"], f"l{i}d")
+        if gang:
+            k.gang_rmsnorm_layer(input=x, weight=wn2, output=rms)
+            k.gang_linear_silu_layer(input=rms, weight=wgu, output=silu_out, tile_n=64, output_stride=geom.mlp)
+            k.gang_splitk_linear_with_residual_layer(input=silu_out, weight=wd, residual=x, workspace=ws, output=mlp_out,
+                                                     tile_n=64, output_stride=H, k_splits=4)
+            x = mlp_out
+        else:
+            k.rmsnorm_layer(input=x, weight=wn2, output=rms, grid_dim=(T, 1, 1), block_dim=(128, 1, 1))
+            k.linear_layer(input=rms, weight=wgu, output=mlp_mid, grid_dim=(tasks, 1, 1), block_dim=(128, 1, 1))
+            k.silu_mul_layer(input=mlp_mid, output=silu_out, grid_dim=(tasks // 2, 1, 1), block_dim=(128, 1, 1))
+            if variant == "splitk":
+                k.splitk_linear_layer(input=silu_out, weight=wd, output=x, grid_dim=(H // 128, 128 * 128 // H, 1), block_dim=(256, 1, 1))
+            else:
+                k.linear_with_residual_layer(input=silu_out, weight=wd, residual=x, output=mlp_out, grid_dim=(H // 64, 1, 1), block_dim=(128, 1, 1))
+                x = mlp_out
+    return keep
+
+
+def _shape_of(plan):
+    """(kind, n, k, flags) per device op: what the program does, independent of tensor names."""
+    out = []
+    for ln in plan.strip().splitlines():
+        f = ln.split()
+        kv = dict(x.split("=", 1) for x in f[2:] if "=" in x)
+        out.append((f[1], kv["n"], kv["k"], kv["flags"]))
+    return out
+
+
+@pytest.mark.parametrize("R", [1, 4])
+def test_split_k_and_gang_spellings_lower_to_the_plain_program(native_lib, R):
+    plans = {}
+    for variant in ("plain", "splitk", "gang"):
+        k = _kernel(R=R, pages=4 * R, fuse=True)
+        keep = _variant_graph(k, variant)
+        plans[variant] = k.plan()
+        k.finalize()
+        del keep
+    base = _shape_of(plans["plain"])
+    assert [b[0] for b in base] == ["embed"] + (["linear", "attention", "linear", "linear", "linear"] if R <= 2 else
+                                                ["rmsnorm", "linear", "attention", "linear", "rmsnorm", "linear", "linear"]) * 2
+    assert _shape_of(plans["splitk"]) == base
+    assert _shape_of(plans["gang"]) == base
+    assert plans["splitk"].count("accumulates into its output") == 4
+
+
+def test_fused_silu_linear_and_workspace_split_k(native_lib):
+    k = _kernel(R=4, pages=16)
+    T = 4
+    x = k.attach_input(torch.zeros(T, 256, dtype=torch.bfloat16), "x")
+    g, u = k.attach_input(torch.zeros(512, 256, dtype=torch.bfloat16), "g"), k.attach_input(torch.zeros(512, 256, dtype=torch.bfloat16), "u")
+    wgu = k.shuffle_tensors([g, u], 0, 1, name="gu")
+    mid = k.new_tensor(dims=(T, 1024), name="mid")
+    wd = k.attach_input(torch.zeros(256, 512, dtype=torch.bfloat16), "wd")
+    ws = k.new_tensor(dims=(2 * T, 256), name="ws")
+    o1, o2 = k.new_tensor(dims=(T, 256), name="o1"), k.new_tensor(dims=(T, 256), name="o2")
+    k.linear_layer(input=x, weight=wgu, output=mid, grid_dim=(8, 1, 1), block_dim=(128, 1, 1))
+    k.silu_mul_linear_with_residual_layer(input=mid, weight=wd, residual=x, output=o1, grid_dim=(4, 1, 1), block_dim=(256, 1, 1))
+    k.splitk_linear_layer(input=mid, weight=k.attach_input(torch.zeros(256, 1024, dtype=torch.bfloat16), "w2"), output=ws,
+                          grid_dim=(2, 2, 1), block_dim=(256, 1, 1))
+    k.splitk_reduce_layer(workspace=ws, residual=o1, output=o2, k_splits=2, grid_dim=(2, 1, 1), block_dim=(256, 1, 1))
+    plan = k.plan().strip().splitlines()
+    assert [ln.split()[1] for ln in plan] == ["linear", "silu_mul", "linear", "linear"]  # mid has a second reader: no fusion
+    assert "split-k workspace + reduce folded" in plan[3] and "out=o2" in plan[3]
+    k.finalize()
+    k = _kernel(R=4, pages=16)
+    with pytest.raises(NotImplementedError, match="splitk_reduce"):
+        k.splitk_reduce_layer(workspace=k.new_tensor(dims=(8, 64), name="ws"), residual=k.new_tensor(dims=(4, 64), name="r"),
+                              output=k.new_tensor(dims=(4, 64), name="o"), k_splits=2, grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+        k.plan()
+    k.finalize()
+
+
+def test_attention_layer_needs_one_page_per_request(native_lib):
+    k = _kernel(R=2, max_seq=64, page=64, pages=2)
+    kc = k.attach_input(torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16), "kc")
+    vc = k.attach_input(torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16), "vc")
+    qn, kn = k.attach_input(torch.ones(128, dtype=torch.bfloat16), "qn"), k.attach_input(torch.ones(128, dtype=torch.bfloat16), "kn")
+    cs = k.attach_input(torch.zeros(64, 128, dtype=torch.bfloat16), "cos")
+    sn = k.attach_input(torch.zeros(64, 128, dtype=torch.bfloat16), "sin")
+    qkv = k.new_tensor(dims=(2, 8 * 128), name="qkv")
+    out = k.new_tensor(dims=(2, 4 * 128), name="out")
+    k.attention_layer(input=qkv, k_cache=kc, v_cache=vc, q_norm=qn, k_norm=kn, cos_pos_embed=cs, sin_pos_embed=sn,
+                      output=out, grid_dim=(2, 2, 1), block_dim=(128, 1, 1))
+    assert k.plan().split()[1] == "attention"
+    k.finalize()
+    k = _kernel(R=2, max_seq=64, page=16, pages=8)
+    kc = k.attach_input(torch.zeros(8, 16, 2, 128, dtype=torch.bfloat16), "kc")
+    with pytest.raises(NotImplementedError, match="one page per request"):
+        k.attention_layer(input=k.new_tensor(dims=(2, 1024), name="qkv"), k_cache=kc, v_cache=kc, q_norm=qn, k_norm=kn,
+                          cos_pos_embed=cs, sin_pos_embed=sn, output=k.new_tensor(dims=(2, 512), name="o"),
+                          grid_dim=(2, 2, 1), block_dim=(128, 1, 1))
+    k.finalize()

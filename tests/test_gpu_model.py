@@ -248,3 +248,115 @@ def test_full_geometry_layers_against_host_oracle():
     logits, toks = _teacher_forced(geom, w, prompt, torch.tensor(ref_tokens), n_new, page_size=64)
     err, firm = _check_against(logits, toks, ref_logits, torch.tensor(ref_tokens), len(prompt), "8B geometry, 2 layers")
     print(f"8B geometry x2 layers: max logit error {err:.4g}, {firm}/{n_new} firm steps")
+
+
+def _teacher_forced_batch(geom, w_cuda, prompts, ref_tokens, iters, page_size=64, num_layers=None, **kw):
+    """Ragged requests in one batch, one launch per iteration, the reference's tokens forced after
+    each.  Returns per request the logits of its decode steps [n_r, vocab] and its greedy tokens."""
+    B = len(prompts)
+    maxP = max(len(p) for p in prompts)
+    dec = mk.Qwen3Decoder(_geom(geom), w_cuda, max_seq_length=maxP + iters + 2, max_requests=B, page_size=page_size,
+                          keep_logits=True, max_iterations=1, num_layers=num_layers, **kw)
+    dec.set_prompts(prompts)
+    logits = [[] for _ in range(B)]
+    toks = [[] for _ in range(B)]
+    for it in range(iters):
+        dec.run()
+        lg = dec.logits.clone().cpu()
+        for r, p in enumerate(prompts):
+            P = len(p)
+            if it >= P - 1:
+                j = it - (P - 1)
+                logits[r].append(lg[r])
+                toks[r].append(int(dec.tokens[r, P + j]))
+                dec.tokens[r, P + j] = int(ref_tokens[r][P + j])
+    dec.finalize()
+    return [torch.stack(x) for x in logits], toks
+
+
+def test_full_depth_model_32_decode_steps_against_host_oracle():
+    """The benchmarked model itself: Qwen3-8B geometry, all 36 layers, full vocabulary, batch 1,
+    8 prompt tokens + 32 teacher-forced decode steps against the oracle on the host cores.  The
+    seeded weights are drawn on the GPU and copied to the host, so both sides hold the same bytes."""
+    geom = O.QWEN3_8B
+    wd = O.make_weights(geom, 0, device="cuda")
+    w = {k: v.cpu() for k, v in wd.items()}
+    prompt = O.make_prompt(geom, 8, 0)
+    n_new = 32
+    ref = O.TorchRefModel(geom, w, 48)
+    ref_tokens, ref_logits = ref.generate(prompt, n_new)
+    del ref
+    P = len(prompt)
+    dec = mk.Qwen3Decoder(_geom(geom), wd, max_seq_length=P + n_new + 1, max_requests=1, page_size=64, keep_logits=True,
+                          max_iterations=1)
+    dec.set_prompts([prompt])
+    logits, toks = [], []
+    for it in range(P + n_new - 1):
+        dec.run()
+        if it >= P - 1:
+            j = it - (P - 1)
+            logits.append(dec.logits[0].clone().cpu())
+            toks.append(int(dec.tokens[0, P + j]))
+            dec.tokens[0, P + j] = int(ref_tokens[P + j])
+    dec.finalize()
+    err, firm = _check_against(torch.stack(logits), toks, ref_logits, torch.tensor(ref_tokens), P, "8B geometry, 36 layers")
+    print(f"8B geometry x36 layers: max logit error {err:.4g}, {firm}/{n_new} firm steps")
+    assert firm >= n_new // 2, "too few steps with a firm reference margin to call the tokens checked"
+
+
+@pytest.mark.parametrize("B", [5, 20])
+def test_wide_batches_at_full_width_against_host_oracle(B):
+    """Qwen3-8B width and vocabulary, 2 layers, a batch of ragged requests on the stream-K
+    mma.sync path (B = 5) and on the tcgen05 path (B = 20): every request's teacher-forced logits
+    and tokens against its own run of the oracle (decode is batch-invariant)."""
+    geom = O.Geometry(layers=2)
+    wd = O.make_weights(geom, 0, device="cuda")
+    w = {k: v.cpu() for k, v in wd.items()}
+    prompts = [O.make_prompt(geom, 3 + (r * 5) % 7, r) for r in range(B)]
+    iters = 14
+    refs = []
+    for p in prompts:
+        m = O.TorchRefModel(geom, w, 32)
+        refs.append(m.generate(p, iters - (len(p) - 1)))
+    logits, toks = _teacher_forced_batch(geom, wd, prompts, [torch.tensor(t) for t, _ in refs], iters)
+    worst, firm = 0.0, 0
+    for r, p in enumerate(prompts):
+        ref_tokens, ref_logits = refs[r]
+        e, f = _check_against(logits[r], toks[r], ref_logits, torch.tensor(ref_tokens), len(p), f"batch {B} request {r}")
+        worst, firm = max(worst, e), firm + f
+    print(f"8B width x2 layers, batch {B}: max logit error {worst:.4g}, {firm} firm token checks")
+
+
+def test_barrier_counter_wraps_inside_a_launch():
+    """The grid barrier's 32-bit counter is started just below its wrap: a 30-token generation crosses
+    it a few barriers in and must give the same tokens as a run that starts at zero."""
+    geom = O.TINY
+    w = O.make_weights(geom, 0, norm_jitter=0.25)
+    p = O.make_prompt(geom, 6, 0)
+    base, _ = _free_run(geom, w, [p], 24)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    epoch0 = 2**32 // sms - 2
+    dec = mk.Qwen3Decoder(_geom(geom), _cuda(w), max_seq_length=6 + 24, max_requests=1, page_size=16,
+                          test_barrier_epoch=epoch0, timeout_ms=2000)
+    dec.set_prompts([p])
+    dec.run()
+    got = dec.generated(0).cpu().tolist()
+    dec.finalize()
+    assert got == base[0]
+
+
+@pytest.mark.parametrize("cluster", [2, 4])
+@pytest.mark.parametrize("B", [1, 20])
+def test_cluster_first_grid_barrier_gives_the_same_tokens(cluster, B):
+    """The hierarchical grid barrier (thread-block clusters meet in shared memory first) against the flat one."""
+    geom = O.TINY
+    w = O.make_weights(geom, 0, norm_jitter=0.25)
+    prompts = [O.make_prompt(geom, 4 + r % 5, r) for r in range(B)]
+    base, _ = _free_run(geom, w, prompts, 16)
+    dec = mk.Qwen3Decoder(_geom(geom), _cuda(w), max_seq_length=max(len(p) for p in prompts) + 16, max_requests=B,
+                          page_size=16, cluster_size=cluster, timeout_ms=2000)
+    dec.set_prompts(prompts)
+    dec.run()
+    got = [dec.generated(r).cpu().tolist() for r in range(B)]
+    dec.finalize()
+    assert got == base

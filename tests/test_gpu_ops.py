@@ -309,3 +309,92 @@ def test_batch_rows_are_independent():
     for t in range(1, T):
         assert torch.equal(od[t], od[0])
     k.finalize()
+
+
+# ---- the reference's other spellings of the linear layers ----------------------------------
+@pytest.mark.parametrize("T", [1, 5, 24])
+def test_split_k_linear_accumulates_into_its_output(T):
+    """splitk_linear_layer on sm_100: output += input * W^T, the output holding the residual stream
+    (python/mirage/mpk/models/qwen3/builder.py:556-563)."""
+    N, K = 1024, 2048
+    x, w, r = _rand((T, K), 41), _rand((N, K), 42, 0.05), _rand((T, N), 43)
+    k, meta, _ = onepass_kernel(T)
+    od = r.clone().cuda()
+    k.splitk_linear_layer(input=k.attach_input(x.cuda(), "x"), weight=k.attach_input(w.cuda(), "w"),
+                          output=k.attach_input(od, "o"), grid_dim=(N // 128, 128 * 128 // N, 1), block_dim=(256, 1, 1))
+    k.compile()
+    k()
+    bf16_close(od, O.mpk_linear(x, w, residual=r), 1e-2, "split-k linear into the residual stream")
+    k.finalize()
+
+
+def test_split_k_workspace_and_reduce():
+    T, N, K, S = 3, 512, 1024, 4
+    x, w, r = _rand((T, K), 44), _rand((N, K), 45, 0.05), _rand((T, N), 46)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, N, dtype=BF, device="cuda")
+    ws = k.new_tensor(dims=(S * T, N), name="splitk_ws")
+    k.splitk_linear_layer(input=k.attach_input(x.cuda(), "x"), weight=k.attach_input(w.cuda(), "w"), output=ws,
+                          grid_dim=(N // 128, S, 1), block_dim=(256, 1, 1))
+    k.splitk_reduce_layer(workspace=ws, residual=k.attach_input(r.cuda(), "r"), output=k.attach_input(od, "o"),
+                          k_splits=S, grid_dim=(N // 128, 1, 1), block_dim=(256, 1, 1))
+    k.compile()
+    k()
+    bf16_close(od, O.mpk_linear(x, w, residual=r), 1e-2, "split-k workspace + reduce")
+    k.finalize()
+
+
+@pytest.mark.parametrize("T,groups", [(2, 1), (2, 8), (6, 1)])
+def test_silu_mul_linear_with_residual(T, groups):
+    """The fused SiLU*up + down projection layer (persistent_kernel.py:2174): its input row is
+    [gate | up] halves, so the gate/up weight is shuffled in ONE group for it; with more groups the
+    layer still reads halves of whatever the linear before it wrote."""
+    K, I, N = 512, 1024, 384
+    x, wg, wu = _rand((T, K), 47), _rand((I, K), 48, 0.05), _rand((I, K), 49, 0.05)
+    wd, r = _rand((N, I), 50, 0.05), _rand((T, N), 51)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, N, dtype=BF, device="cuda")
+    wgu = k.shuffle_tensors([k.attach_input(wg.cuda(), "wg"), k.attach_input(wu.cuda(), "wu")], 0, groups, "wgu")
+    mid = k.new_tensor(dims=(T, 2 * I), name="mlp_mid")
+    k.linear_layer(input=k.attach_input(x.cuda(), "x"), weight=wgu, output=mid, grid_dim=(2 * I // 64, 1, 1),
+                   block_dim=(128, 1, 1))
+    k.silu_mul_linear_with_residual_layer(input=mid, weight=k.attach_input(wd.cuda(), "wd"),
+                                          residual=k.attach_input(r.cuda(), "r"), output=k.attach_input(od, "o"),
+                                          grid_dim=(N // 64, 1, 1), block_dim=(256, 1, 1))
+    kinds = [ln.split()[1] for ln in k.plan().strip().splitlines()]
+    assert kinds == (["linear", "linear"] if groups == 1 else ["linear", "silu_mul", "linear"])
+    k.compile()
+    k()
+    # the mid tensor as the reference lays it out: `groups` blocks of [gate rows | up rows]
+    per = I // groups
+    wcat = torch.cat([torch.cat((wg[g * per:(g + 1) * per], wu[g * per:(g + 1) * per])) for g in range(groups)])
+    midref = O.mpk_linear(x, wcat)
+    h = O.mpk_silu_mul(midref[:, :I], midref[:, I:])
+    bf16_close(od, O.mpk_linear(h, wd, residual=r), 1e-2, "silu_mul_linear_with_residual")
+    k.finalize()
+
+
+@pytest.mark.parametrize("T", [1, 12])
+def test_gang_spellings_run_the_same_arithmetic(T):
+    """gang_rmsnorm -> gang_linear_silu -> gang_splitk_linear_with_residual: Fleet's MLP half
+    (demo/qwen3/demo.py:925-1075 with USE_GANG and USE_FUSED_SILU), tiling arguments as hints."""
+    K, I = 512, 1024
+    x, wn = _rand((T, K), 52), (1 + 0.3 * _rand((K,), 53).float()).to(BF)
+    wg, wu, wd = _rand((I, K), 54, 0.05), _rand((I, K), 55, 0.05), _rand((K, I), 56, 0.05)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, K, dtype=BF, device="cuda")
+    xt = k.attach_input(x.cuda(), "x")
+    rms = k.new_tensor(dims=(T, K), name="rmsnorm_out")
+    act = k.new_tensor(dims=(T, I), name="silu_mul_out")
+    ws = k.new_tensor(dims=(4 * T, K), dtype=mk.float32, name="splitk_ws")
+    wgu = k.shuffle_tensors([k.attach_input(wg.cuda(), "wg"), k.attach_input(wu.cuda(), "wu")], 0, I // 64, "wgu")
+    k.gang_rmsnorm_layer(input=xt, weight=k.attach_input(wn.cuda(), "wn"), output=rms)
+    k.gang_linear_silu_layer(input=rms, weight=wgu, output=act, tile_n=64, output_stride=I, m_tiles=1, wgm=4)
+    k.gang_splitk_linear_with_residual_layer(input=act, weight=k.attach_input(wd.cuda(), "wd"), residual=xt, workspace=ws,
+                                             output=k.attach_input(od, "o"), tile_n=64, output_stride=K, k_splits=4)
+    k.compile()
+    k()
+    xn = O.mpk_rmsnorm(x, wn)
+    h = O.mpk_silu_mul(O.mpk_linear(xn, wg), O.mpk_linear(xn, wu))
+    bf16_close(od, O.mpk_linear(h, wd, residual=x), 1e-2, "gang MLP half")
+    k.finalize()

@@ -1,7 +1,8 @@
-"""Tensor-parallel decode on 2 GPUs of one box: one process per GPU, weights sharded by
-heads / MLP columns, the two allreduces per layer done inside the megakernel over NVLink
-peer memory.  Teacher-forced logits and tokens against the reference fixture.  Skipped
-with fewer than 2 GPUs."""
+"""Tensor-parallel decode on 2, 4 and 8 GPUs of one box: one process per GPU, weights sharded by
+heads / MLP columns, the two allreduces per layer folded into the row-parallel linears' epilogues
+(fp32 partial sums pushed over NVLink peer memory) and the next layers' input staging.
+Teacher-forced logits and tokens against the fixtures the unmodified reference model produced,
+at the single-GPU tolerance.  Each case is skipped where the box has fewer GPUs."""
 import os
 import socket
 
@@ -13,6 +14,7 @@ from oracle import qwen3_oracle as O
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = 2e-2
 
 
 def _free_port():
@@ -21,62 +23,103 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, ws, port, fixture, n_new, ret):
-    import torch.distributed as dist
+def tp_teacher_forced(rank, ws, fixture, n_new, batch=1, fuse=True, device=None):
+    """Runs on every rank (process group already initialised): the fixture's prompt in `batch`
+    identical requests, the reference's tokens forced after every iteration.  Returns this rank's
+    per-step logits [n_new, batch, vocab] and greedy tokens [n_new][batch]."""
     import fleet_chiplet_megakernel_b200 as mk
-    os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(port)
-    os.environ["NCCL_NVLS_ENABLE"] = "0"
-    torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=ws)
     fx = torch.load(os.path.join(GOLD, fixture))
     geom = O.Geometry(**fx["geometry"])
     w = O.make_weights(geom, fx["seed"], norm_jitter=fx["norm_jitter"])
     g = mk.Qwen3Geometry(hidden=geom.hidden, n_q=geom.n_q, n_kv=geom.n_kv, mlp=geom.mlp, layers=geom.layers,
                          vocab=geom.vocab)
-    mine = mk.shard_qwen3_weights({k: v.cuda() for k, v in w.items()}, ws, rank)
+    dev = device or f"cuda:{rank}"
+    mine = mk.shard_qwen3_weights({k: v.to(dev) for k, v in w.items()}, ws, rank)
     P = len(fx["prompt"])
-    dec = mk.Qwen3Decoder(g, mine, max_seq_length=P + n_new + 1, max_requests=1, page_size=16, keep_logits=True,
-                          max_iterations=1, world_size=ws, rank=rank, device=f"cuda:{rank}", timeout_ms=3000)
-    dec.set_prompts([fx["prompt"]])
+    dec = mk.Qwen3Decoder(g, mine, max_seq_length=P + n_new + 1, max_requests=batch, page_size=16, keep_logits=True,
+                          max_iterations=1, world_size=ws, rank=rank, device=dev, timeout_ms=3000, fuse=fuse)
+    dec.set_prompts([fx["prompt"]] * batch)
     logits, toks = [], []
     ref = fx["tokens"]
     for it in range(P + n_new - 1):
         dec.run()
         if it >= P - 1:
             j = it - (P - 1)
-            logits.append(dec.logits[0].clone().cpu())
-            toks.append(int(dec.tokens[0, P + j]))
-            dec.tokens[0, P + j] = int(ref[P + j])
+            logits.append(dec.logits.clone().cpu())
+            toks.append([int(dec.tokens[r, P + j]) for r in range(batch)])
+            dec.tokens[:, P + j] = int(ref[P + j])
+    plan = dec.mpk.describe()
     dec.finalize()
-    ret[rank] = (torch.stack(logits), toks)
+    return torch.stack(logits), toks, plan
+
+
+def check_tp_result(fixture, n_new, logits, toks):
+    """logits [n_new, batch, vocab], toks [n_new][batch] against the fixture: max error in units of the
+    step's largest |logit|, tokens identical wherever the reference's top-2 margin is firm."""
+    fx = torch.load(os.path.join(GOLD, fixture))
+    ref = fx["logits"][:n_new]
+    P = len(fx["prompt"])
+    scale = ref.float().abs().amax(-1)
+    margin = O.top2_margin(ref)
+    worst, firm = 0.0, 0
+    for b in range(logits.shape[1]):
+        worst = max(worst, O.max_rel_err(logits[:, b], ref))
+        for j in range(n_new):
+            if margin[j] > TOL * scale[j]:
+                firm += 1
+                assert toks[j][b] == int(fx["tokens"][P + j]), f"step {j} request {b}"
+    return worst, firm
+
+
+def _worker(rank, ws, port, fixture, n_new, batch, fuse, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    ret[rank] = tp_teacher_forced(rank, ws, fixture, n_new, batch=batch, fuse=fuse)
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("fixture", ["tiny_generate.pt", "small_generate.pt"])
-def test_tp2_matches_reference_fixture(fixture):
-    ws, n_new = 2, 24
+def _run(ws, fixture, n_new, batch=1, fuse=True, tol=TOL):
+    if torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(ws, _free_port(), fixture, n_new, ret), nprocs=ws, join=True)
-    fx = torch.load(os.path.join(GOLD, fixture))
-    l0, t0 = ret[0]
-    l1, t1 = ret[1]
-    assert torch.equal(l0, l1) and t0 == t1, "ranks disagree on logits or tokens"
-    # Against the single-GPU PyTorch fixture the tensor-parallel run carries one more bf16
-    # rounding per row-parallel linear (the partial sums cross NVLink as bf16, as the
-    # reference's allreduce on bf16 task outputs does), on top of a comparison whose noise
-    # floor is already 0.0196: the fixture's own model re-run with fp64 linears.  Hence
-    # 2.5e-2 here instead of the single-GPU tests' 2e-2; the tokens are still held to the
-    # fixture wherever its top-2 margin exceeds 2e-2.
-    err = O.max_rel_err(l0, fx["logits"][:n_new])
-    assert err <= 2.5e-2, err
-    P = len(fx["prompt"])
-    scale = fx["logits"][:n_new].float().abs().amax(-1)
-    margin = O.top2_margin(fx["logits"][:n_new])
-    for j in range(n_new):
-        if margin[j] > 2e-2 * scale[j]:
-            assert t0[j] == int(fx["tokens"][P + j]), f"step {j}"
-    print(f"TP=2 {fixture}: max logit error {err:.4g}")
+    mp.spawn(_worker, args=(ws, _free_port(), fixture, n_new, batch, fuse, ret), nprocs=ws, join=True)
+    l0, t0, plan = ret[0]
+    for r in range(1, ws):
+        lr, tr, _ = ret[r]
+        assert torch.equal(l0, lr) and t0 == tr, f"rank {r} disagrees with rank 0 on logits or tokens"
+    err, firm = check_tp_result(fixture, n_new, l0, t0)
+    assert err <= tol, f"TP={ws} {fixture}: logits off by {err:.4g}"
+    print(f"TP={ws} batch {batch} {fixture}: max logit error {err:.4g}, {firm} firm token checks")
+    return plan
+
+
+@pytest.mark.parametrize("fixture", ["tiny_generate.pt", "small_generate.pt"])
+def test_tp2_matches_reference_fixture(fixture):
+    plan = _run(2, fixture, 24)
+    assert "allreduce folded" in plan and " allreduce " not in plan  # no stand-alone exchange op is left
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+def test_tp_kv8_matches_reference_fixture(ws):
+    _run(ws, "kv8_generate.pt", 32)
+
+
+@pytest.mark.parametrize("batch", [4, 20])
+def test_tp2_wider_batches(batch):
+    """The stream-K (mma.sync) and tcgen05 paths under tensor parallelism: the rmsnorm task gathers."""
+    _run(2, "kv8_generate.pt", 12, batch=batch)
+
+
+def test_tp2_stand_alone_allreduce_op():
+    """fuse=False keeps every layer as recorded: the allreduce runs as its own device op on the bf16
+    outputs of the row-parallel linears, as the reference's allreduce task does
+    (tasks/ampere/reduction.cuh:139-166).  That is one more bf16 rounding per exchange than the
+    single-GPU model has, hence the wider bound here (the folded path above meets 2e-2)."""
+    plan = _run(2, "tiny_generate.pt", 12, fuse=False, tol=2.5e-2)
+    assert " allreduce " in plan

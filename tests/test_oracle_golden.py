@@ -39,6 +39,10 @@ def test_torch_restatement_matches_reference_small():
     _generate_case("small_generate.pt")
 
 
+def test_torch_restatement_matches_reference_kv8():
+    _generate_case("kv8_generate.pt")
+
+
 def test_task_arithmetic_within_tolerance_of_reference():
     """The megakernel-task arithmetic (fp32 norms) stays inside the 2e-2 logit
     tolerance of the reference PyTorch model under teacher forcing."""

@@ -3,6 +3,7 @@ megakernel's driver does, compute their partial layer outputs with the oracle's 
 arithmetic (residual contributed by rank 0 only, as the reference's row-parallel linears
 do, src/kernel/task_register.cc:553-555) and all-reduce them; the sum must equal the
 unsharded layer.  No GPU."""
+import ctypes as C
 import os
 import socket
 
@@ -70,3 +71,44 @@ def test_two_rank_sharding_and_rank0_residual_sum_to_the_full_layer():
     ret = mgr.dict()
     mp.spawn(_worker, args=(ws, _free_port(), ret), nprocs=ws, join=True)
     assert ret["err"] < 2e-2, ret["err"]
+
+
+def test_exchange_sequence_survives_long_launches_and_the_32_bit_wrap(native_lib):
+    """Exchange numbers keep growing across launches by the number of exchanges each launch really ran
+    (72 per iteration for a 36-layer model): consecutive exchanges alternate between the halves of the
+    region, and nothing a slot can still hold from its earlier uses is mistaken for the awaited number,
+    through a 20 000-iteration launch and across the 32-bit wrap."""
+    lib = native_lib
+    seq, word, stale = C.c_uint32(), C.c_int64(), C.c_int()
+    world, tokens, cols = 8, 4, 4096
+    half_words = world * tokens * cols
+    for total in (0, 5, 2**20 - 3, 2**32 - 72 * 10_000 - 7):   # the last one wraps in the middle of the launch
+        prev_half = None
+        launch = 72 * 20_000
+        # every exchange near the start, the end and the wrap; every 997th in between
+        ks = set(range(1, 400)) | set(range(launch - 400, launch + 1)) | set(range(1, launch, 997))
+        wrap_k = (2**32 - total) % 2**32
+        ks |= {k for k in range(max(1, wrap_k - 200), wrap_k + 200) if 1 <= k <= launch}
+        last = None
+        for k in sorted(ks):
+            assert lib.mk_debug_exchange_sequence(total, k, world, tokens, cols, C.byref(seq), C.byref(word), C.byref(stale)) == 0
+            assert seq.value == (total + k) % 2**32
+            assert word.value == (seq.value & 1) * half_words
+            assert stale.value == 0
+            if last is not None and k == last + 1:
+                assert (seq.value & 1) != prev_half, "consecutive exchanges must use different halves"
+            prev_half, last = seq.value & 1, k
+        # the next launch continues where this one stopped
+        assert lib.mk_debug_exchange_sequence((total + launch) % 2**32, 1, world, tokens, cols, C.byref(seq), None, None) == 0
+        assert seq.value == (total + launch + 1) % 2**32
+
+
+def test_barrier_counter_comparison_is_wrap_safe(native_lib):
+    lib = native_lib
+    grid = 148
+    for epoch in (1, 1000, 2**32 // grid - 1, 2**32 // grid, 2**32 // grid + 1, 2**31 // grid, 181 * 200_000):
+        target = (epoch * grid) % 2**32
+        assert lib.mk_barrier_target_reached(target, epoch, grid) == 1
+        assert lib.mk_barrier_target_reached((target - 1) % 2**32, epoch, grid) == 0
+        assert lib.mk_barrier_target_reached((target - grid) % 2**32, epoch, grid) == 0
+        assert lib.mk_barrier_target_reached((target + 5) % 2**32, epoch, grid) == 1
