@@ -12,7 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200mk.so")
-SOURCES = ["mk_kernel.cu", "mk_runtime.cpp", "mk_noalloc.cu"]
+# mk_kernel_tp.cu and mk_kernel_hier.cu include mk_kernel.cu with other build switches (see its header)
+SOURCES = ["mk_kernel.cu", "mk_kernel_tp.cu", "mk_kernel_hier.cu", "mk_runtime.cpp", "mk_noalloc.cu"]
 HEADERS = ["mk_types.h", os.path.join("..", "..", "include", "b200mk.h")]
 
 
@@ -34,13 +35,28 @@ def needs_build():
 def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-shared", "-Xcompiler", "-fPIC", "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd))
-    subprocess.check_call(cmd)
+        flags = ["-Xptxas", "-v"] + flags
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    # one nvcc per source, side by side (the three builds of the kernel dominate), then one link
+    procs = []
+    for src in SOURCES:
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
+        cmd = [_nvcc()] + flags + ["-c", os.path.join(CSRC, src), "-o", obj]
+        if verbose:
+            print(" ".join(cmd))
+        procs.append((cmd, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    objs = []
+    for cmd, obj, pr in procs:
+        out, _ = pr.communicate()
+        if verbose or pr.returncode != 0:
+            sys.stdout.write(out)
+        if pr.returncode != 0:
+            raise subprocess.CalledProcessError(pr.returncode, cmd)
+        objs.append(obj)
+    subprocess.check_call([_nvcc(), "-shared", "-o", LIB] + objs)
     return LIB
 
 

@@ -19,7 +19,32 @@
 
 #include "mk_types.h"
 
+// This file is compiled three times into one library (see the wrappers mk_kernel_tp.cu and
+// mk_kernel_hier.cu): the persistent kernel runs every op body once per layer out of a cold
+// instruction cache, and code that is merely present in an op (a branch for another
+// configuration, the registers it pins) measurably slows the batch-1 step down.  So the
+// single-GPU kernels carry no tensor-parallel exchange code (+2.8 % when present) and only the
+// kernels launched in thread-block clusters carry the hierarchical grid barrier (+2.0 %).
+//   MK_VARIANT        inner namespace of this compilation: base | tp | hier
+//   MK_WITH_XCHG      1: linear epilogues can push to / input staging can gather from the ranks' exchange regions
+//   MK_HIER_BARRIER   1: cluster-first grid barrier (the kernel must be launched with a cluster dimension)
+#ifndef MK_VARIANT
+#define MK_VARIANT base
+#endif
+#ifndef MK_WITH_XCHG
+#define MK_WITH_XCHG 0
+#endif
+#ifndef MK_HIER_BARRIER
+#define MK_HIER_BARRIER 0
+#endif
+#if MK_WITH_XCHG
+#define MK_XF(op, f) ((op).flags & (f))
+#else
+#define MK_XF(op, f) 0
+#endif
+
 namespace mk {
+namespace MK_VARIANT {
 
 // ------------------------------------------------------------------------------------
 // PTX helpers
@@ -125,8 +150,10 @@ struct Ctx {
   bool dead;                // abort flag seen at the op's barrier (CTA-uniform)
   unsigned ar_seq;          // cross-rank exchanges (allreduce pushes) executed so far in this launch
   unsigned lin_seq;         // linear ops whose barrier has been passed in this launch
+#if MK_HIER_BARRIER
   unsigned nbar;            // grid barriers waited for in this launch (phase of the cluster mbarriers)
-  uint32_t cl_rank, cl_size;  // this CTA's rank in its thread-block cluster, CTAs per cluster (1: no clusters)
+  uint32_t cl_rank, cl_size;  // this CTA's rank in its thread-block cluster, CTAs per cluster
+#endif
   __device__ Ctx(const KParams& p_) : p(p_) {}
   __device__ uint32_t full_bar(int s) const { return smem_addr + p.bar_off + 8 * s; }
   __device__ uint32_t empty_bar(int s) const { return smem_addr + p.bar_off + 8 * (p.num_stages + s); }
@@ -212,6 +239,7 @@ __device__ __forceinline__ bool mbar_wait(const Ctx& c, uint32_t bar, uint32_t p
 //
 // The arrival half on its own: an op that has loads to issue which do not depend on other
 // CTAs arrives first and issues them while the others catch up.
+#if MK_HIER_BARRIER
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
@@ -311,6 +339,47 @@ __device__ __forceinline__ void grid_wait(Ctx& c) {
   c.nbar += 1;
   consumer_sync();
 }
+#else
+__device__ __forceinline__ void grid_arrive(Ctx& c) {
+  consumer_sync();
+  c.epoch += 1;
+  c.arrived = true;
+  // arrive with a release reduction: nothing comes back, polling can start at once
+  if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(c.p.grid_bar) : "memory");
+}
+// The waiting half.  Inlined where values loaded ahead of the barrier must stay in registers
+// (a call would spill them, and a spill waits for the load).
+__device__ __forceinline__ void grid_wait(Ctx& c) {
+  c.arrived = false;
+  if (c.tid == 0) {
+    const unsigned target = c.epoch * gridDim.x;
+    unsigned long long t0 = 0;
+    unsigned spins = 0;
+    // the abort flag is the word behind the counter: one 8-byte load polls both
+    bool dead = false;
+    while (true) {
+      const uint2 v = ld_bar_pair(c.p.grid_bar);
+      if (v.y != 0u) {
+        dead = true;
+        break;
+      }
+      if ((int)(v.x - target) >= 0) break;
+      if (((++spins) & 1023u) == 0) {
+        const unsigned long long now = globaltimer();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > 2 * c.p.timeout_ns) {
+          raise_abort(c, ST_TIMEOUT_GRID, (int)c.epoch, (int)ld_acquire_u32(c.p.grid_bar));
+          dead = true;
+          break;
+        }
+      }
+    }
+    c.flags()[3] = dead ? 1 : 0;
+  }
+  consumer_sync();
+}
+#endif  // MK_HIER_BARRIER
 __device__ __noinline__ void grid_sync(Ctx& c) {
   if (!c.arrived) grid_arrive(c);
   grid_wait(c);
@@ -515,8 +584,14 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int v = v0 + vstep * i;
-    raw[i] = make_uint4(0, 0, 0, 0);
-    if (valid && v < kvec) raw[i] = gather ? xchg_gather8(c, xchg_cur(c), tok, v * 8) : __ldcg(src + v);
+    raw[i] = (valid && v < kvec && !gather) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+  }
+  if (gather) {  // (kept apart from the plain loads above: a call between them would serialise them)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = v0 + vstep * i;
+      if (valid && v < kvec) raw[i] = xchg_gather8(c, xchg_cur(c), tok, v * 8);
+    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -539,6 +614,7 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
 // `gather`: the rows are not read from `in` but summed over the ranks' slots of the latest exchange.
 __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0,
                                      int rows, int T, const uint4* pre_w, bool gather = false) {
+  if (!MK_WITH_XCHG) gather = false;  // (compiled out of the single-GPU build)
   uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3, kvec = K >> 3;
@@ -569,8 +645,14 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int v = vb + i * vstep;
-        val[i] = make_uint4(0, 0, 0, 0);
-        if (valid && v < kvec) val[i] = gather ? xchg_gather8(c, xchg_cur(c), tok0 + tb, v * 8) : __ldcg(src + v);
+        val[i] = (valid && v < kvec && !gather) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
+      }
+      if (gather) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int v = vb + i * vstep;
+          if (valid && v < kvec) val[i] = xchg_gather8(c, xchg_cur(c), tok0 + tb, v * 8);
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -678,15 +760,19 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   const int kRedStride = p.sums_stride;
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
   if (op.flags & F_SILU_MUL) {
-    // rows 0..63 of the tile are gate columns, rows 64..127 the matching up columns
+    // rows 0..63 of the tile are gate columns, rows 64..127 the matching up columns; with F_SILU4 the
+    // weight is laid out for the row-owner path instead: units of 8 rows, [4 gate | 4 up]
     const int half = op.n >> 1;
+    const bool by4 = (op.flags & F_SILU4) != 0;
 #pragma unroll 1
     for (int e = c.tid; e < 64 * ntok; e += kNumConsumers) {
-      const int row = e & 63, tb = e >> 6;
-      const int col = blk * 64 + row;
+      const int idx = e & 63, tb = e >> 6;
+      const int col = blk * 64 + idx;
+      const int row = by4 ? ((idx >> 2) << 3) + (idx & 3) : idx;
+      const int urow = by4 ? row + 4 : row + 64;
       if (col < half) {
         const float g = rbf(red[row * kRedStride + tb]);  // linear output is bf16 before the activation
-        const float u = rbf(red[(row + 64) * kRedStride + tb]);
+        const float u = rbf(red[urow * kRedStride + tb]);
         const float s = rbf(__fdividef(g, 1.0f + __expf(-g)));
         out[(size_t)(tok0 + tb) * op.ld_out + col] = __float2bfloat16_rn(s * u);
       }
@@ -695,7 +781,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   }
   const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
-  const bool push = (op.flags & F_PUSH) != 0;
+  const bool push = MK_XF(op, F_PUSH) != 0;
 #pragma unroll 1
   for (int e = c.tid; e < kTileRows * ntok; e += kNumConsumers) {
     const int row = e & 127, tb = e >> 7;
@@ -706,7 +792,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
       if (with_res) {
         float r;
         if (e < kNumConsumers) r = res0;
-        else if (op.flags & F_GATHER_RES) r = xchg_gather1(c, xchg_cur(c), tok, col);
+        else if (MK_XF(op, F_GATHER_RES)) r = xchg_gather1(c, xchg_cur(c), tok, col);
         else r = __bfloat162float(__ldcg(res + (size_t)tok * op.ld_res + col));
         v += r;
       }
@@ -839,7 +925,7 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
   stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w,
-          (op.flags & F_GATHER_IN) != 0);
+          MK_XF(op, F_GATHER_IN) != 0);
   MK_STAMP(c, 1);
 
   const unsigned total = (unsigned)op.nblk * (unsigned)nkt;
@@ -884,7 +970,7 @@ __device__ __noinline__ void linear_pass(Ctx& c, const OpDesc& op, int tok0, int
       new_blk = false;
       res0 = 0.f;
       if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
-        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+        res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
                                          : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
@@ -988,7 +1074,7 @@ __device__ __noinline__ void linear_pass_wide(Ctx& c, const OpDesc& op, int tok0
       new_blk = false;
       res0 = 0.f;
       if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
-        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+        res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
                                          : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
@@ -1123,7 +1209,7 @@ __device__ __noinline__ void linear_pass_umma(Ctx& c, const OpDesc& op, int tok0
       new_blk = false;
       res0 = 0.f;
       if (res_tok && blk * kTileRows + (c.tid & 127) < op.n)
-        res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
+        res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + (c.tid >> 7), blk * kTileRows + (c.tid & 127))
                                          : __bfloat162float(__ldcg(res_ptr + blk * kTileRows));
     }
     // every warp follows the ring (one arrival per warp and phase keeps the "empty" count
@@ -1238,9 +1324,9 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int kp = nks * kRowsStageK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  if (nks <= 24 && ntok <= 2 && !(op.flags & (F_NORM_IN | F_GATHER_IN))) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
+  if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN) && !MK_XF(op, F_GATHER_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
   else stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w,
-               (op.flags & F_GATHER_IN) != 0);
+               MK_XF(op, F_GATHER_IN) != 0);
   MK_STAMP(c, 1);
   int row0, row1;
   bool any;
@@ -1286,7 +1372,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     float res0 = 0.f;
     const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
     if (with_res && e_live)
-      res0 = (op.flags & F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
+      res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
                                        : __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
     float acc[4][4];  // [2 * tile + (k step & 1)]: two chains per tile, added up at the end
 #pragma unroll
@@ -1360,8 +1446,8 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
       if (e_live) {
 #pragma unroll
         for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + e_tok];
-        if (with_res) v = (p.numerics == NUM_TORCH && !(op.flags & F_PUSH)) ? rbf(v) + res0 : v + res0;
-        if (op.flags & F_PUSH) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
+        if (with_res) v = (p.numerics == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
+        if (MK_XF(op, F_PUSH)) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
         else out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
       }
       if (op.flags & F_ARGMAX) {
@@ -1417,7 +1503,7 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
       for (int g = 0; g < passes; ++g) linear_pass(c, op, g * op.aux3, T, g, (pre && g == 0) ? pre_w : nullptr);
     }
   }
-  if (op.flags & F_PUSH) c.ar_seq += 1;  // every CTA counts the exchange, with or without rows of its own
+  if (MK_XF(op, F_PUSH)) c.ar_seq += 1;  // every CTA counts the exchange, with or without rows of its own
 }
 
 // ------------------------------------------------------------------------------------
@@ -1788,6 +1874,49 @@ __device__ __forceinline__ void attn_l2_ahead(const Ctx& c, const OpDesc& op, co
   }
 }
 
+// Prompt chunks (several tokens of one request in an iteration).  Waits for the op's barrier, then one
+// warp per (token, kv head) pair normalises and rotates the token's new K and stores it, with its V, at
+// the token's own position in the cache; a second grid barrier makes all of them visible.  Returns true
+// when the launch is aborting.  (Both halves of a warp compute the same pair: the shuffles in
+// head_norm_rope use the full mask.)
+__device__ __noinline__ bool attn_barrier_then_append(Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int T) {
+  const KParams& p = c.p;
+  if (op.flags & F_SYNC_BEFORE) {
+    grid_wait(c);
+    if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+    c.dead = c.flags()[3] != 0;
+    if (c.dead) return true;
+  } else if (op_barrier(c, op)) {
+    return true;
+  }
+  const int l16 = c.lane & 15;
+  const bool dbl_k = op.aux0 < 32;
+  const uint4 wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
+#pragma unroll 1
+  for (int pair = blockIdx.x * kNumConsumerWarps + c.warp; pair < T * pl.HKV; pair += gridDim.x * kNumConsumerWarps) {
+    const int t = pair / pl.HKV, h = pair % pl.HKV;
+    const int L = lens[t];
+    if (L <= 0) continue;
+    const int pos = min(L - 1, op.aux2 - 1);
+    const uint4 cs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
+    const uint4 sn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)t * op.ld_in + (size_t)h * (pl.qpk + 2) * kHeadDim;
+    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+    F8 kf;
+    unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
+    kf = head_norm_rope(kf, wk, cs, sn, l16, op.flags, p.numerics, dbl_k);
+    const int pg = __ldcg(p.kv_indices + lens[kAttnLensMax + t] + ((L - 1) >> p.page_shift));
+    if (c.lane < 16) {
+      const size_t dst = ((((size_t)pg << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + h) * kHeadDim;
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = pack8(kf.v);
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+    }
+  }
+  grid_sync(c);
+  c.dead = c.flags()[3] != 0;
+  return c.dead;
+}
+
 // Larger batches: with more (request, kv head) pairs than CTAs and sequences short enough to
 // need no split, a CTA runs 2 or 4 pairs side by side instead of one after the other: its 8
 // warps form groups of 4 or 2, every group is a small copy of the CTA-wide scheme (its warps
@@ -1797,7 +1926,7 @@ __device__ __forceinline__ void attn_l2_ahead(const Ctx& c, const OpDesc& op, co
 __device__ __forceinline__ void group_sync(int g, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(2 + g), "r"(nthreads) : "memory");
 }
-__device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const AttnPlan& pl0, const int* lens, int wpg) {
+__device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const AttnPlan& pl0, const int* lens, int wpg, int T, bool chunked) {
   const KParams& p = c.p;
   const int G = gridDim.x;
   AttnPlan pl = pl0;
@@ -1816,6 +1945,10 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
   float* sm_o = reinterpret_cast<float*>(reinterpret_cast<uint4*>(c.smem + p.x_off) + 4 * 80) + c.warp * 4 * kHeadDim;
   float* sm_ml = reinterpret_cast<float*>(reinterpret_cast<uint4*>(c.smem + p.x_off) + 4 * 80) + kNumConsumerWarps * 4 * kHeadDim;
   bool first = true;
+  if (chunked) {
+    if (attn_barrier_then_append(c, op, pl, lens, T)) return;
+    first = false;
+  }
 #pragma unroll 1
   for (int task = blockIdx.x + G * g;; task += G * ngrp) {
     AttnTask a;
@@ -1851,7 +1984,7 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
-        if (a.p1 == L) {  // append the new token's K and V to the cache
+        if (a.p1 == L && !chunked) {  // append the new token's K and V to the cache
           const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
@@ -1934,12 +2067,24 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const int key = (c.iter << 8) ^ (op.aux0 * 16 + op.aux1);  // iteration and head geometry
   const bool fill = c.attn_iter != key;
   c.attn_iter = key;
+  int* multi = pgs + 16 + 3 + 9;  // [1]: some request has several tokens in this iteration (a prompt chunk)
   if (fill) {
+    if (c.tid == 0) *multi = 0;
+    consumer_sync();
+    // Token t of request r (qo_indptr[r] <= t < qo_indptr[r + 1]) sits at position kv_len(r) - (tokens of r behind
+    // it) - 1: its sequence length, itself included, is what the tasks below call L.
 #pragma unroll 1
-    for (int r = c.tid; r < T; r += kNumConsumers) {
-      const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
-      lens[r] = (last - first - 1) * p.page_size + __ldcg(p.kv_last_page_len + r);
-      lens[kAttnLensMax + r] = first;
+    for (int r = c.tid; r < p.max_reqs; r += kNumConsumers) {
+      const int q0 = __ldcg(p.qo_indptr + r), q1 = min(__ldcg(p.qo_indptr + r + 1), T);
+      if (q1 > q0) {
+        const int first = __ldcg(p.kv_indptr + r), last = __ldcg(p.kv_indptr + r + 1);
+        const int kvlen = (last - first - 1) * p.page_size + __ldcg(p.kv_last_page_len + r);
+        for (int t = q0; t < q1; ++t) {
+          lens[t] = kvlen - (q1 - 1 - t);
+          lens[kAttnLensMax + t] = first;
+        }
+        if (q1 - q0 > 1) *multi = 1;
+      }
     }
     consumer_sync();
   }
@@ -1974,7 +2119,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   // More (request, kv head) pairs than CTAs and no sequence that needs splitting: several pairs per CTA at a time.
   if constexpr (PATH == PATH_UMMA) {
     if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4) {
-      attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4);
+      attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4, T, *multi != 0);
       return;
     }
   }
@@ -1998,10 +2143,18 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
 
   bool first = true;
+  const bool chunked = *multi != 0;
+  if (chunked) {
+    // A prompt chunk: its tokens attend to each other's K/V, which only exist once every token's K has been
+    // normalised, rotated and appended.  So this iteration appends first, for all tokens, behind the op's
+    // own barrier, and meets at one more grid barrier before any row is read (nothing is fetched early).
+    if (attn_barrier_then_append(c, op, pl, lens, T)) return;
+    first = false;
+  }
 #pragma unroll 1
   for (int task = blockIdx.x;; task += G) {
     AttnTask a;
-    attn_prepare(c, op, pl, lens, task, l16, a, first ? pgc : nullptr, fill, first ? geom : nullptr);
+    attn_prepare(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;
@@ -2042,7 +2195,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
-        if (a.p1 == L) {  // the last chunk appends the new token's K and V to the cache
+        if (a.p1 == L && !chunked) {  // the last chunk appends the new token's K and V to the cache
           const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
@@ -2054,7 +2207,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     const uint4 knew = sm_k[l16];
     MK_STAMP(c, 2);
     float m, l, o[8];
-    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, task == (int)blockIdx.x ? pgs : nullptr);
+    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, (task == (int)blockIdx.x && !chunked) ? pgs : nullptr);
     MK_STAMP(c, 3);
     // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
     // elements then combines the position groups of each head
@@ -2158,7 +2311,7 @@ __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   }
   if (op_barrier(c, op)) return;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    if (op.flags & F_GATHER_IN) stage_x(c, nullptr, 0, op.n, kp, op.w, tok, 1, tok + 1, pre ? pre_w : nullptr, true);
+    if (MK_XF(op, F_GATHER_IN)) stage_x(c, nullptr, 0, op.n, kp, op.w, tok, 1, tok + 1, pre ? pre_w : nullptr, true);
     else stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1,
                  pre ? pre_w : nullptr);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
@@ -2280,6 +2433,7 @@ __device__ __noinline__ void op_allreduce(Ctx& c, const OpDesc& op, int T) {
     }
     return;
   }
+#if MK_WITH_XCHG
   const unsigned seq = xchg_next(c);
 #pragma unroll 1
   for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
@@ -2296,6 +2450,7 @@ __device__ __noinline__ void op_allreduce(Ctx& c, const OpDesc& op, int T) {
     reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)row * op.ld_out)[v] = xchg_gather8(c, seq, row, v * 8);
   }
   c.ar_seq += 1;
+#endif  // (the host launches the tensor-parallel build of this kernel whenever world > 1)
 }
 
 // ------------------------------------------------------------------------------------
@@ -2358,7 +2513,11 @@ __device__ __noinline__ int bookkeep_prepare(Ctx& c) {
     p.qo_indptr[nreq] = ntok;
     p.kv_indptr[nreq] = npages;
     const int st = p.step[rid];
-    const int nnew = min(1, p.max_tokens - ntok);
+    // a request still inside its prompt gets a chunk of it (as many tokens as the budget allows), a
+    // decoding one its single token; either may get nothing when the iteration's budget is spent
+    const int left = p.prompt_lengths[rid] - st;
+    const int budget = p.max_tokens - ntok;
+    const int nnew = left > 0 ? min(left, min(p.max_tokens_per_req, budget)) : min(1, budget);
     for (int j = 0; j < nnew; ++j) p.input_tokens[ntok + j] = p.tokens[(size_t)rid * p.max_seq_len + st + j];
     const int need = (st + nnew + p.page_size - 1) / p.page_size;
     const int last = (st + nnew) % p.page_size;
@@ -2379,16 +2538,21 @@ __device__ __noinline__ int bookkeep_prepare(Ctx& c) {
   while (nreq < R && ntok < p.max_tokens) {
     const int rid = p.sched[2];
     if (rid >= p.total_requests) break;
-    if (tail - head <= 0) break;  // no page for a new request yet: admit it later
+    const int nnew = max(1, min(p.prompt_lengths[rid], min(p.max_tokens_per_req, p.max_tokens - ntok)));
+    const int need = (nnew + p.page_size - 1) / p.page_size;
+    if (tail - head < need) break;  // no pages for a new request yet: admit it later
     p.request_ids[nreq] = rid;
     p.qo_indptr[nreq] = ntok;
     p.kv_indptr[nreq] = npages;
-    p.input_tokens[ntok] = p.tokens[(size_t)rid * p.max_seq_len];
-    p.kv_last_page_len[nreq] = 1;
-    p.kv_indices[npages] = p.page_queue[head % p.max_pages];
-    ++head;
-    npages += 1;
-    ntok += 1;
+    for (int j = 0; j < nnew; ++j) p.input_tokens[ntok + j] = p.tokens[(size_t)rid * p.max_seq_len + j];
+    const int last = nnew % p.page_size;
+    p.kv_last_page_len[nreq] = last == 0 ? p.page_size : last;
+    for (int j = 0; j < need; ++j) {
+      p.kv_indices[npages + j] = p.page_queue[head % p.max_pages];
+      ++head;
+    }
+    npages += need;
+    ntok += nnew;
     ++nreq;
     p.sched[2] = rid + 1;
   }
@@ -2759,10 +2923,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
   c.smem = smem_raw + pad;
   c.smem_addr = raw_addr + pad;
   c.epoch = p.bar_epoch0;
+#if MK_HIER_BARRIER
   c.nbar = 0;
   c.cl_size = p.cluster > 1 ? (uint32_t)p.cluster : 1u;
   c.cl_rank = 0;
   if (c.cl_size > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(c.cl_rank));
+#endif
   c.cons_idx = 0;
   c.xphase = 0;
   c.arrived = false;
@@ -2788,8 +2954,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
       mbar_init(c.xfull_bar(s), 1);
     }
     mbar_init(c.done_bar(), 1);
+#if MK_HIER_BARRIER
     mbar_init(c.cl_arrive_bar(), c.cl_size);
     mbar_init(c.cl_open_bar(), 1);
+#endif
     fl[0] = 0;
     fl[1] = 0;
     fl[2] = 0;
@@ -2800,10 +2968,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+#if MK_HIER_BARRIER
   if (c.cl_size > 1) {  // no CTA may arrive on a peer's mbarrier before it is initialised
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
+#endif
   // Tensor memory for the tcgen05 linears (32 or 64 token rows per box): x_rows columns of fp32
   // accumulators, allocated once by warp 0 and freed by it when the CTA leaves.
   constexpr bool use_tmem = PATH == PATH_UMMA;
@@ -2841,21 +3011,36 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
           consumer_sync();
           if (c.tid == 0) {
             int n = 0;
+            const int done_before = p.sched[7];  // iterations completed by earlier kernels of this generation call
+            const int git = done_before + iter;  // this iteration's number within the call
+            bool hand_over = false;
             if (!aborted(c)) {
-              // sched[4] != 0: the last iteration's outputs have not been appended yet
-              if (p.sched[4] != 0) bookkeep_finish(c);
-              p.sched[4] = 0;
-              if (p.max_iters == 0 || iter <= p.max_iters) {
-                n = bookkeep_prepare(c);
-                if (n > 0) p.sched[4] = 1;
+              if (iter == 1 && p.sched[5] > 0) {
+                // prepared by the kernel that handed this iteration over
+                n = p.sched[5];
+                p.sched[5] = 0;
+              } else {
+                // sched[4] != 0: the last iteration's outputs have not been appended yet
+                if (p.sched[4] != 0) bookkeep_finish(c);
+                p.sched[4] = 0;
+                if (p.max_iters == 0 || git <= p.max_iters) {
+                  n = bookkeep_prepare(c);
+                  if (n > 0) p.sched[4] = 1;
+                }
+              }
+              if (n > 0 && (n < p.tok_lo || n > p.tok_hi)) {
+                // not an iteration for this program: leave it prepared and let the host launch the other one
+                p.sched[5] = n;
+                p.sched[7] = git - 1;
+                hand_over = true;
               }
             }
-            if (iter - 1 < p.max_step_times) {
-              p.step_times[2 * (iter - 1)] = globaltimer();
-              p.step_times[2 * (iter - 1) + 1] = (unsigned long long)n;
+            if (!hand_over && git - 1 < p.max_step_times) {
+              p.step_times[2 * (git - 1)] = globaltimer();
+              p.step_times[2 * (git - 1) + 1] = (unsigned long long)n;
             }
-            p.sched[3] = iter - 1;
-            p.ctrl[0] = n > 0 ? n : -1;
+            p.sched[3] = git - 1;
+            p.ctrl[0] = hand_over ? -2 : (n > 0 ? n : -1);
             __threadfence();
           }
         }
@@ -2952,12 +3137,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c.tmem), "r"((uint32_t)p.x_rows) : "memory");
   }
+#if MK_HIER_BARRIER
   if (c.cl_size > 1) {  // a peer may still be storing into this CTA's shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
+#endif
 }
 
+}  // namespace MK_VARIANT
+
+#ifndef MK_VARIANT_SECONDARY
 __global__ void init_state_kernel(KParams p) {
   const int tid = threadIdx.x + blockIdx.x * blockDim.x;
   const int nth = blockDim.x * gridDim.x;
@@ -2974,27 +3164,50 @@ __global__ void init_state_kernel(KParams p) {
     p.sched[2] = 0;
     p.sched[3] = 0;
     p.sched[4] = 0;
+    p.sched[5] = 0;
+    p.sched[6] = 0;
+    p.sched[7] = 0;
   }
 }
 
+#endif
 }  // namespace mk
 
+#define MK_CAT2(a, b) a##b
+#define MK_CAT(a, b) MK_CAT2(a, b)
+
+#ifdef MK_VARIANT_SECONDARY
+// a secondary build only exports its kernel instances
+extern "C" const void* MK_CAT(mk_kernel_variant_, MK_VARIANT)(int path) {
+  switch (path) {
+    case mk::PATH_ROWS: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_ROWS>;
+    case mk::PATH_UMMA: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_UMMA>;
+    default: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_TILES>;
+  }
+}
+#else
 // ------------------------------------------------------------------------------------
 // host-side launch helpers (called by the runtime in mk_runtime.cpp)
 // ------------------------------------------------------------------------------------
+extern "C" const void* mk_kernel_variant_tp(int path);
+extern "C" const void* mk_kernel_variant_hier(int path);
 namespace {
-const void* kernel_for_path(int path) {
-  switch (path) {
-    case mk::PATH_ROWS: return (const void*)mk::megakernel<mk::PATH_ROWS>;
-    case mk::PATH_UMMA: return (const void*)mk::megakernel<mk::PATH_UMMA>;
-    default: return (const void*)mk::megakernel<mk::PATH_TILES>;
+// the build of the kernel a launch needs: tensor-parallel exchange code only when there are peers,
+// the hierarchical barrier only when the launch uses clusters
+const void* kernel_for(const mk::KParams* p) {
+  if (p->cluster > 1) return mk_kernel_variant_hier(p->path);
+  if (p->world > 1) return mk_kernel_variant_tp(p->path);
+  switch (p->path) {
+    case mk::PATH_ROWS: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_ROWS>;
+    case mk::PATH_UMMA: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_UMMA>;
+    default: return (const void*)mk::MK_VARIANT::megakernel<mk::PATH_TILES>;
   }
 }
 }  // namespace
 
-extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes) {
+extern "C" int mk_kernel_max_ctas_per_sm(const mk::KParams* p, int smem_bytes) {
   int n = 0;
-  const void* k = kernel_for_path(path);
+  const void* k = kernel_for(p);
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, k, mk::kNumThreads, smem_bytes) != cudaSuccess) return -1;
   return n;
@@ -3002,7 +3215,7 @@ extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes) {
 
 // Clusters of `cluster` CTAs that can be resident at once (the hierarchical barrier needs all of them).
 extern "C" int mk_kernel_max_clusters(int path, int smem_bytes, int cluster, int grid) {
-  const void* k = kernel_for_path(path);
+  const void* k = mk_kernel_variant_hier(path);
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -3024,7 +3237,7 @@ extern "C" int mk_kernel_max_clusters(int path, int smem_bytes, int cluster, int
 }
 
 extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream) {
-  const void* k = kernel_for_path(p->path);
+  const void* k = kernel_for(p);
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return (int)e;
   void* args[] = {(void*)p};
@@ -3055,3 +3268,4 @@ extern "C" int mk_kernel_init_state(const mk::KParams* p, void* stream) {
   mk::init_state_kernel<<<4, 256, 0, (cudaStream_t)stream>>>(*p);
   return (int)cudaGetLastError();
 }
+#endif  // MK_VARIANT_SECONDARY

@@ -24,7 +24,7 @@
 #include "../../include/b200mk.h"
 #include "mk_types.h"
 
-extern "C" int mk_kernel_max_ctas_per_sm(int path, int smem_bytes);
+extern "C" int mk_kernel_max_ctas_per_sm(const mk::KParams* p, int smem_bytes);
 extern "C" int mk_kernel_max_clusters(int path, int smem_bytes, int cluster, int grid);
 extern "C" int mk_kernel_launch(const mk::KParams* p, int grid, int smem_bytes, void* stream);
 extern "C" int mk_kernel_init_state(const mk::KParams* p, void* stream);
@@ -95,6 +95,23 @@ bool starts_with(const std::string& s, const char* p) { return s.rfind(p, 0) == 
 
 }  // namespace
 
+// A lowered program and what was built for it.  A handle holds one, or two over the same
+// tensors and scheduler state: the primary one, planned for iterations of at most
+// max_num_batched_requests tokens (every request decoding), and, where prompt chunks make
+// iterations wider than that and the width puts the linears on another path, a second one
+// planned for max_num_batched_tokens.  The persistent kernel hands an iteration that is not
+// for its program back to the host, which launches the other one (see mk_wait).
+struct Program {
+  std::vector<PlanOp> plan;
+  bool rows_mode = false;
+  int max_tokens = 0;  // widest iteration it is planned for
+  mk::KParams kp{};
+  int smem_bytes = 0;
+  int64_t weight_bytes = 0;
+  int max_nblk = 1;
+  size_t attn_count_bytes = 0, piece_count_bytes = 0;  // arrival counters, cleared before every kernel launch
+};
+
 struct mk_handle {
   mk_config cfg{};
   std::vector<Tensor> tensors;
@@ -103,6 +120,13 @@ struct mk_handle {
   std::vector<PlanOp> plan;
   bool planned = false, compiled = false, meta_set = false;
   bool rows_mode = false;  // linear layers run row-owner (F_ROWS)
+  // plan / rows_mode / kp / smem_bytes / weight_bytes / max_nblk above and below are the program being
+  // built or, after compile, a copy of the primary program (what the introspection calls describe)
+  Program prog[2];
+  int nprog = 0;
+  int cur_prog = 0;          // program the next kernel of a launch uses
+  int plan_tokens = 0;       // widest iteration the plan being built must serve
+  int force_interleave = 0;  // gate/up weight layout fixed by the primary program (4 or 64), 0 = the plan's own choice
   std::string err;
   void* meta[10] = {};
   int64_t total_requests = 0;
@@ -275,19 +299,22 @@ int plan_graph(mk_handle* h) {
   // rows in its own shared memory: worth it for one or two tokens, beyond that the rows
   // would push the CTA past the small shared-memory carve-out and a separate rmsnorm task
   // with the linear reading activation boxes is faster.
-  const bool fuse_norm = fuse && cfg.max_num_batched_tokens <= 2;
+  const bool fuse_norm = fuse && h->plan_tokens <= 2;
   // One or two tokens: linear layers run row-owner (every CTA owns whole output rows and keeps
   // the token rows resident in shared memory), provided the widest input still leaves room
   // for three weight stages inside the small carve-out.
-  bool rows_mode = cfg.max_num_batched_tokens <= 2;
+  bool rows_mode = h->plan_tokens <= 2;
   for (const RecOp& op : h->nops) {
     if (!rows_mode || !is_linear(op.name)) continue;
     const int wi = op.name == "rmsnorm_linear" ? 2 : 1;
     if ((int)op.t.size() <= wi || !valid_tensor(h, op.t[wi]) || h->tensors[op.t[wi]].ndim != 2) continue;
     const int64_t kpad = (h->tensors[op.t[wi]].dims[1] + mk::kRowsStageK - 1) / mk::kRowsStageK * mk::kRowsStageK;
-    if (cfg.max_num_batched_tokens * (kpad + 8) * 2 + 16 > kRowsXBudget) rows_mode = false;
+    if (h->plan_tokens * (kpad + 8) * 2 + 16 > kRowsXBudget) rows_mode = false;
   }
   h->rows_mode = rows_mode;
+  // layout of fused gate/up weights: [4 gate | 4 up] per 8-row unit for the row-owner path, [64 | 64] per tile
+  // otherwise; a second program over the same weights takes the primary program's layout
+  const int gu_interleave = h->force_interleave ? h->force_interleave : (rows_mode ? 4 : 64);
   const int nops_all = (int)h->nops.size();
   // True when the value layer `i` writes into tensor `tid` is read by layer i+1 only:
   // walk the layers in execution order (wrapping into the next iteration) until the
@@ -443,7 +470,8 @@ int plan_graph(mk_handle* h) {
             prev.flags |= mk::F_SILU_MUL;
             prev.out = tmp;
             prev.note += prev.note.empty() ? "silu_mul fused" : ", silu_mul fused";
-            h->tensors[prev.w].interleave = rows_mode ? 4 : 64;
+            h->tensors[prev.w].interleave = gu_interleave;
+            if (gu_interleave == 4 && !rows_mode) prev.flags |= mk::F_SILU4;
             fused_up = true;
           }
         }
@@ -468,7 +496,8 @@ int plan_graph(mk_handle* h) {
           return h->fail(MK_E_UNSUPPORTED, "%s: the weight must come from shuffle_tensors([gate, up]) and the output width be a multiple of 64", nm.c_str());
         po.flags |= mk::F_SILU_MUL;
         po.note = "silu_mul fused";
-        h->tensors[w].interleave = rows_mode ? 4 : 64;
+        h->tensors[w].interleave = gu_interleave;
+        if (gu_interleave == 4 && !rows_mode) po.flags |= mk::F_SILU4;
       }
       po.type = mk::OP_LINEAR;
       if (rows_mode) po.flags |= mk::F_ROWS;
@@ -513,7 +542,8 @@ int plan_graph(mk_handle* h) {
           po.flags |= mk::F_SILU_MUL;
           po.out = sm.t[1];
           po.note += po.note.empty() ? "silu_mul fused" : ", silu_mul fused";
-          h->tensors[w].interleave = rows_mode ? 4 : 64;
+          h->tensors[w].interleave = gu_interleave;
+        if (gu_interleave == 4 && !rows_mode) po.flags |= mk::F_SILU4;
           ++i;
         }
       }
@@ -855,8 +885,12 @@ int mk_set_profiler(mk_handle* h, void* ptr, int64_t n_entries) {
 // Size of this rank's exchange region for the allreduce layers of the planned graph (0 if none).
 static size_t xchg_bytes(mk_handle* h) {
   int cols = 0;
-  for (const PlanOp& po : h->plan)
-    if (po.type == mk::OP_ALLREDUCE || (po.type == mk::OP_LINEAR && (po.flags & mk::F_PUSH))) cols = std::max(cols, po.n);
+  auto scan = [&](const std::vector<PlanOp>& plan) {
+    for (const PlanOp& po : plan)
+      if (po.type == mk::OP_ALLREDUCE || (po.type == mk::OP_LINEAR && (po.flags & mk::F_PUSH))) cols = std::max(cols, po.n);
+  };
+  scan(h->plan);
+  for (int i = 0; i < h->nprog; ++i) scan(h->prog[i].plan);
   if (cols == 0 || h->cfg.world_size < 2) return 0;
   h->xchg_tokens = h->cfg.max_num_batched_tokens;
   h->xchg_cols = cols;
@@ -899,6 +933,15 @@ int mk_comm_connect(mk_handle* h, const unsigned char* handles, int n) {
   return 0;
 }
 
+// Shape class of an iteration width: which path and activation-box height the linears get.
+static int width_class(int tokens) { return tokens <= 2 ? 2 : (tokens <= 8 ? 8 : (tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64))); }
+// Two programs when prompt chunks make some iterations wider than the decode iterations can be and the
+// two widths put the linears on different paths (otherwise one program planned for the wider one serves all).
+static bool two_programs(const mk_config& c) {
+  return c.mode == MK_MODE_OFFLINE && c.max_num_batched_tokens > c.max_num_batched_requests &&
+         width_class(c.max_num_batched_tokens) != width_class(c.max_num_batched_requests);
+}
+
 int mk_plan(mk_handle* h) {
   if (!h) return MK_E_INVALID;
   const mk_config& c = h->cfg;
@@ -909,6 +952,8 @@ int mk_plan(mk_handle* h) {
   if (c.page_size < 1 || c.max_num_pages < 1 || c.max_seq_length < 2) return h->fail(MK_E_INVALID, "bad paging/sequence limits");
   if (c.page_size & (c.page_size - 1)) return h->fail(MK_E_UNSUPPORTED, "page_size must be a power of two (got %d)", c.page_size);
   if (c.world_size < 1 || c.rank < 0 || c.rank >= c.world_size) return h->fail(MK_E_INVALID, "bad rank/world_size");
+  h->force_interleave = 0;
+  h->plan_tokens = two_programs(c) ? c.max_num_batched_requests : c.max_num_batched_tokens;
   return plan_graph(h);
 }
 
@@ -981,41 +1026,19 @@ int mk_barrier_target_reached(uint32_t counter, uint32_t epoch, uint32_t arrival
   return (int)(counter - epoch * arrivals_per_barrier) >= 0 ? 1 : 0;
 }
 
-int mk_compile(mk_handle* h) {
-  if (!h) return MK_E_INVALID;
-  if (h->compiled) return h->fail(MK_E_STATE, "already compiled");
-  if (!h->meta_set) return h->fail(MK_E_STATE, "mk_set_meta must be called before mk_compile");
-  if (int e = mk_plan(h)) return e;
+// Everything of mk_compile that depends on the width a program is planned for (h->plan_tokens): the
+// shared-memory carve-up, scratch, tensor maps, op descriptors and kernel parameters of the plan in
+// h->plan.  `first`: also allocates the scheduler state the programs of a handle share.
+static int compile_program(mk_handle* h, bool first) {
   const mk_config& cfg = h->cfg;
   cudaError_t ce;
-  int dev = cfg.device;
-  if (dev < 0) {
-    if ((ce = cudaGetDevice(&dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDevice (is a CUDA device present?)");
-  } else if ((ce = cudaSetDevice(dev)) != cudaSuccess) {
-    return h->cuda_fail(ce, "cudaSetDevice");
-  }
-  cudaDeviceProp prop;
-  if ((ce = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDeviceProperties");
-  if (prop.major != 10) return h->fail(MK_E_UNSUPPORTED, "this library only runs on sm_100 (found sm_%d%d)", prop.major, prop.minor);
-  if (!prop.cooperativeLaunch) return h->fail(MK_E_UNSUPPORTED, "device lacks cooperative launch");
-  h->num_sms = prop.multiProcessorCount;
-
-  // 1. runtime-owned tensors (shuffles are filled below)
-  for (auto& t : h->tensors)
-    if (t.owned && !t.ptr)
-      if (int e = h->dmalloc(&t.ptr, t.alloc_bytes())) return e;
-  for (auto& t : h->tensors)
-    if (!t.src.empty())
-      if (int e = materialise_shuffle(h, t)) return e;
-  if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return h->cuda_fail(ce, "shuffle copies");
-
   // 2. shared-memory carve-up: [weight ring: stages x (32 KB of weights + two activation
   // boxes of x_rows token rows)][x region: rows staged by the consumers for a fused input
   // norm, attention scratch][sums block of a tile: 128 x x_rows floats][small scratch]
   // [barriers, flags].  Above 8 tokens nothing is staged by the consumers and the sums
   // block shares the x region.
-  const bool wide = cfg.max_num_batched_tokens > mk::kMaxTokGroup;
-  const int nt = cfg.max_num_batched_tokens;
+  const bool wide = h->plan_tokens > mk::kMaxTokGroup;
+  const int nt = h->plan_tokens;
   const bool rows_mode = h->rows_mode;  // row-owner linears: resident token rows, no activation boxes
   const int x_rows = rows_mode ? 0 : (nt <= 8 ? 8 : (nt <= 16 ? 16 : (nt <= 32 ? 32 : 64)));
   const int stage_bytes = mk::kStageBytes + 2 * x_rows * 128;
@@ -1091,14 +1114,17 @@ int mk_compile(mk_handle* h) {
   kp.bar_off = kp.red_off + kRedBytes;
   h->smem_bytes = kp.bar_off + 1024 + 1024;
   kp.path = rows_mode ? mk::PATH_ROWS : (x_rows >= 32 ? mk::PATH_UMMA : mk::PATH_TILES);
-  const int per_sm = mk_kernel_max_ctas_per_sm(kp.path, h->smem_bytes);
+  kp.rank = cfg.rank;
+  kp.world = cfg.world_size;
+  kp.cluster = 1;
+  const int per_sm = mk_kernel_max_ctas_per_sm(&kp, h->smem_bytes);
   if (per_sm < 1) return h->fail(MK_E_CUDA, "the megakernel does not fit on an SM with %d bytes of shared memory", h->smem_bytes);
   h->grid = h->num_sms;
   if (cfg.num_workers > 0) h->grid = std::min(h->grid, cfg.num_workers);
   // Grid barrier shape: hierarchical (cluster-first) when asked for and every cluster of the grid
   // can be resident at once; otherwise flat.
-  kp.cluster = 1;
   if (cfg.cluster_size == 2 || cfg.cluster_size == 4) {
+    if (cfg.world_size > 1) return h->fail(MK_E_UNSUPPORTED, "the cluster-first grid barrier is only built for single-GPU launches");
     const int cs = cfg.cluster_size;
     const int fit = mk_kernel_max_clusters(kp.path, h->smem_bytes, cs, h->grid / cs * cs);
     if (fit >= 1) {
@@ -1121,11 +1147,12 @@ int mk_compile(mk_handle* h) {
 
   // 3. scratch and state
   const int G = h->grid;
-  const int groups = (cfg.max_num_batched_tokens + min_tpp - 1) / min_tpp;
+  const int groups = (h->plan_tokens + min_tpp - 1) / min_tpp;
   void* p = nullptr;
   if (int e = h->dmalloc(&p, (size_t)groups * G * 2 * mk::kTileRows * kp.sums_stride * 4)) return e;
   kp.partial = (float*)p;
-  h->piece_count_bytes = (size_t)groups * max_nblk * 4;
+  const size_t piece_count_bytes = (size_t)groups * max_nblk * 4;
+  h->piece_count_bytes = piece_count_bytes;
   if (int e = h->dmalloc(&p, h->piece_count_bytes)) return e;
   kp.piece_count = (unsigned*)p;
   kp.piece_stride = max_nblk;
@@ -1136,23 +1163,36 @@ int mk_compile(mk_handle* h) {
       max_qpk = std::max(max_qpk, po.aux1 / po.aux0);
     }
   kp.attn_max_chunks = kAttnMaxChunks;
-  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_tokens * max_hkv * kAttnMaxChunks * max_qpk * (mk::kHeadDim + 2) * 4)) return e;
+  if (int e = h->dmalloc(&p, (size_t)h->plan_tokens * max_hkv * kAttnMaxChunks * max_qpk * (mk::kHeadDim + 2) * 4)) return e;
   kp.attn_part = (float*)p;
-  h->attn_count_bytes = (size_t)cfg.max_num_batched_tokens * max_hkv * 4;
+  h->attn_count_bytes = (size_t)h->plan_tokens * max_hkv * 4;
   if (int e = h->dmalloc(&p, h->attn_count_bytes)) return e;
   kp.attn_count = (unsigned*)p;
-  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_requests * 4)) return e;
-  kp.request_ids = (int*)p;
-  if (int e = h->dmalloc(&p, (size_t)cfg.max_num_pages * 4)) return e;
-  kp.page_queue = (int*)p;
-  if (int e = h->dmalloc(&p, 256)) return e;
-  kp.sched = (int*)p;
-  kp.grid_bar = (unsigned*)p + 16;
-  kp.ctrl = (int*)p + 20;
-  kp.abort_flag = (int*)p + 17;  // beside the barrier counter: one 8-byte load polls both
-  kp.status = (int*)p + 32;
-  if (int e = h->dmalloc(&p, (size_t)kMaxStepTimes * 16)) return e;
-  kp.step_times = (unsigned long long*)p;
+  if (first) {
+    if (int e = h->dmalloc(&p, (size_t)cfg.max_num_batched_requests * 4)) return e;
+    kp.request_ids = (int*)p;
+    if (int e = h->dmalloc(&p, (size_t)cfg.max_num_pages * 4)) return e;
+    kp.page_queue = (int*)p;
+    if (int e = h->dmalloc(&p, 256)) return e;
+    kp.sched = (int*)p;
+    kp.grid_bar = (unsigned*)p + 16;
+    kp.ctrl = (int*)p + 20;
+    kp.abort_flag = (int*)p + 17;  // beside the barrier counter: one 8-byte load polls both
+    kp.status = (int*)p + 32;
+    if (int e = h->dmalloc(&p, (size_t)kMaxStepTimes * 16)) return e;
+    kp.step_times = (unsigned long long*)p;
+  } else {
+    // the scheduler's state is shared by the programs of a handle
+    const mk::KParams& k0 = h->prog[0].kp;
+    kp.request_ids = k0.request_ids;
+    kp.page_queue = k0.page_queue;
+    kp.sched = k0.sched;
+    kp.grid_bar = k0.grid_bar;
+    kp.ctrl = k0.ctrl;
+    kp.abort_flag = k0.abort_flag;
+    kp.status = k0.status;
+    kp.step_times = k0.step_times;
+  }
   kp.max_step_times = kMaxStepTimes;
 
   // 4. the program
@@ -1212,9 +1252,9 @@ int mk_compile(mk_handle* h) {
         h->weight_bytes += (int64_t)units * mk::kUnitRows * d.nkt * mk::kRowsStageK * 2;
         if (po.flags & mk::F_ARGMAX) {
           void* q = nullptr;
-          if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+          if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
           d.amax_val = last_amax_val = (float*)q;
-          if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+          if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
           d.amax_idx = last_amax_idx = (int*)q;
         }
         continue;
@@ -1251,9 +1291,9 @@ int mk_compile(mk_handle* h) {
       h->weight_bytes += (int64_t)d.nblk * d.nkt * mk::kStageBytes;
       if (po.flags & mk::F_ARGMAX) {
         void* q = nullptr;
-        if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+        if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
         d.amax_val = last_amax_val = (float*)q;
-        if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+        if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
         d.amax_idx = last_amax_idx = (int*)q;
       }
     } else if (po.type == mk::OP_ATTN) {
@@ -1265,9 +1305,9 @@ int mk_compile(mk_handle* h) {
       d.sin = tp(po.sin);
     } else if (po.type == mk::OP_ARGMAX_PARTIAL) {
       void* q = nullptr;
-      if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+      if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
       d.amax_val = last_amax_val = (float*)q;
-      if (int e = h->dmalloc(&q, (size_t)cfg.max_num_batched_tokens * po.amax_n * 4)) return e;
+      if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
       d.amax_idx = last_amax_idx = (int*)q;
     } else if (po.type == mk::OP_ARGMAX_REDUCE) {
       d.amax_val = last_amax_val;
@@ -1306,7 +1346,8 @@ int mk_compile(mk_handle* h) {
   kp.kv_last_page_len = (int*)h->meta[9];
   kp.max_seq_len = cfg.max_seq_length;
   kp.max_reqs = cfg.max_num_batched_requests;
-  kp.max_tokens = cfg.max_num_batched_tokens;
+  kp.max_tokens = cfg.max_num_batched_tokens;  // the scheduler's budget per iteration (tok_lo/tok_hi say what this program serves)
+  kp.max_tokens_per_req = cfg.max_num_batched_tokens;
   kp.max_pages = cfg.max_num_pages;
   kp.page_size = cfg.page_size;
   kp.page_shift = 0;
@@ -1328,12 +1369,79 @@ int mk_compile(mk_handle* h) {
   // prefetch_kb > 0 sets it, < 0 turns it off
   const int pf_kb = cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 512 : 0);
   kp.prefetch_tiles = pf_kb > 0 ? std::max(1, pf_kb * 1024 / mk::kStageBytes) : 0;
-  if (h->prof_ptr) {
+  if (h->prof_ptr && first) {  // (the trace describes the primary program's ops)
     const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;
     if (h->prof_entries < need) return h->fail(MK_E_INVALID, "profiler buffer has %lld words, the trace needs %lld", (long long)h->prof_entries, (long long)need);
     kp.prof = (unsigned long long*)h->prof_ptr;
     kp.trace_op = cfg.trace_op - 1;
   }
+  return 0;
+}
+
+int mk_compile(mk_handle* h) {
+  if (!h) return MK_E_INVALID;
+  if (h->compiled) return h->fail(MK_E_STATE, "already compiled");
+  if (!h->meta_set) return h->fail(MK_E_STATE, "mk_set_meta must be called before mk_compile");
+  if (int e = mk_plan(h)) return e;
+  const mk_config& cfg = h->cfg;
+  cudaError_t ce;
+  int dev = cfg.device;
+  if (dev < 0) {
+    if ((ce = cudaGetDevice(&dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDevice (is a CUDA device present?)");
+  } else if ((ce = cudaSetDevice(dev)) != cudaSuccess) {
+    return h->cuda_fail(ce, "cudaSetDevice");
+  }
+  cudaDeviceProp prop;
+  if ((ce = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return h->cuda_fail(ce, "cudaGetDeviceProperties");
+  if (prop.major != 10) return h->fail(MK_E_UNSUPPORTED, "this library only runs on sm_100 (found sm_%d%d)", prop.major, prop.minor);
+  if (!prop.cooperativeLaunch) return h->fail(MK_E_UNSUPPORTED, "device lacks cooperative launch");
+  h->num_sms = prop.multiProcessorCount;
+
+  // 1. runtime-owned tensors (shuffles are filled below)
+  for (auto& t : h->tensors)
+    if (t.owned && !t.ptr)
+      if (int e = h->dmalloc(&t.ptr, t.alloc_bytes())) return e;
+  for (auto& t : h->tensors)
+    if (!t.src.empty())
+      if (int e = materialise_shuffle(h, t)) return e;
+  if ((ce = cudaDeviceSynchronize()) != cudaSuccess) return h->cuda_fail(ce, "shuffle copies");
+
+  // 2. the programs
+  const bool two = two_programs(cfg);
+  if (two && cfg.cluster_size > 1)
+    return h->fail(MK_E_UNSUPPORTED, "cluster_size needs max_num_batched_tokens == max_num_batched_requests (one program)");
+  h->nprog = 0;
+  if (int e = compile_program(h, true)) return e;
+  h->prog[0].plan = h->plan; h->prog[0].rows_mode = h->rows_mode; h->prog[0].max_tokens = h->plan_tokens;
+  h->prog[0].kp = h->kp; h->prog[0].smem_bytes = h->smem_bytes; h->prog[0].weight_bytes = h->weight_bytes;
+  h->prog[0].max_nblk = h->max_nblk;
+  h->prog[0].attn_count_bytes = h->attn_count_bytes; h->prog[0].piece_count_bytes = h->piece_count_bytes;
+  h->nprog = 1;
+  if (two) {
+    h->plan_tokens = cfg.max_num_batched_tokens;
+    h->force_interleave = h->prog[0].rows_mode ? 4 : 64;
+    if (int e = plan_graph(h)) return e;   // (same fusion decisions where they do not depend on the width)
+    if (int e = compile_program(h, false)) return e;
+    h->prog[1].plan = h->plan; h->prog[1].rows_mode = h->rows_mode; h->prog[1].max_tokens = h->plan_tokens;
+    h->prog[1].kp = h->kp; h->prog[1].smem_bytes = h->smem_bytes; h->prog[1].weight_bytes = h->weight_bytes;
+    h->prog[1].max_nblk = h->max_nblk;
+    h->prog[1].attn_count_bytes = h->attn_count_bytes; h->prog[1].piece_count_bytes = h->piece_count_bytes;
+    h->force_interleave = 0;
+    h->nprog = 2;
+    h->prog[0].kp.tok_lo = 1;
+    h->prog[0].kp.tok_hi = h->prog[0].max_tokens;
+    h->prog[1].kp.tok_lo = h->prog[0].max_tokens + 1;
+    h->prog[1].kp.tok_hi = h->prog[1].max_tokens;
+    // the handle's own copies describe the primary program again
+    h->plan = h->prog[0].plan; h->rows_mode = h->prog[0].rows_mode; h->kp = h->prog[0].kp;
+    h->smem_bytes = h->prog[0].smem_bytes; h->weight_bytes = h->prog[0].weight_bytes; h->max_nblk = h->prog[0].max_nblk;
+    h->plan_tokens = h->prog[0].max_tokens;
+  } else {
+    h->prog[0].kp.tok_lo = 1;
+    h->prog[0].kp.tok_hi = 1 << 30;
+    h->kp = h->prog[0].kp;
+  }
+  h->cur_prog = 0;
   h->compiled = true;
   if (cfg.mode == MK_MODE_OFFLINE) return mk_init_requests(h, nullptr);
   return 0;
@@ -1350,6 +1458,33 @@ int mk_init_requests(mk_handle* h, void* stream) {
   return 0;
 }
 
+// One kernel of a generation call: the program's counters and the launch state are reset, then the
+// persistent kernel of that program is launched.
+static int launch_program(mk_handle* h, int idx, void* stream) {
+  Program& P = h->prog[idx];
+  cudaStream_t s = (cudaStream_t)stream;
+  // grid barrier, control word, abort flag and status live in one 256-byte block behind sched[0..15]
+  cudaError_t ce = cudaMemsetAsync((char*)P.kp.sched + 64, 0, 192, s);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  if (P.kp.bar_epoch0 != 0) {
+    // (tests) the counter starts where barrier number bar_epoch0 has just been passed
+    const unsigned start = P.kp.bar_epoch0 * (unsigned)(h->grid / std::max(1, P.kp.cluster));
+    ce = cudaMemcpyAsync(P.kp.grid_bar, &start, 4, cudaMemcpyHostToDevice, s);
+    if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  }
+  // a launch that aborted may have left the arrival counters of its attention chunks and of its
+  // split-k pieces half-way: a finisher that gave up clears its counter while late pieces still add to it
+  ce = cudaMemsetAsync(P.kp.attn_count, 0, P.attn_count_bytes, s);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  ce = cudaMemsetAsync(P.kp.piece_count, 0, P.piece_count_bytes, s);
+  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  // exchange sequence numbers continue where the last kernel stopped (mk_wait adds what it executed)
+  P.kp.xchg_seq_base = h->xchg_total;
+  int e = mk_kernel_launch(&P.kp, h->grid, P.smem_bytes, stream);
+  if (e) return h->cuda_fail((cudaError_t)e, "cooperative launch");
+  return 0;
+}
+
 int mk_launch_async(mk_handle* h, void* stream) {
   if (!h) return MK_E_INVALID;
   if (!h->compiled) return h->fail(MK_E_STATE, "not compiled");
@@ -1357,26 +1492,10 @@ int mk_launch_async(mk_handle* h, void* stream) {
   if (h->poisoned)
     return h->fail(MK_E_STATE, "an earlier tensor-parallel launch aborted: the ranks' exchange sequence numbers may "
                                "differ; finalize this handle on every rank and build a new one");
-  cudaStream_t s = (cudaStream_t)stream;
-  // grid barrier, control word, abort flag and status live in one 256-byte block behind sched[0..15]
-  cudaError_t ce = cudaMemsetAsync((char*)h->kp.sched + 64, 0, 192, s);
+  // a generation call starts with no iteration handed over and none completed (sched[5..7])
+  cudaError_t ce = cudaMemsetAsync(h->prog[0].kp.sched + 5, 0, 12, (cudaStream_t)stream);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
-  if (h->kp.bar_epoch0 != 0) {
-    // (tests) the counter starts where barrier number bar_epoch0 has just been passed
-    const unsigned start = h->kp.bar_epoch0 * (unsigned)(h->grid / std::max(1, h->kp.cluster));
-    ce = cudaMemcpyAsync(h->kp.grid_bar, &start, 4, cudaMemcpyHostToDevice, s);
-    if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
-  }
-  // a launch that aborted may have left the arrival counters of its attention chunks and of its
-  // split-k pieces half-way: a finisher that gave up clears its counter while late pieces still add to it
-  ce = cudaMemsetAsync(h->kp.attn_count, 0, h->attn_count_bytes, s);
-  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
-  ce = cudaMemsetAsync(h->kp.piece_count, 0, h->piece_count_bytes, s);
-  if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
-  // exchange sequence numbers continue where the last launch stopped (mk_wait adds what it executed)
-  h->kp.xchg_seq_base = h->xchg_total;
-  int e = mk_kernel_launch(&h->kp, h->grid, h->smem_bytes, stream);
-  if (e) return h->cuda_fail((cudaError_t)e, "cooperative launch");
+  if (int e = launch_program(h, h->cur_prog, stream)) return e;
   h->launched = true;
   h->in_flight = true;
   return 0;
@@ -1385,29 +1504,36 @@ int mk_launch_async(mk_handle* h, void* stream) {
 int mk_wait(mk_handle* h, void* stream) {
   if (!h) return MK_E_INVALID;
   if (!h->launched) return h->fail(MK_E_STATE, "nothing launched");
-  cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
-  h->in_flight = false;
-  if (ce != cudaSuccess) return h->cuda_fail(ce, "megakernel");
-  int st[24];
-  ce = cudaMemcpy(st, h->kp.abort_flag, sizeof(int) * 24, cudaMemcpyDeviceToHost);
-  if (ce != cudaSuccess) return h->cuda_fail(ce, "status readback");
-  if (h->cfg.world_size > 1) {
-    int done = 0;
-    ce = cudaMemcpy(&done, h->kp.sched + 6, 4, cudaMemcpyDeviceToHost);
+  while (true) {
+    cudaError_t ce = cudaStreamSynchronize((cudaStream_t)stream);
+    h->in_flight = false;
+    if (ce != cudaSuccess) return h->cuda_fail(ce, "megakernel");
+    int st[24];
+    ce = cudaMemcpy(st, h->prog[0].kp.abort_flag, sizeof(int) * 24, cudaMemcpyDeviceToHost);
     if (ce != cudaSuccess) return h->cuda_fail(ce, "status readback");
-    h->xchg_total += (unsigned)done;
+    if (h->cfg.world_size > 1) {
+      int done = 0;
+      ce = cudaMemcpy(&done, h->prog[0].kp.sched + 6, 4, cudaMemcpyDeviceToHost);
+      if (ce != cudaSuccess) return h->cuda_fail(ce, "status readback");
+      h->xchg_total += (unsigned)done;
+    }
+    if (st[0] != 0) {
+      static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
+                                    "producer never got the next iteration", "peer never arrived", "token id out of range",
+                                    "out of KV pages", "a peer rank never delivered its allreduce share"};
+      const int* s = st + 15;  // status sits 15 words behind the abort flag
+      const int code = s[0];
+      if (h->cfg.world_size > 1) h->poisoned = true;
+      return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
+                     (code >= 0 && code < 9) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
+    }
+    // ctrl[0] (3 words behind the abort flag) == -2: the kernel prepared an iteration that belongs to the
+    // handle's other program and ended; that program takes over on the same stream
+    if (st[3] != -2 || h->nprog < 2) return 0;
+    h->cur_prog ^= 1;
+    if (int e = launch_program(h, h->cur_prog, stream)) return e;
+    h->in_flight = true;
   }
-  if (st[0] != 0) {
-    static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
-                                  "producer never got the next iteration", "peer never arrived", "token id out of range",
-                                  "out of KV pages", "a peer rank never delivered its allreduce share"};
-    const int* s = st + 15;  // status sits 15 words behind the abort flag
-    const int code = s[0];
-    if (h->cfg.world_size > 1) h->poisoned = true;
-    return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
-                   (code >= 0 && code < 9) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
-  }
-  return 0;
 }
 
 int mk_launch(mk_handle* h, void* stream) {

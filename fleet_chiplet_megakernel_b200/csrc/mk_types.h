@@ -59,6 +59,7 @@ enum OpFlags : int {
   F_PUSH = 1 << 12,         // linear: the epilogue stores its fp32 sums into every rank's exchange slots instead of `out`
   F_GATHER_IN = 1 << 13,    // linear / rmsnorm: the input rows are the rank-order sum of the latest exchange's slots
   F_GATHER_RES = 1 << 14,   // linear: the residual is the rank-order sum of the latest exchange's slots
+  F_SILU4 = 1 << 15,        // linear with F_SILU_MUL on the tile paths: rows are [4 gate | 4 up] per 8-row unit (the row-owner layout)
 };
 
 enum Numerics : int {
@@ -139,6 +140,12 @@ struct KParams {
   int* kv_indices;
   int* kv_last_page_len;
   int max_seq_len, max_reqs, max_tokens, max_pages, page_size, total_requests;
+  int max_tokens_per_req;  // prompt tokens one request may get per iteration (chunked prefill)
+  // A handle may hold two programs over the same state: one planned for iterations of at most
+  // max_reqs tokens (decode) and one for the larger iterations that carry prompt chunks.  A launch
+  // serves iterations of tok_lo .. tok_hi tokens and hands any other to the host, which launches
+  // the other program (ctrl[0] = -2, the prepared token count in sched[5]).
+  int tok_lo, tok_hi;
   int page_shift;  // log2(page_size): page sizes are powers of two
   long long eos;
   int vocab_limit;  // embedding rows, to refuse out-of-range token ids
@@ -146,11 +153,14 @@ struct KParams {
   int* request_ids;   // [max_reqs]
   int* page_queue;    // ring of free pages [max_pages]
   int* sched;         // [0]=page head [1]=page tail [2]=next request id [3]=iterations done
-                      // [4]=outputs of the last iteration not appended yet [6]=exchanges executed by the last launch
+                      // [4]=outputs of the last iteration not appended yet
+                      // [5]=tokens of an iteration that is prepared but was handed to the other program
+                      // [6]=exchanges executed by the last launch
+                      // [7]=iterations completed by earlier kernels of the current generation call
   unsigned* grid_bar;
   int cluster;            // CTAs per thread-block cluster of the launch (1 = flat grid barrier)
   unsigned bar_epoch0;    // barrier epoch the launch starts at (the counter is preset to match; tests start near the wrap)
-  int* ctrl;          // [0] = active tokens of the iteration, -1 = terminate
+  int* ctrl;          // [0] = active tokens of the iteration, -1 = terminate, -2 = hand over to the other program
   int* abort_flag;
   int* status;        // [0]=code [1]=cta [2]=op [3]=iter [4..7]=detail
   unsigned long long* step_times;

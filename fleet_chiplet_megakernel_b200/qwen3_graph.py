@@ -179,9 +179,13 @@ class Qwen3Decoder:
                  max_iterations: int = 0, num_layers=None, timeout_ms: int = 0, trace: bool = False,
                  trace_op: int = -1, debug_flags: int = 0, world_size: int = 1, rank: int = 0, cluster_size: int = 0,
                  test_barrier_epoch: int = 0, max_num_batched_tokens: int | None = None):
-        """``weights`` are this rank's shard (see ``shard_qwen3_weights``) when world_size > 1."""
+        """``weights`` are this rank's shard (see ``shard_qwen3_weights``) when world_size > 1.
+        ``max_num_batched_tokens`` (default: max_requests, one token per request and iteration) is the
+        token budget of an iteration: above max_requests, a request that is still inside its prompt is fed
+        a chunk of it per iteration (the reference's chunked prefill, persistent_kernel.cuh:380-536)."""
         self.geom, self.device = geom, torch.device(device)
         R = max_requests
+        T = max(R, max_num_batched_tokens or R)
         total = total_requests if total_requests is not None else R
         pages_per_req = math.ceil(max_seq_length / page_size)
         self.max_num_pages = max_num_pages if max_num_pages is not None else R * pages_per_req
@@ -190,8 +194,8 @@ class Qwen3Decoder:
         self.tokens = torch.zeros(total, max_seq_length, dtype=torch.int64, device=dev)
         self.prompt_lengths = torch.zeros(total, dtype=torch.int32, device=dev)
         self.step = torch.zeros(total, dtype=torch.int32, device=dev)
-        self.input_tokens = torch.zeros(R, 1, dtype=torch.int64, device=dev)
-        self.output_tokens = torch.zeros(R, 1, dtype=torch.int64, device=dev)
+        self.input_tokens = torch.zeros(T, 1, dtype=torch.int64, device=dev)
+        self.output_tokens = torch.zeros(T, 1, dtype=torch.int64, device=dev)
         self.num_new_tokens = torch.ones(total, dtype=torch.int32, device=dev)
         self.qo_indptr = torch.zeros(R + 1, dtype=torch.int32, device=dev)
         self.kv_indptr = torch.zeros(R + 1, dtype=torch.int32, device=dev)
@@ -201,12 +205,12 @@ class Qwen3Decoder:
                                    dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.cos, self.sin = rope_tables(geom, max(max_seq_length, 8), dev)
-        self.logits = torch.zeros(R, weights["lm_head"].shape[0], dtype=torch.bfloat16, device=dev) if keep_logits else None
+        self.logits = torch.zeros(T, weights["lm_head"].shape[0], dtype=torch.bfloat16, device=dev) if keep_logits else None
         self.profiler = torch.zeros(1 << 20, dtype=torch.int64, device=dev) if trace else None
         self.mpk = PersistentKernel(
             mode="offline", world_size=world_size, mpi_rank=rank, num_workers=0, num_local_schedulers=0,
             num_remote_schedulers=0, max_seq_length=max_seq_length, max_num_batched_requests=R,
-            max_num_batched_tokens=R, max_num_pages=self.max_num_pages, page_size=page_size,
+            max_num_batched_tokens=T, max_num_pages=self.max_num_pages, page_size=page_size,
             meta_tensors={"step": self.step, "tokens": self.tokens, "input_tokens": self.input_tokens,
                           "output_tokens": self.output_tokens, "num_new_tokens": self.num_new_tokens,
                           "prompt_lengths": self.prompt_lengths, "qo_indptr_buffer": self.qo_indptr,

@@ -155,14 +155,18 @@ class TorchRefModel:
     """Batch-1 restatement of Qwen3ForCausalLM (modeling_qwen3.py:416-567) with
     its contiguous one-page KV cache (:425-446)."""
 
-    def __init__(self, geom: Geometry, weights: dict, max_seq: int, layers: int | None = None):
+    def __init__(self, geom: Geometry, weights: dict, max_seq: int, layers: int | None = None, device: str = "cpu"):
+        """``device``: where the torch ops run.  "cpu" is the oracle; "cuda" runs the very same ops
+        through torch's GPU libraries (the reference's own GPU PyTorch path), which the tests use as a
+        second opinion on how far two executions of the reference model drift apart."""
         self.g = geom
         self.w = weights
+        self.device = device
         self.n_layers = geom.layers if layers is None else layers
         self.max_seq = max_seq
-        self.k_cache = torch.zeros(self.n_layers, max_seq, geom.n_kv, geom.head_dim, dtype=BF16)
+        self.k_cache = torch.zeros(self.n_layers, max_seq, geom.n_kv, geom.head_dim, dtype=BF16, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
-        self.cos, self.sin = rope_tables(geom, max_seq)
+        self.cos, self.sin = rope_tables(geom, max_seq, device)
 
     # Qwen3Attention.forward, modeling_qwen3.py:263-337
     def _attention(self, i, h, pos0):
@@ -209,7 +213,7 @@ class TorchRefModel:
     # Qwen3Model.forward + Qwen3ForCausalLM.forward, modeling_qwen3.py:473-505, 543-567
     @torch.inference_mode()
     def forward(self, token_ids, pos0):
-        h = F.embedding(token_ids, self.w["embed"])
+        h = F.embedding(token_ids.to(self.device), self.w["embed"])
         h = self.forward_hidden(h, pos0)
         h = ref_rmsnorm(h, self.w["norm"])
         return F.linear(h, self.w["lm_head"])
@@ -230,7 +234,7 @@ class TorchRefModel:
             lg = self.forward(torch.tensor(toks), 0)
         for j in range(n_new):
             last = lg[-1]
-            logits_out.append(last.clone())
+            logits_out.append(last.clone().cpu())
             nxt = int(last.argmax(-1))
             toks.append(nxt if forced is None else int(forced[j]))
             if j + 1 < n_new:
