@@ -18,7 +18,7 @@ class MkConfig(C.Structure):
         ("max_seq_length", C.c_int32), ("max_num_batched_requests", C.c_int32),
         ("max_num_batched_tokens", C.c_int32), ("max_num_pages", C.c_int32), ("page_size", C.c_int32),
         ("numerics", C.c_int32), ("eos_token_id", C.c_int64), ("fuse", C.c_int32),
-        ("max_iterations", C.c_int32), ("timeout_ms", C.c_int64), ("device", C.c_int32),
+        ("max_iterations", C.c_int32), ("timeout_ms", C.c_int64), ("device", C.c_int32), ("max_tokens_per_request", C.c_int32),
         ("trace_op", C.c_int32), ("debug_flags", C.c_int32), ("max_stages", C.c_int32), ("prefetch_kb", C.c_int32),
         ("cluster_size", C.c_int32), ("test_barrier_epoch", C.c_uint32), ("reserved", C.c_int32 * 2),
     ]

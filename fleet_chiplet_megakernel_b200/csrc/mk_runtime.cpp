@@ -1347,7 +1347,7 @@ static int compile_program(mk_handle* h, bool first) {
   kp.max_seq_len = cfg.max_seq_length;
   kp.max_reqs = cfg.max_num_batched_requests;
   kp.max_tokens = cfg.max_num_batched_tokens;  // the scheduler's budget per iteration (tok_lo/tok_hi say what this program serves)
-  kp.max_tokens_per_req = cfg.max_num_batched_tokens;
+  kp.max_tokens_per_req = cfg.max_tokens_per_request > 0 ? cfg.max_tokens_per_request : cfg.max_num_batched_tokens;
   kp.max_pages = cfg.max_num_pages;
   kp.page_size = cfg.page_size;
   kp.page_shift = 0;

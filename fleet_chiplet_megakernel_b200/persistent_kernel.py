@@ -111,6 +111,7 @@ class PersistentKernel:
         max_stages: int = 0,
         prefetch_kb: int = 0,
         test_barrier_epoch: int = 0,
+        max_tokens_per_request: int = 0,
     ):
         self.__finalized__ = False
         self._is_compiled = False
@@ -182,6 +183,7 @@ class PersistentKernel:
         cfg.max_iterations = int(max_iterations)
         cfg.timeout_ms = int(timeout_ms)
         cfg.device = -1
+        cfg.max_tokens_per_request = int(max_tokens_per_request)
         cfg.trace_op = int(trace_op) + 1
         # measurement / test aids: explicit arguments only (never read from the environment)
         cfg.debug_flags = int(debug_flags)

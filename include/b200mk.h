@@ -52,6 +52,9 @@ typedef struct mk_config {
   int32_t max_iterations;           /* 0 = run until every request has finished */
   int64_t timeout_ms;               /* bound of every in-kernel wait; 0 = default (4000) */
   int32_t device;                   /* CUDA device ordinal, -1 = current */
+  int32_t max_tokens_per_request;   /* prompt tokens one request may be fed per iteration (the reference's
+                                       MPK_MAX_TOKENS_PER_REQUEST, persistent_kernel.cuh:443-449); 0 = as many as
+                                       the iteration's token budget max_num_batched_tokens allows */
   /* ---- measurement and test aids: not part of the operator API.  Leave them zero in
    * production; mk_create warns on stderr when debug_flags is set, because it changes results. */
   int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer (stored +1: 0 = none) */

@@ -256,7 +256,7 @@ def _teacher_forced_batch(geom, w_cuda, prompts, ref_tokens, iters, page_size=64
     B = len(prompts)
     maxP = max(len(p) for p in prompts)
     dec = mk.Qwen3Decoder(_geom(geom), w_cuda, max_seq_length=maxP + iters + 2, max_requests=B, page_size=page_size,
-                          keep_logits=True, max_iterations=1, num_layers=num_layers, **kw)
+                          keep_logits=True, max_iterations=1, num_layers=num_layers, max_tokens_per_request=1, **kw)
     dec.set_prompts(prompts)
     logits = [[] for _ in range(B)]
     toks = [[] for _ in range(B)]

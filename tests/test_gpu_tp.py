@@ -37,7 +37,8 @@ def tp_teacher_forced(rank, ws, fixture, n_new, batch=1, fuse=True, device=None)
     mine = mk.shard_qwen3_weights({k: v.to(dev) for k, v in w.items()}, ws, rank)
     P = len(fx["prompt"])
     dec = mk.Qwen3Decoder(g, mine, max_seq_length=P + n_new + 1, max_requests=batch, page_size=16, keep_logits=True,
-                          max_iterations=1, world_size=ws, rank=rank, device=dev, timeout_ms=3000, fuse=fuse)
+                          max_iterations=1, world_size=ws, rank=rank, device=dev, timeout_ms=3000, fuse=fuse,
+                          max_tokens_per_request=1)
     dec.set_prompts([fx["prompt"]] * batch)
     logits, toks = [], []
     ref = fx["tokens"]
