@@ -205,18 +205,23 @@ def fixture_parity(rank, world, dev, n_new=20):
         dec.run()
         if it >= P - 1:
             j = it - (P - 1)
-            ours = dec.logits[0].float().cpu()
+            ours = dec.logits[0].float().cpu()  # this rank's slice of the vocabulary (the LM head is sharded by rows)
             ref = ref_lg[j].float()
             scale = float(ref.abs().max())
-            worst = max(worst, float((ours - ref).abs().max()) / scale)
+            off = rank * ours.shape[0]
+            worst = max(worst, float((ours - ref[off:off + ours.shape[0]]).abs().max()) / scale)
             top2 = ref.topk(2).values
             if float(top2[0] - top2[1]) > 2e-2 * scale:
                 firm += 1
                 firm_equal += int(int(dec.tokens[0, P + j]) == int(ref_tok[P + j]))
             dec.tokens[0, P + j] = int(ref_tok[P + j])
     dec.finalize()
-    return {"world": world, "max_rel_err": worst, "tolerance": 2e-2, "steps": n_new, "firm_steps": firm,
-            "firm_tokens_equal": firm_equal == firm, "fixture": "tests/golden/kv8_generate.pt (reference model output)"}
+    import torch.distributed as dist
+    v = torch.tensor([worst, float(firm_equal == firm)], device=dev, dtype=torch.float64)
+    dist.all_reduce(v[:1], op=dist.ReduceOp.MAX)   # every rank checked its own slice of the logits
+    dist.all_reduce(v[1:], op=dist.ReduceOp.MIN)
+    return {"world": world, "max_rel_err": float(v[0]), "tolerance": 2e-2, "steps": n_new, "firm_steps": firm,
+            "firm_tokens_equal": bool(v[1] > 0.5), "fixture": "tests/golden/kv8_generate.pt (reference model output)"}
 
 
 def prefill_iterations(batch, budget):
@@ -340,7 +345,7 @@ def run_ours(args):
         tokens_same = bool(torch.equal(lo, hi))
     # context of the last request admitted (the earlier ones are up to prefill_iters tokens further: negligible)
     ctx = [PROMPT_LEN + W + j for j in range(K)]
-    mean_bytes = statistics.mean(algorithmic_bytes(g, B, [L] * B, world)[0] for L in ctx)
+    mean_bytes = statistics.mean(algorithmic_bytes(g, B, [L] * B, world, lm_head_sharded=True)[0] for L in ctx)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -352,7 +357,7 @@ def run_ours(args):
 
     def frac_of(ms, batch, steps, warm):
         c = [PROMPT_LEN + warm + j for j in range(steps)]
-        mb = statistics.mean(algorithmic_bytes(g, batch, [L] * batch, world)[0] for L in c)
+        mb = statistics.mean(algorithmic_bytes(g, batch, [L] * batch, world, lm_head_sharded=True)[0] for L in c)
         return mb / (ms * 1e-3) / 1e9 / peak
 
     extra = {}
@@ -382,7 +387,7 @@ def run_ours(args):
                    "batch": B, "l2": "inputs larger than L2 (15.1 GB of weights per step)",
                    "timing": "globaltimer stamp per iteration inside the single persistent launch",
                    "numerics": args.numerics, "grid": main["grid"],
-                   "parallelism": f"tp{world} (heads and MLP columns split, LM head replicated)" if world > 1 else "single GPU",
+                   "parallelism": f"tp{world} (heads, MLP columns and LM-head vocabulary rows split)" if world > 1 else "single GPU",
                    "launch_ms_total": main["launch_ms"], "iterations": main["iters"],
                    "prefill": f"chunked, {main['budget']} tokens per iteration: {main['prefill_iters']} iteration(s), "
                               f"{main['prefill_ms']:.2f} ms"},

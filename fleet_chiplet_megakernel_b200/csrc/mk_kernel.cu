@@ -2393,20 +2393,54 @@ __device__ void op_argmax_partial(Ctx& c, const OpDesc& op, int T) {
 __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
   long long* out = reinterpret_cast<long long*>(op.out);
   const bool spread = T > 8;
-  if (!spread && blockIdx.x != 0) return;
-  for (int tok = spread ? blockIdx.x : 0; tok < T; tok += spread ? gridDim.x : 1) {
-    ArgBest b;
-    b.v = -INFINITY;
-    b.i = 0x7fffffff;
-    for (int i = c.tid; i < op.amax_n; i += kNumConsumers) {
-      ArgBest x;
-      x.v = __ldcg(op.amax_val + (size_t)tok * op.amax_n + i);
-      x.i = __ldcg(op.amax_idx + (size_t)tok * op.amax_n + i);
-      b = arg_better(b, x);
+#if MK_WITH_XCHG
+  const bool xrank = (op.flags & F_XRANK) != 0;  // aux0 = first vocabulary index of this rank's shard
+#endif
+  if (spread || blockIdx.x == 0) {
+    for (int tok = spread ? blockIdx.x : 0; tok < T; tok += spread ? gridDim.x : 1) {
+      ArgBest b;
+      b.v = -INFINITY;
+      b.i = 0x7fffffff;
+      for (int i = c.tid; i < op.amax_n; i += kNumConsumers) {
+        ArgBest x;
+        x.v = __ldcg(op.amax_val + (size_t)tok * op.amax_n + i);
+        x.i = __ldcg(op.amax_idx + (size_t)tok * op.amax_n + i);
+        b = arg_better(b, x);
+      }
+      b = block_argmax(c, b);
+#if MK_WITH_XCHG
+      if (xrank && c.tid == 0) {
+        // every rank tells every rank its best (value, global index) of the token; all pick the same winner
+        // (larger value, then lower index: the shards are contiguous, so this is the unsharded rule)
+        const KParams& p = c.p;
+        const unsigned seq = xchg_next(c);
+        if (b.i != 0x7fffffff) b.i += op.aux0;
+        const size_t mine = (size_t)p.xchg_amax_word + ((size_t)p.rank * p.xchg_tokens + tok) * 2;
+        for (int r = 0; r < p.world; ++r) {
+          uint2* w = reinterpret_cast<uint2*>(p.xchg[r]) + mine;
+          st_sys_v2(w, __float_as_uint(b.v), seq);
+          st_sys_v2(w + 1, (uint32_t)b.i, seq);
+        }
+        ArgBest g;
+        g.v = -INFINITY;
+        g.i = 0x7fffffff;
+        for (int r = 0; r < p.world; ++r) {
+          const uint2* w = reinterpret_cast<const uint2*>(p.xchg[p.rank]) + (size_t)p.xchg_amax_word + ((size_t)r * p.xchg_tokens + tok) * 2;
+          if (!xchg_wait_word(c, w, seq, r) || !xchg_wait_word(c, w + 1, seq, r)) break;
+          ArgBest x;
+          x.v = __uint_as_float(ld_sys_v2(w).x);
+          x.i = (int)ld_sys_v2(w + 1).x;
+          g = arg_better(g, x);
+        }
+        b = g;
+      }
+#endif
+      if (c.tid == 0) out[(size_t)tok * op.ld_out] = (b.i == 0x7fffffff) ? -1 : (long long)b.i;
     }
-    b = block_argmax(c, b);
-    if (c.tid == 0) out[(size_t)tok * op.ld_out] = (b.i == 0x7fffffff) ? -1 : (long long)b.i;
   }
+#if MK_WITH_XCHG
+  if (xrank) c.ar_seq += 1;
+#endif
   if (spread) grid_sync(c);
 }
 

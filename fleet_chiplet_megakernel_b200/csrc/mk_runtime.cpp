@@ -144,6 +144,7 @@ struct mk_handle {
   void* xchg_peer[8] = {};
   bool xchg_ready = false;
   int xchg_tokens = 0, xchg_cols = 0;
+  long long xchg_amax_word = 0;
   unsigned xchg_total = 0;      // cross-rank exchanges executed by all completed launches (all ranks advance alike)
   bool in_flight = false;       // launched and not yet waited for
   bool poisoned = false;        // a tensor-parallel launch aborted: the ranks' exchange sequences may differ
@@ -259,6 +260,18 @@ RecOp canonical_op(const RecOp& in) {
     op.name = "splitk_reduce";
   }
   return op;
+}
+
+// argmax_reduce parameters beyond the reference's: [1] = first vocabulary index of this rank's LM-head shard,
+// [2] != 0 = the ranks exchange their (value, index) pairs and take the global best.
+int argmax_across_ranks(mk_handle* h, const RecOp& reduce, PlanOp& rd) {
+  if (reduce.params.size() >= 3 && reduce.params[2] != 0) {
+    if (h->cfg.world_size < 2) return 0;  // a single rank holds the whole vocabulary
+    rd.flags |= mk::F_XRANK;
+    rd.aux0 = (int)reduce.params[1];
+    rd.note = "best (value, index) exchanged between the ranks";
+  }
+  return 0;
 }
 
 // A runtime-owned tensor the lowering itself needs (found by name on a re-plan).
@@ -560,6 +573,7 @@ int plan_graph(mk_handle* h) {
         rd.out = h->nops[i + 2].t.back();
         rd.amax_n = po.amax_n;
         rd.in = -2;  // reads the previous op's partials
+        if (int e = argmax_across_ranks(h, h->nops[i + 2], rd)) return e;
         if (h->tensors[rd.out].dtype != MK_I64) return h->fail(MK_E_INVALID, "argmax output must be int64");
         h->plan.push_back(rd);
         i += 2;
@@ -630,6 +644,8 @@ int plan_graph(mk_handle* h) {
       rd.out = out;
       rd.amax_n = po.amax_n;
       rd.in = -2;
+      if (!single)
+        if (int e = argmax_across_ranks(h, h->nops[i + 1], rd)) return e;
       h->plan.push_back(rd);
       if (!single) ++i;
       continue;
@@ -885,17 +901,21 @@ int mk_set_profiler(mk_handle* h, void* ptr, int64_t n_entries) {
 // Size of this rank's exchange region for the allreduce layers of the planned graph (0 if none).
 static size_t xchg_bytes(mk_handle* h) {
   int cols = 0;
+  bool amax = false;
   auto scan = [&](const std::vector<PlanOp>& plan) {
-    for (const PlanOp& po : plan)
+    for (const PlanOp& po : plan) {
       if (po.type == mk::OP_ALLREDUCE || (po.type == mk::OP_LINEAR && (po.flags & mk::F_PUSH))) cols = std::max(cols, po.n);
+      if (po.type == mk::OP_ARGMAX_REDUCE && (po.flags & mk::F_XRANK)) amax = true;
+    }
   };
   scan(h->plan);
   for (int i = 0; i < h->nprog; ++i) scan(h->prog[i].plan);
-  if (cols == 0 || h->cfg.world_size < 2) return 0;
+  if ((cols == 0 && !amax) || h->cfg.world_size < 2) return 0;
   h->xchg_tokens = h->cfg.max_num_batched_tokens;
-  h->xchg_cols = cols;
-  // two halves x ranks x token rows x columns of 8-byte {value, exchange number} words
-  return (size_t)2 * h->cfg.world_size * h->xchg_tokens * cols * 8;
+  h->xchg_cols = std::max(cols, 8);
+  // two halves x ranks x token rows x columns of 8-byte {value, exchange number} words, then the argmax area
+  h->xchg_amax_word = (long long)2 * h->cfg.world_size * h->xchg_tokens * h->xchg_cols;
+  return ((size_t)h->xchg_amax_word + (size_t)h->cfg.world_size * h->xchg_tokens * 2) * 8;
 }
 
 int mk_comm_prepare(mk_handle* h, unsigned char handle_out[64]) {
@@ -1361,6 +1381,7 @@ static int compile_program(mk_handle* h, bool first) {
     for (int r = 0; r < cfg.world_size; ++r) kp.xchg[r] = (unsigned char*)h->xchg_peer[r];
     kp.xchg_tokens = h->xchg_tokens;
     kp.xchg_cols = h->xchg_cols;
+    kp.xchg_amax_word = h->xchg_amax_word;
   }
   kp.trace_op = -1;
   kp.debug_flags = cfg.debug_flags;

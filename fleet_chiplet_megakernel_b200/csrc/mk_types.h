@@ -59,6 +59,7 @@ enum OpFlags : int {
   F_PUSH = 1 << 12,         // linear: the epilogue stores its fp32 sums into every rank's exchange slots instead of `out`
   F_GATHER_IN = 1 << 13,    // linear / rmsnorm: the input rows are the rank-order sum of the latest exchange's slots
   F_GATHER_RES = 1 << 14,   // linear: the residual is the rank-order sum of the latest exchange's slots
+  F_XRANK = 1 << 16,        // argmax reduce: the per-rank (value, index) pairs of a vocabulary-sharded LM head are exchanged and the global best is taken
   F_SILU4 = 1 << 15,        // linear with F_SILU_MUL on the tile paths: rows are [4 gate | 4 up] per 8-row unit (the row-owner layout)
 };
 
@@ -182,6 +183,9 @@ struct KParams {
   // Exchange s uses the half of the region selected by s & 1 (see xchg_word).
   unsigned char* xchg[8];
   int xchg_tokens, xchg_cols;
+  // behind the slots: [world][xchg_tokens][2] words {logit value, number} {vocabulary index, number} for the
+  // argmax of a vocabulary-sharded LM head (one buffer: a rank cannot be a whole iteration ahead of a peer)
+  long long xchg_amax_word;  // index of that area, in 8-byte words
   unsigned xchg_seq_base;  // exchanges executed by all earlier launches: sequence numbers keep growing (mod 2^32)
   // optional per-op trace of the last iteration: [(op * grid + cta) * 4 + k] globaltimer ns,
   // k = 0 op reached, 1 barrier passed, 2 op done; op == num_ops is the iteration prologue

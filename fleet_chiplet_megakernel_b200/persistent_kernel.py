@@ -554,14 +554,20 @@ class PersistentKernel:
         self.argmax_partial_output_size = input.dim(1) // num_tasks
         self._op("argmax_partial", [input, output_value, output_index], [num_tasks], grid_dim, block_dim)
 
-    def argmax_reduce_layer(self, input: tuple, output: DTensor, grid_dim: tuple, block_dim: tuple):
+    def argmax_reduce_layer(self, input: tuple, output: DTensor, grid_dim: tuple, block_dim: tuple,
+                            vocab_offset: int = 0, across_ranks: bool = False):
+        """persistent_kernel.py:2232-2257.  Beyond the reference (which replicates the LM head on every
+        rank): with ``across_ranks`` the input holds the partials of this rank's slice of the vocabulary,
+        starting at ``vocab_offset``; the ranks exchange their best (value, index) pairs over NVLink inside
+        the kernel and every rank writes the same global token."""
         assert len(input) == 2
         input_value, input_index = input
         assert input_value.num_dims == 2
         assert input_index.num_dims == 2
         assert output.num_dims == 2
         self._op("argmax_reduce", [input_value, input_index, output],
-                 [getattr(self, "argmax_partial_output_size", 0)], grid_dim, block_dim)
+                 [getattr(self, "argmax_partial_output_size", 0), int(vocab_offset), 1 if across_ranks else 0],
+                 grid_dim, block_dim)
 
     # -- compile / run -------------------------------------------------------------------
     def plan(self) -> str:

@@ -41,16 +41,18 @@ def rope_tables(geom: Qwen3Geometry, max_pos: int, device):
     return emb.cos().to(torch.bfloat16).to(device).contiguous(), emb.sin().to(torch.bfloat16).to(device).contiguous()
 
 
-def shard_qwen3_weights(weights: dict, world_size: int, rank: int) -> dict:
+def shard_qwen3_weights(weights: dict, world_size: int, rank: int, shard_lm_head: bool = True) -> dict:
     """Tensor-parallel shard of a full weight dict, as the reference's converter cuts a checkpoint
     (demo/qwen3/models/convert.py:13-28): q/k/v/gate/up by output rows (column parallel), o/down by
-    input columns (row parallel), everything else replicated."""
+    input columns (row parallel), everything else replicated.  Beyond the reference, the LM head is cut by
+    vocabulary rows as well (``shard_lm_head``): the reference replicates it (modeling_qwen3.py:514), which
+    leaves every rank streaming the full 1.2 GB head however many ranks there are."""
     if world_size == 1:
         return weights
     out = {}
     for name, t in weights.items():
         leaf = name.split(".")[-1]
-        if leaf in ("q", "k", "v", "gate", "up"):
+        if leaf in ("q", "k", "v", "gate", "up") or (name == "lm_head" and shard_lm_head and t.shape[0] % world_size == 0):
             out[name] = t.chunk(world_size, dim=0)[rank].contiguous()
         elif leaf in ("o", "down"):
             out[name] = t.chunk(world_size, dim=1)[rank].contiguous()
@@ -150,7 +152,8 @@ def build_qwen3_graph(mpk: PersistentKernel, geom: Qwen3Geometry, weights: dict,
         return x
     w_norm = mpk.attach_input(torch_tensor=weights["norm"], name="model_norm_weight")
     w_proj = mpk.attach_input(torch_tensor=weights["lm_head"], name="lm_head")
-    vocab = weights["lm_head"].shape[0]
+    vocab = weights["lm_head"].shape[0]  # this rank's rows: the whole vocabulary, or its slice of a sharded head
+    head_sharded = ws > 1 and vocab * ws == geom.vocab
     if logits is not None:
         argmax_in = mpk.attach_input(torch_tensor=logits, name="argmax_in")
     else:
@@ -165,7 +168,8 @@ def build_qwen3_graph(mpk: PersistentKernel, geom: Qwen3Geometry, weights: dict,
     mpk.argmax_partial_layer(input=argmax_in, output=(argmax_part_value, argmax_part_index), grid_dim=(tasks, 1, 1),
                              block_dim=(128, 1, 1))
     mpk.argmax_reduce_layer(input=(argmax_part_value, argmax_part_index), output=argmax_out, grid_dim=(1, 1, 1),
-                            block_dim=(128, 1, 1))
+                            block_dim=(128, 1, 1), vocab_offset=mpk.mpi_rank * vocab if head_sharded else 0,
+                            across_ranks=head_sharded)
     return argmax_in
 
 
