@@ -764,6 +764,25 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     // weight is laid out for the row-owner path instead: units of 8 rows, [4 gate | 4 up]
     const int half = op.n >> 1;
     const bool by4 = (op.flags & F_SILU4) != 0;
+    if (ntok > 2 && (op.ld_out & 7) == 0 && (blk + 1) * 64 <= half) {
+      // a thread takes 8 consecutive output columns of one token: lanes of a warp read different tokens
+      // (no bank conflicts in the sums block) and store 16 bytes
+#pragma unroll 1
+      for (int u = c.tid; u < 8 * ntok; u += kNumConsumers) {
+        const int tb = u % ntok, cg = u / ntok;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int idx = cg * 8 + i;
+          const int row = by4 ? ((idx >> 2) << 3) + (idx & 3) : idx;
+          const float g = rbf(red[row * kRedStride + tb]);  // linear output is bf16 before the activation
+          const float up = rbf(red[(by4 ? row + 4 : row + 64) * kRedStride + tb]);
+          v[i] = rbf(__fdividef(g, 1.0f + __expf(-g))) * up;
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)(tok0 + tb) * op.ld_out + blk * 64 + cg * 8) = pack8(v);
+      }
+      return;
+    }
 #pragma unroll 1
     for (int e = c.tid; e < 64 * ntok; e += kNumConsumers) {
       const int idx = e & 63, tb = e >> 6;
@@ -782,6 +801,42 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   const bool with_res = (op.flags & F_RESIDUAL) && (!(op.flags & F_RES_RANK0) || p.rank == 0);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
   const bool push = MK_XF(op, F_PUSH) != 0;
+  // Wide batches: a thread takes 8 consecutive output columns of one token (one 16-byte residual load, one
+  // 16-byte store), four such units per round with their loads issued together: one dependent 2-byte load
+  // per element made the block's finisher the slowest CTA of the op by far (at 64 tokens: 32 round trips).
+  // Lanes of a warp take different tokens, so the sums block is read without bank conflicts.
+  const bool vec = !push && !MK_XF(op, F_GATHER_RES) && ntok > 2 && (op.ld_out & 7) == 0 && (!with_res || (op.ld_res & 7) == 0) &&
+                   ((blk + 1) * kTileRows <= op.n);
+  if (vec) {
+    const int nunits = (kTileRows / 8) * ntok;
+#pragma unroll 1
+    for (int u0 = c.tid; u0 < nunits; u0 += 4 * kNumConsumers) {
+      uint4 rv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int u = u0 + k * kNumConsumers;
+        rv[k] = make_uint4(0, 0, 0, 0);
+        if (with_res && u < nunits)
+          rv[k] = __ldcg(reinterpret_cast<const uint4*>(res + (size_t)(tok0 + u % ntok) * op.ld_res + blk * kTileRows + (u / ntok) * 8));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int u = u0 + k * kNumConsumers;
+        if (u < nunits) {
+          const int tb = u % ntok, cg = u / ntok;
+          float r[8], v[8];
+          unpack8(rv[k], r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] = red[(cg * 8 + i) * kRedStride + tb];
+            if (p.numerics == NUM_TORCH) v[i] = rbf(v[i]);
+            v[i] += r[i];
+          }
+          *reinterpret_cast<uint4*>(out + (size_t)(tok0 + tb) * op.ld_out + blk * kTileRows + cg * 8) = pack8(v);
+        }
+      }
+    }
+  } else
 #pragma unroll 1
   for (int e = c.tid; e < kTileRows * ntok; e += kNumConsumers) {
     const int row = e & 127, tb = e >> 7;
@@ -881,7 +936,7 @@ __device__ __noinline__ void linear_finish_piece(Ctx& c, const OpDesc& op, int b
     consumer_sync();
     __threadfence();
     // all pieces' loads go out together: one L2 round trip instead of one per piece
-#pragma unroll 1
+#pragma unroll 2
     for (int i = c.tid; i < nvec4; i += kNumConsumers) {
       float4 acc = red4[i];
 #pragma unroll 1

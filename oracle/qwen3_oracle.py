@@ -371,3 +371,162 @@ def max_rel_err(a, b):
 def top2_margin(logits):
     t = logits.float().topk(2, dim=-1).values
     return t[..., 0] - t[..., 1]
+
+
+# ---------------------------------------------------------------------------
+# Qwen3-MoE (the reference's MoE demo, demo/qwen3/demo_30B_A3B.py)
+# ---------------------------------------------------------------------------
+# The PyTorch side of that demo is transformers' Qwen3MoeForCausalLM (demo_30B_A3B.py:1, 381-392), a
+# third-party dependency whose source is not part of the reference tree (pinned transformers==4.57.1 in
+# requirements.txt; this image has 5.5.0).  TorchMoeRefModel restates its published algorithm
+# (models/qwen3_moe/modeling_qwen3_moe.py of transformers: Qwen3MoeRMSNorm, Qwen3MoeAttention with eager
+# attention, Qwen3MoeTopKRouter, Qwen3MoeExperts, Qwen3MoeSparseMoeBlock, Qwen3MoeDecoderLayer) and is
+# pinned by tests/golden/make_golden_moe.py, which runs the installed transformers model on the same seeded
+# weights and commits ITS outputs as the fixture.
+@dataclass(frozen=True)
+class MoeGeometry:
+    hidden: int = 2048
+    n_q: int = 32
+    n_kv: int = 4
+    head_dim: int = 128
+    experts: int = 128
+    top_k: int = 8
+    moe_mlp: int = 768
+    layers: int = 48
+    vocab: int = 151936
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    init_std: float = 0.02
+
+    def asdict(self):
+        return asdict(self)
+
+
+QWEN3_30B_A3B = MoeGeometry()
+MOE_TINY = MoeGeometry(hidden=512, n_q=8, n_kv=2, experts=16, top_k=4, moe_mlp=256, layers=2, vocab=2048)
+
+
+def moe_weight_names(g: MoeGeometry):
+    names = [("embed", (g.vocab, g.hidden))]
+    for i in range(g.layers):
+        names += [(f"l{i}.q", (g.n_q * g.head_dim, g.hidden)), (f"l{i}.k", (g.n_kv * g.head_dim, g.hidden)),
+                  (f"l{i}.v", (g.n_kv * g.head_dim, g.hidden)), (f"l{i}.o", (g.hidden, g.n_q * g.head_dim)),
+                  (f"l{i}.router", (g.experts, g.hidden)), (f"l{i}.w13", (g.experts, 2 * g.moe_mlp, g.hidden)),
+                  (f"l{i}.w2", (g.experts, g.hidden, g.moe_mlp))]
+    names.append(("lm_head", (g.vocab, g.hidden)))
+    return names
+
+
+def make_moe_weights(g: MoeGeometry, seed: int = 0, device: str = "cpu", norm_jitter: float = 0.0, router_std: float = 1.0):
+    """bf16 weights ~ N(0, init_std) in the order of ``moe_weight_names``; the router rows are scaled by
+    ``router_std / init_std`` so that the routing logits spread (with N(0, 0.02) rows every expert scores the
+    same to within bf16 noise and the top-k would be decided by rounding)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    w = {}
+    for name, shape in moe_weight_names(g):
+        t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device)
+        std = router_std / math.sqrt(g.hidden) if name.endswith(".router") else g.init_std
+        w[name] = (t * std).to(BF16)
+        del t
+
+    def norm(n):
+        if norm_jitter == 0.0:
+            return torch.ones(n, dtype=BF16, device=device)
+        u = torch.rand(n, generator=gen, dtype=torch.float32, device=device)
+        return (1.0 + norm_jitter * (2 * u - 1)).to(BF16)
+
+    for i in range(g.layers):
+        w[f"l{i}.ln1"], w[f"l{i}.ln2"] = norm(g.hidden), norm(g.hidden)
+        w[f"l{i}.qn"], w[f"l{i}.kn"] = norm(g.head_dim), norm(g.head_dim)
+    w["norm"] = norm(g.hidden)
+    return w
+
+
+def hf_rmsnorm(x, w, eps=1e-6):
+    """Qwen3MoeRMSNorm.forward: fp32 normalisation with eps, cast back, then the weight."""
+    xf = x.float()
+    xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return w * xf.to(x.dtype)
+
+
+def moe_route(logits, top_k):
+    """Qwen3MoeTopKRouter.forward (norm_topk_prob=True): fp32 softmax over the experts, top-k, renormalised."""
+    p = torch.softmax(logits, dtype=torch.float, dim=-1)
+    val, idx = torch.topk(p, top_k, dim=-1)
+    val = val / val.sum(dim=-1, keepdim=True)
+    return val, idx
+
+
+class TorchMoeRefModel:
+    """Batch-1 restatement of transformers' Qwen3MoeForCausalLM (eager attention) with a contiguous KV cache."""
+
+    def __init__(self, g: MoeGeometry, weights: dict, max_seq: int, layers: int | None = None, device: str = "cpu"):
+        self.g, self.w, self.device = g, weights, device
+        self.n_layers = g.layers if layers is None else layers
+        self.k_cache = torch.zeros(self.n_layers, g.n_kv, max_seq, g.head_dim, dtype=BF16, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        d = g.head_dim
+        inv_freq = 1.0 / (g.rope_theta ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
+        freqs = torch.arange(max_seq, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        self.cos, self.sin = emb.cos().to(BF16).to(device), emb.sin().to(BF16).to(device)
+
+    def _attention(self, i, h, pos0):
+        g, w = self.g, self.w
+        n = h.shape[0]
+        x = hf_rmsnorm(h, w[f"l{i}.ln1"], g.eps)
+        q = hf_rmsnorm(F.linear(x, w[f"l{i}.q"]).view(n, g.n_q, g.head_dim), w[f"l{i}.qn"], g.eps).transpose(0, 1)
+        k = hf_rmsnorm(F.linear(x, w[f"l{i}.k"]).view(n, g.n_kv, g.head_dim), w[f"l{i}.kn"], g.eps).transpose(0, 1)
+        v = F.linear(x, w[f"l{i}.v"]).view(n, g.n_kv, g.head_dim).transpose(0, 1)
+        cos, sin = self.cos[pos0:pos0 + n][None], self.sin[pos0:pos0 + n][None]
+        q = (q * cos) + (ref_rotate_half(q) * sin)
+        k = (k * cos) + (ref_rotate_half(k) * sin)
+        self.k_cache[i, :, pos0:pos0 + n] = k
+        self.v_cache[i, :, pos0:pos0 + n] = v
+        L = pos0 + n
+        rep = g.n_q // g.n_kv
+        kk = self.k_cache[i, :, :L].repeat_interleave(rep, dim=0)
+        vv = self.v_cache[i, :, :L].repeat_interleave(rep, dim=0)
+        s = torch.matmul(q, kk.transpose(1, 2)) * (g.head_dim ** -0.5)
+        if n > 1:  # causal mask of a multi-token prefill
+            mask = torch.full((n, L), float("-inf"), device=s.device).triu(diagonal=L - n + 1)
+            s = s + mask.to(s.dtype)[None]
+        p = torch.softmax(s, dim=-1, dtype=torch.float32).to(q.dtype)
+        o = torch.matmul(p, vv).transpose(0, 1).reshape(n, g.n_q * g.head_dim)
+        return F.linear(o, w[f"l{i}.o"])
+
+    def _moe(self, i, h):
+        g, w = self.g, self.w
+        x = hf_rmsnorm(h, w[f"l{i}.ln2"], g.eps)
+        val, idx = moe_route(F.linear(x, w[f"l{i}.router"]), g.top_k)
+        out = torch.zeros_like(x)
+        for e in sorted(set(idx.flatten().tolist())):  # Qwen3MoeExperts.forward: experts in index order
+            slot, tok = torch.where((idx == e).t())
+            cur = x[tok]
+            gate, up = F.linear(cur, w[f"l{i}.w13"][e]).chunk(2, dim=-1)
+            cur = F.linear(F.silu(gate) * up, w[f"l{i}.w2"][e])
+            cur = cur * val[tok, slot, None]
+            out.index_add_(0, tok, cur.to(out.dtype))
+        return out
+
+    @torch.inference_mode()
+    def forward(self, token_ids, pos0):
+        h = F.embedding(token_ids.to(self.device), self.w["embed"])
+        for i in range(self.n_layers):
+            h = h + self._attention(i, h, pos0)
+            h = h + self._moe(i, h)
+        return F.linear(hf_rmsnorm(h, self.w["norm"], self.g.eps), self.w["lm_head"])
+
+    @torch.inference_mode()
+    def generate(self, prompt, n_new, forced=None):
+        toks = prompt.clone().tolist()
+        P = len(toks)
+        logits_out = []
+        lg = self.forward(torch.tensor(toks), 0)
+        for j in range(n_new):
+            last = lg[-1]
+            logits_out.append(last.clone().cpu())
+            toks.append(int(last.argmax(-1)) if forced is None else int(forced[j]))
+            if j + 1 < n_new:
+                lg = self.forward(torch.tensor([toks[-1]]), P + j)
+        return toks, torch.stack(logits_out)

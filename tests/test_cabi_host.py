@@ -343,3 +343,34 @@ def test_attention_layer_needs_one_page_per_request(native_lib):
                           cos_pos_embed=cs, sin_pos_embed=sn, output=k.new_tensor(dims=(2, 512), name="o"),
                           grid_dim=(2, 2, 1), block_dim=(128, 1, 1))
     k.finalize()
+
+
+def test_mpk_wrapper_builds_the_same_program(native_lib):
+    """MPK fills in missing meta tensors and records the Qwen3 graph from checkpoint-named weights."""
+    geom = mk.Qwen3Geometry(hidden=512, n_q=4, n_kv=2, mlp=1024, layers=2, vocab=2048)
+    w = _weights(geom, 2)
+    names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
+             "o": "self_attn.o_proj.weight", "qn": "self_attn.q_norm.weight", "kn": "self_attn.k_norm.weight",
+             "gate": "mlp.gate_proj.weight", "up": "mlp.up_proj.weight", "down": "mlp.down_proj.weight",
+             "ln1": "input_layernorm.weight", "ln2": "post_attention_layernorm.weight"}
+    sd = {"model.embed_tokens.weight": w["embed"], "model.norm.weight": w["norm"], "lm_head.weight": w["lm_head"]}
+    for i in range(2):
+        for s, l in names.items():
+            sd[f"model.layers.{i}.{l}"] = w[f"l{i}.{s}"]
+    kc = [torch.zeros(8, 16, 2, 128, dtype=torch.bfloat16) for _ in range(2)]
+    cos = torch.zeros(64, 128, dtype=torch.bfloat16)
+    mc = mk.MirageModelConfig(hidden_size=512, intermediate_size=1024, vocab_size=2048, local_num_q_heads=4,
+                              local_num_kv_heads=2, head_dim=128, num_layers=2, k_cache=kc, v_cache=[t.clone() for t in kc],
+                              position_embeddings=(cos, cos.clone()), state_dict=sd)
+    meta = mk.MPKMetadata(mode="offline", total_num_requests=2, max_seq_length=64, max_num_batched_requests=2,
+                          max_num_batched_tokens=2, max_num_pages=8, page_size=16, device="cpu", model_config=mc)
+    m = mk.MPK(meta)
+    assert m.tokens.shape == (2, 64) and m.qo_indptr_buffer.shape == (3,)
+    m.build()
+    kinds = [ln.split()[1] for ln in m.persistent_kernel.plan().strip().splitlines()]
+    assert kinds == ["embed"] + ["linear", "attention", "linear", "linear", "linear"] * 2 + ["linear", "argmax_reduce"]
+    with pytest.raises(NotImplementedError):
+        m.load_new_request("a string prompt needs a tokenizer")
+    m.load_new_request([5, 6, 7])
+    assert m.tokens[1, :4].tolist() == [5, 6, 7, 0] and m.prompt_lengths.tolist() == [3, 3]
+    m.finalize()

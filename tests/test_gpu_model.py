@@ -461,3 +461,37 @@ def test_chunked_prefill_with_more_requests_than_slots():
             row = lg[n - len(p)].float()
             gap = abs(float(row[solo[0][n]]) - float(row[batched[r][n]]))
             assert gap <= TOL * float(row.abs().max()), f"request {r} diverges at {n} without a near-tie (gap {gap:.4g})"
+
+
+def test_mpk_wrapper_generates_what_the_decoder_generates():
+    """MPK / MPKMetadata (the reference's serving-side wrapper, python/mirage/mpk/mpk.py): metadata + a model
+    config with checkpoint-named weights, build, compile, run a prompt."""
+    geom = O.TINY
+    w = O.make_weights(geom, 0, norm_jitter=0.25)
+    p = O.make_prompt(geom, 6, 0)
+    base, _ = _free_run(geom, w, [p], 14)
+    long_names = {"q": "self_attn.q_proj.weight", "k": "self_attn.k_proj.weight", "v": "self_attn.v_proj.weight",
+                  "o": "self_attn.o_proj.weight", "qn": "self_attn.q_norm.weight", "kn": "self_attn.k_norm.weight",
+                  "gate": "mlp.gate_proj.weight", "up": "mlp.up_proj.weight", "down": "mlp.down_proj.weight",
+                  "ln1": "input_layernorm.weight", "ln2": "post_attention_layernorm.weight"}
+    sd = {"model.embed_tokens.weight": w["embed"].cuda(), "model.norm.weight": w["norm"].cuda(),
+          "lm_head.weight": w["lm_head"].cuda()}
+    for i in range(geom.layers):
+        for s, l in long_names.items():
+            sd[f"model.layers.{i}.{l}"] = w[f"l{i}.{s}"].cuda()
+    max_seq, page, pages = 20, 16, 2
+    kc = [torch.zeros(pages, page, geom.n_kv, 128, dtype=torch.bfloat16, device="cuda") for _ in range(geom.layers)]
+    vc = [torch.zeros_like(t) for t in kc]
+    cos, sin = mk.qwen3_graph.rope_tables(_geom(geom), max_seq, "cuda")
+    mc = mk.MirageModelConfig(hidden_size=geom.hidden, intermediate_size=geom.mlp, vocab_size=geom.vocab,
+                              local_num_q_heads=geom.n_q, local_num_kv_heads=geom.n_kv, head_dim=128,
+                              num_layers=geom.layers, k_cache=kc, v_cache=vc, position_embeddings=(cos, sin), state_dict=sd)
+    meta = mk.MPKMetadata(mode="offline", total_num_requests=1, max_seq_length=max_seq, max_num_batched_requests=1,
+                          max_num_batched_tokens=8, max_num_pages=pages, page_size=page, model_config=mc,
+                          eos_token_id=0x7FFFFFFF)
+    m = mk.MPK(meta)
+    m.build()
+    m.compile()
+    out = m.run(p)
+    m.finalize()
+    assert out[0].cpu().tolist() == base[0]

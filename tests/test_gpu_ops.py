@@ -398,3 +398,37 @@ def test_gang_spellings_run_the_same_arithmetic(T):
     h = O.mpk_silu_mul(O.mpk_linear(xn, wg), O.mpk_linear(xn, wu))
     bf16_close(od, O.mpk_linear(h, wd, residual=x), 1e-2, "gang MLP half")
     k.finalize()
+
+
+@pytest.mark.parametrize("T", [2, 9])
+def test_mlp_half_written_in_the_fleet_dsl(T):
+    """The MLP half of a layer through the task DSL (decorated op functions on a fleet.Graph)."""
+    import fleet_chiplet_megakernel_b200.fleet as fleet
+    K, I = 512, 1024
+    x, wn = _rand((T, K), 61), (1 + 0.3 * _rand((K,), 62).float()).to(BF)
+    wg, wu, wd = _rand((I, K), 63, 0.05), _rand((I, K), 64, 0.05), _rand((K, I), 65, 0.05)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, K, dtype=BF, device="cuda")
+
+    @fleet.task(level="cu")
+    def norm(a, w, o):
+        return fleet.ops.rmsnorm(a, w, o)
+
+    @fleet.task(level="xcd", tiling="split_k")
+    def down(a, w, o, r):
+        return fleet.ops.linear(a, w, o, residual=r, strategy=fleet.strategy_from_meta(fleet.get_meta(down)))
+
+    g = fleet.Graph(k)
+    xt = g.input(x.cuda(), "x")
+    rms = g.intermediate((T, K), name="rmsnorm_out")
+    act = g.intermediate((T, I), name="silu_mul_out")
+    wgu = g.shuffle_inputs([g.input(wg.cuda(), "wg"), g.input(wu.cuda(), "wu")], I // 64, "wgu")
+    norm(xt, g.input(wn.cuda(), "wn"), rms)
+    fleet.ops.linear_silu(rms, wgu, act)
+    down(act, g.input(wd.cuda(), "wd"), g.input(od, "o"), xt)
+    k.compile()
+    k()
+    xn = O.mpk_rmsnorm(x, wn)
+    h = O.mpk_silu_mul(O.mpk_linear(xn, wg), O.mpk_linear(xn, wu))
+    bf16_close(od, O.mpk_linear(h, wd, residual=x), 1e-2, "MLP half through the DSL")
+    k.finalize()

@@ -87,3 +87,27 @@ def test_single_layer_config_matches_reference():
 def test_argmax_tie_rule():
     lg = torch.tensor([1.0, 3.0, 3.0, 2.0], dtype=torch.bfloat16)
     assert int(O.mpk_argmax(lg)) == 1
+
+
+def test_moe_restatement_matches_transformers_fixture():
+    """Qwen3-MoE: the oracle against the fixture transformers' Qwen3MoeForCausalLM produced (make_golden_moe.py)."""
+    fx = _load("moe_tiny_generate.pt")
+    g = O.MoeGeometry(**fx["geometry"])
+    w = O.make_moe_weights(g, fx["seed"], norm_jitter=fx["norm_jitter"])
+    n_new = fx["logits"].shape[0]
+    m = O.TorchMoeRefModel(g, w, fx["max_seq"])
+    toks, logits = m.generate(fx["prompt"], n_new)
+    assert toks == fx["tokens"].tolist()
+    assert torch.equal(logits, fx["logits"]), "restatement is not bit-exact against transformers' logits"
+
+
+def test_moe_routing_semantics():
+    """softmax -> top-k -> renormalise (the reference's tests/runtime_python/blackwell/sm100_moe/test_gate_topk.py:34-78)."""
+    g = torch.Generator().manual_seed(1)
+    logits = torch.randn(5, 128, generator=g).to(torch.bfloat16)
+    val, idx = O.moe_route(logits, 8)
+    p = torch.softmax(logits.float(), -1)
+    top = p.topk(8, -1)
+    assert torch.equal(idx, top.indices)
+    assert torch.allclose(val.sum(-1), torch.ones(5), atol=1e-6)
+    assert torch.allclose(val, top.values / top.values.sum(-1, keepdim=True))
