@@ -12,8 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200mk.so")
-# mk_kernel_tp.cu and mk_kernel_hier.cu include mk_kernel.cu with other build switches (see its header)
-SOURCES = ["mk_kernel.cu", "mk_kernel_tp.cu", "mk_kernel_hier.cu", "mk_runtime.cpp", "mk_noalloc.cu"]
+# mk_kernel_tp.cu, mk_kernel_hier.cu and mk_kernel_moe.cu include mk_kernel.cu with other build switches (see its header)
+SOURCES = ["mk_kernel.cu", "mk_kernel_tp.cu", "mk_kernel_hier.cu", "mk_kernel_moe.cu", "mk_runtime.cpp", "mk_noalloc.cu"]
 HEADERS = ["mk_types.h", os.path.join("..", "..", "include", "b200mk.h")]
 
 

@@ -28,6 +28,7 @@
 //   MK_VARIANT        inner namespace of this compilation: base | tp | hier
 //   MK_WITH_XCHG      1: linear epilogues can push to / input staging can gather from the ranks' exchange regions
 //   MK_HIER_BARRIER   1: cluster-first grid barrier (the kernel must be launched with a cluster dimension)
+//   MK_WITH_MOE       1: the mixture-of-experts ops (routing, per-expert row-owner linears, weighted combine)
 #ifndef MK_VARIANT
 #define MK_VARIANT base
 #endif
@@ -36,6 +37,9 @@
 #endif
 #ifndef MK_HIER_BARRIER
 #define MK_HIER_BARRIER 0
+#endif
+#ifndef MK_WITH_MOE
+#define MK_WITH_MOE 0
 #endif
 #if MK_WITH_XCHG
 #define MK_XF(op, f) ((op).flags & (f))
@@ -2398,7 +2402,8 @@ __device__ void op_silu_mul(Ctx& c, const OpDesc& op, int T) {
   const int nvec = op.n >> 3;
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
-  for (long long e = (long long)blockIdx.x * kNumConsumers + c.tid; e < (long long)T * nvec;
+  const long long rows = (long long)T * (op.aux1 > 0 ? op.aux1 : 1);  // aux1: rows per token (expert slots of a MoE layer)
+  for (long long e = (long long)blockIdx.x * kNumConsumers + c.tid; e < rows * nvec;
        e += (long long)gridDim.x * kNumConsumers) {
     const int tok = (int)(e / nvec), col = (int)(e % nvec) * 8;
     const size_t src = (size_t)tok * op.ld_in + (size_t)(col / bk) * 2 * bk + col % bk;
@@ -2514,6 +2519,235 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
 #endif
   if (spread) grid_sync(c);
 }
+
+
+#if MK_WITH_MOE
+// ------------------------------------------------------------------------------------
+// mixture of experts (Qwen3-MoE decode, one or two batched tokens)
+// ------------------------------------------------------------------------------------
+// The reference runs routing, the two expert linears, SiLU*up and the weighted sum as tasks of their
+// own (tasks/blackwell/topk_softmax_sm100.cuh, moe_linear_sm100.cuh, mul_sum_add_sm100.cuh).  Here, at
+// one or two tokens, every (token, expert slot) pair is a GEMV: the expert linears run on the row-owner
+// path over a VIRTUAL row space of pairs x rows-per-expert.  A CTA owns a contiguous range of it, walks
+// it pair by pair in chunks of at most 32 rows, and the chunk's weight rows are the expert's rows of
+// the [experts * rows, K] weight (the TMA row coordinate is expert * rows + row).  The producer can
+// only run as far ahead as the routing is known: it waits for the consumers to pass the op's barrier.
+
+// aux0 = top-k, aux1 = experts.  in: router logits [T, experts] bf16; amax_val / amax_idx: the runtime's
+// routing tables [T, top-k] (fp32 weight, expert id).  One warp per token: fp32 softmax over the experts,
+// k rounds of (largest probability, lowest index), weights renormalised over the k picked
+// (transformers' Qwen3MoeTopKRouter with norm_topk_prob; reference task: topk_softmax_sm100.cuh:61-290).
+__device__ __noinline__ void op_moe_route(Ctx& c, const OpDesc& op, int T) {
+  const int E = op.aux1, K = op.aux0;
+  const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
+#pragma unroll 1
+  for (int t = blockIdx.x * kNumConsumerWarps + c.warp; t < T; t += gridDim.x * kNumConsumerWarps) {
+    float v[8];  // up to 256 experts: 8 per lane
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = c.lane + 32 * i;
+      v[i] = e < E ? __bfloat162float(__ldcg(in + (size_t)t * op.ld_in + e)) : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = (c.lane + 32 * i) < E ? expf(v[i] - mx) : 0.f;
+      sum += v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    float picked_sum = 0.f, my_w = 0.f;
+    int my_e = 0;
+#pragma unroll 1
+    for (int k = 0; k < K; ++k) {
+      ArgBest b;
+      b.v = -INFINITY;
+      b.i = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        ArgBest x;
+        x.v = v[i] * inv;
+        x.i = c.lane + 32 * i;
+        if (x.i < E && v[i] >= 0.f) b = arg_better(b, x);
+      }
+      b = warp_argmax(b);
+      picked_sum += b.v;
+      if (c.lane == k) {
+        my_w = b.v;
+        my_e = b.i;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c.lane + 32 * i == b.i) v[i] = -1.f;  // taken
+    }
+    if (c.lane < K) {
+      op.amax_val[(size_t)t * K + c.lane] = my_w / picked_sum;
+      op.amax_idx[(size_t)t * K + c.lane] = my_e;
+    }
+  }
+}
+
+// The CTA's share of the virtual row space of a MoE linear and its walk: pairs x n rows, contiguous ranges
+// of 8-row units per CTA, segments that end at pair boundaries, chunks of at most 32 rows inside a segment.
+struct MoeWalk {
+  int row0, row1;  // the CTA's virtual rows
+  int n;           // rows per expert (= per pair)
+  bool any;
+};
+__device__ __forceinline__ MoeWalk moe_walk(const OpDesc& op, int pairs) {
+  MoeWalk w;
+  w.n = op.n;
+  const unsigned U = (unsigned)pairs * (unsigned)(op.n / kUnitRows);
+  const unsigned G = min((unsigned)gridDim.x, U);
+  w.any = blockIdx.x < G;
+  w.row0 = w.any ? (int)tile_begin(blockIdx.x, U, G) * kUnitRows : 0;
+  w.row1 = w.any ? (int)tile_begin(blockIdx.x + 1, U, G) * kUnitRows : 0;
+  return w;
+}
+
+// aux0 = top-k, aux1 = experts, n = rows per expert, k = K.  w: [experts * n, K] bf16 (tmap_w: the four maps of
+// the row-owner path over that 2-D view).  in: [T, K] (one row per token) or, with F_MOE_PAIR_IN, [T * top-k, K];
+// out: [T * top-k, n].  amax_idx: the routing table.
+__device__ __noinline__ void op_moe_linear(Ctx& c, const OpDesc& op, int T) {
+  const KParams& p = c.p;
+  if (op_barrier(c, op)) return;
+  c.lin_seq += 1;
+  if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the routing is visible: the producer may pick this op's expert rows
+  const int topk = op.aux0;
+  const int pairs = T * topk;
+  const MoeWalk wk = moe_walk(op, pairs);
+  if (!wk.any || wk.row0 >= wk.row1) return;
+  const int nks = op.nkt;
+  const int kp = nks * kRowsStageK;
+  const bool pair_in = (op.flags & F_MOE_PAIR_IN) != 0;
+  const int p_first = wk.row0 / wk.n, p_last = (wk.row1 - 1) / wk.n;
+  // input rows this CTA needs: those of its pairs (the down projection) or of their tokens
+  const int in_first = pair_in ? p_first : p_first / topk;
+  const int in_last = pair_in ? p_last : p_last / topk;
+  const int nrows = in_last - in_first + 1;  // at most 8 (the host admits MoE graphs for one or two tokens)
+  stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)in_first * op.ld_in, op.ld_in, op.k, kp, nullptr, 0, nrows,
+          nrows, nullptr);
+  const int S = p.num_stages;
+  const int lane = c.lane, warp = c.warp;
+  const int pitch_b = (kp + 8) * 2;
+  const uint32_t xs0 = c.smem_addr + p.x_off;
+  const uint32_t x_zero = xs0 + (uint32_t)(nrows * pitch_b);
+  const uint32_t w_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * 128);
+  const uint32_t w_xor = (uint32_t)(lane & 7);
+  const uint32_t w_hi = (uint32_t)(lane >> 4);
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
+  const int TP = p.sums_stride;
+  float* sums = c.sums();
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  const int e_row = c.tid & 31;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+#pragma unroll 1
+  for (int pr = p_first; pr <= p_last; ++pr) {
+    const int seg0 = max(wk.row0, pr * wk.n), seg1 = min(wk.row1, (pr + 1) * wk.n);
+    const int nch = rows_num_chunks(seg0, seg1);
+    // the B operand of the mma: column 0 = the pair's input row, the other seven columns zero
+    const int xrow = (pair_in ? pr : pr / topk) - in_first;
+    const bool a_real = (lane & 7) == 0;
+    const uint32_t a_row = a_real ? xs0 + (uint32_t)(xrow * pitch_b + (lane >> 3) * 16 + warp * 128) : x_zero;
+#pragma unroll 1
+    for (int ci = 0; ci < nch; ++ci) {
+      const int r0 = rows_chunk_begin(seg0, seg1, nch, ci);
+      const int R = rows_chunk_begin(seg0, seg1, nch, ci + 1) - r0;
+      const int ntile = (R + 15) >> 4;
+      float acc[4][4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+      const uint32_t box_bytes = (uint32_t)R * 128u;
+#pragma unroll 1
+      for (int ks = 0; ks < nks; ++ks) {
+        mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+        const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes + w_off;
+        const uint32_t xa = a_row + (a_real ? (uint32_t)(ks * kRowsStageK * 2) : 0u);
+        uint32_t x[2][4];
+        ldmatrix_x4(xa, x[0][0], x[0][1], x[0][2], x[0][3]);
+        ldmatrix_x4(xa + (a_real ? 64u : 0u), x[1][0], x[1][1], x[1][2], x[1][3]);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (t < ntile) {
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+              uint32_t w0, w1, w2, w3;
+              ldmatrix_x4(wb + (uint32_t)t * 2048u + ((((uint32_t)(2 * st) + w_hi) ^ w_xor) << 4), w0, w1, w2, w3);
+              mma_bf16(acc[2 * t + (st & 1)], w0, w1, w2, w3, x[st >> 1][2 * (st & 1)], x[st >> 1][2 * (st & 1) + 1]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty0 + 8 * s);
+        ++consumed;
+        if (++s == S) {
+          s = 0;
+          parity ^= 1u;
+        }
+      }
+      // column 0 of the accumulators (lanes with (lane & 3) == 0): rows 16t + (lane >> 2) and + 8
+      if ((lane & 3) == 0) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          float* d = sums + ((warp * kChunkRows + 16 * t + (lane >> 2)) * TP);
+          d[0] = acc[2 * t][0] + acc[2 * t + 1][0];
+          d[8 * TP] = acc[2 * t][2] + acc[2 * t + 1][2];
+        }
+      }
+      consumer_sync();
+      if (c.tid < 32 && e_row < R) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP];
+        out[(size_t)pr * op.ld_out + (r0 - pr * wk.n) + e_row] = __float2bfloat16_rn(v);
+      }
+      consumer_sync();
+    }
+  }
+  c.cons_idx += consumed;
+}
+
+// aux0 = top-k.  in: [T * top-k, n] bf16, amax_val: routing weights [T, top-k], res: [T, n] (may be null), out: [T, n].
+// out[t] = bf16( sum over the token's slots of weight * in[pair] ) + residual  (reference task mul_sum_add_sm100.cuh:17-48;
+// the PyTorch model adds the slots up in bf16 and the residual in bf16)
+__device__ void op_moe_combine(Ctx& c, const OpDesc& op, int T) {
+  const int topk = op.aux0;
+  const int nvec = op.n >> 3;
+  const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
+  const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  const bool torch_num = c.p.numerics == NUM_TORCH;
+#pragma unroll 1
+  for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
+    const int t = u / nvec, v = u % nvec;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 1
+    for (int sl = 0; sl < topk; ++sl) {
+      const float wgt = __ldcg(op.amax_val + (size_t)t * topk + sl);
+      float f[8];
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(in + (size_t)(t * topk + sl) * op.ld_in) + v), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = torch_num ? rbf(acc[i] + rbf(f[i] * wgt)) : fmaf(f[i], wgt, acc[i]);
+    }
+    if (res != nullptr) {
+      float r[8];
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(res + (size_t)t * op.ld_res) + v), r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = (torch_num ? rbf(acc[i]) : acc[i]) + r[i];
+    }
+    reinterpret_cast<uint4*>(out + (size_t)t * op.ld_out)[v] = pack8(acc);
+  }
+}
+#endif  // MK_WITH_MOE
 
 // ------------------------------------------------------------------------------------
 // stand-alone allreduce layer
@@ -2797,6 +3031,9 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
   unsigned issued = 0;
   int s = 0;
   uint32_t empty_parity = 1;  // a fresh barrier passes a wait on the "previous" phase
+#if MK_WITH_MOE
+  unsigned lin_seq = 0;       // linear and MoE-linear ops seen so far in this launch (the consumers count the same way)
+#endif
   const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
   // look-ahead: tiles beyond the shared-memory ring are requested into L2 so that HBM
   // keeps streaming while the consumers sit in barriers, staging and epilogues
@@ -2837,6 +3074,64 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
     for (int oi = 0; oi < p.num_ops && !dead; ++oi) {
       const OpDesc& rop = p.ops[oi];
       if constexpr (PATH == PATH_ROWS) {
+#if MK_WITH_MOE
+        if (rop.type == OP_MOE_LINEAR) {
+          // the expert of a pair is only known once the consumers have passed this op's barrier
+          lin_seq += 1;
+          {
+            unsigned long long t0 = 0;
+            int spins = 0;
+            while ((unsigned)fl[4] < lin_seq) {
+              if (fl[0] < 0) { dead = true; break; }
+              __nanosleep(40);
+              if (((++spins) & 1023) == 0) {
+                if (aborted(c)) { dead = true; break; }
+                const unsigned long long now = globaltimer();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > 4 * c.p.timeout_ns) { dead = true; break; }
+              }
+            }
+          }
+          if (dead) break;
+          __threadfence();
+          const int topk = rop.aux0;
+          const MoeWalk wk = moe_walk(rop, T * topk);
+          if (!wk.any || wk.row0 >= wk.row1) continue;
+          const int p_first = wk.row0 / wk.n, p_last = (wk.row1 - 1) / wk.n;
+          for (int pr = p_first; pr <= p_last && !dead; ++pr) {
+            const int expert = __ldcg(rop.amax_idx + pr);
+            const int seg0 = max(wk.row0, pr * wk.n), seg1 = min(wk.row1, (pr + 1) * wk.n);
+            const int nch = rows_num_chunks(seg0, seg1);
+            for (int ci = 0; ci < nch && !dead; ++ci) {
+              const int r0 = rows_chunk_begin(seg0, seg1, nch, ci);
+              const int R = rows_chunk_begin(seg0, seg1, nch, ci + 1) - r0;
+              const void* tmap = reinterpret_cast<const unsigned char*>(rop.tmap_w) + ((R >> 3) - 1) * 128;
+              const uint32_t box_bytes = (uint32_t)R * 128u;
+              const int wrow = expert * wk.n + (r0 - pr * wk.n);  // the chunk's first row in the [experts * n, K] weight
+              for (int ks = 0; ks < rop.nkt; ++ks) {
+                if (!mbar_wait(c, bar_empty0 + 8 * s, empty_parity, ST_TIMEOUT_EMPTY)) {
+                  dead = true;
+                  break;
+                }
+                const uint32_t full = bar_full0 + 8 * s;
+                const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+                mbar_arrive_expect_tx(full, 8u * box_bytes);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  tma_load_2d_hint(dst + (uint32_t)j * box_bytes, tmap, full, ks * kRowsStageK + j * kBoxK, wrow, pol_stream);
+                issued += 1;
+                fl[1] = (int)issued;
+                if (++s == S) {
+                  s = 0;
+                  empty_parity ^= 1u;
+                }
+              }
+            }
+          }
+          continue;
+        }
+        if (rop.type == OP_LINEAR) lin_seq += 1;
+#endif
         if (rop.type != OP_LINEAR) continue;
         // row-owner op: per chunk of up to 32 owned rows, the full K in 512-wide stages of
         // eight boxes; the tensor map for a chunk of R rows is the (R / 8)-th of the op's four
@@ -3205,6 +3500,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) megakernel(const __grid_consta
           case OP_ARGMAX_PARTIAL: if (!op_barrier(c, op)) op_argmax_partial(c, op, T); break;
           case OP_ARGMAX_REDUCE: if (!op_barrier(c, op)) op_argmax_reduce(c, op, T); break;
           case OP_ALLREDUCE: op_allreduce(c, op, T); break;
+#if MK_WITH_MOE
+          case OP_MOE_ROUTE: if (!op_barrier(c, op)) op_moe_route(c, op, T); break;
+          case OP_MOE_LINEAR: op_moe_linear(c, op, T); break;
+          case OP_MOE_COMBINE: if (!op_barrier(c, op)) op_moe_combine(c, op, T); break;
+#endif
           default: op_barrier(c, op); break;
         }
         if (pr && c.tid == 0) pr[2] = globaltimer();
@@ -3296,10 +3596,12 @@ extern "C" const void* MK_CAT(mk_kernel_variant_, MK_VARIANT)(int path) {
 // ------------------------------------------------------------------------------------
 extern "C" const void* mk_kernel_variant_tp(int path);
 extern "C" const void* mk_kernel_variant_hier(int path);
+extern "C" const void* mk_kernel_variant_moe(int path);
 namespace {
 // the build of the kernel a launch needs: tensor-parallel exchange code only when there are peers,
 // the hierarchical barrier only when the launch uses clusters
 const void* kernel_for(const mk::KParams* p) {
+  if (p->has_moe) return mk_kernel_variant_moe(p->path);
   if (p->cluster > 1) return mk_kernel_variant_hier(p->path);
   if (p->world > 1) return mk_kernel_variant_tp(p->path);
   switch (p->path) {

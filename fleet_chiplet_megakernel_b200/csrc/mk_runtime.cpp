@@ -357,6 +357,7 @@ int plan_graph(mk_handle* h) {
   // ordinal of its exchange in the iteration; exchanges counts the exchanges planned so far.
   std::map<int, int> virt;
   int exchanges = 0;
+  int moe_topk = 0;  // experts per token of the latest routing layer
   // Can the output `tid` of the allreduce layer at position i stay virtual?  Every reader up to the
   // tensor's next writer must be an rmsnorm input, the input of a linear that stages its rows itself
   // (row-owner path, or the fused rmsnorm_linear layer) or a linear's residual, must come before any
@@ -678,6 +679,67 @@ int plan_graph(mk_handle* h) {
       po.n = (int)in.dims[1];
       po.aux0 = cfg.world_size;
       po.aux1 = cfg.rank;
+    } else if (nm == "tensor_init") {
+      continue;  // the reference zeroes an accumulation buffer here; nothing accumulates in place in this runtime
+    } else if (starts_with(nm, "moe_topk_softmax")) {
+      // (router logits [T, experts]) -> (top-k weights [T, k], routing indices, mask): the reference's index
+      // and mask tensors describe ITS grouping of tokens per expert; this runtime keeps its own [T, k] tables
+      if (op.t.size() != 4) return h->fail(MK_E_INVALID, "moe_topk_softmax takes (input, topk_weight, routing_indices, mask)");
+      if (int e = check_2d_bf16(h, op.t[0], nm.c_str())) return e;
+      const Tensor &in = h->tensors[op.t[0]], &tw = h->tensors[op.t[1]];
+      if (tw.ndim != 2 || tw.dims[1] < 1 || tw.dims[1] > 32 || in.dims[1] > 256 || tw.dims[1] > in.dims[1])
+        return h->fail(MK_E_UNSUPPORTED, "moe routing: at most 256 experts and 32 experts per token");
+      po.type = mk::OP_MOE_ROUTE;
+      po.in = op.t[0];
+      po.out = op.t[1];
+      po.aux0 = (int)tw.dims[1];
+      po.aux1 = (int)in.dims[1];
+      moe_topk = po.aux0;
+    } else if (starts_with(nm, "moe_w13_linear") || starts_with(nm, "moe_w2_linear") || starts_with(nm, "gang_moe_w")) {
+      // (input, weight [experts, n, K], routing_indices, mask, output [T, k, n])
+      if (op.t.size() != 5) return h->fail(MK_E_INVALID, "%s takes (input, weight, routing_indices, mask, output)", nm.c_str());
+      if (!rows_mode) return h->fail(MK_E_UNSUPPORTED, "mixture-of-experts layers are built for one or two batched tokens (every (token, expert) pair a row-owner GEMV); a grouped GEMM for wider batches is not");
+      if (moe_topk <= 0) return h->fail(MK_E_INVALID, "%s: no moe_topk_softmax_routing layer before it", nm.c_str());
+      const bool w2 = nm.find("w2") != std::string::npos;
+      const Tensor &in = h->tensors[op.t[0]], &w = h->tensors[op.t[1]], &out = h->tensors[op.t[4]];
+      if (w.ndim != 3 || w.dtype != MK_BF16 || in.dtype != MK_BF16 || out.dtype != MK_BF16)
+        return h->fail(MK_E_INVALID, "%s: the weight must be [experts, n, K] bf16", nm.c_str());
+      if (w.strides[2] != 1 || w.strides[1] != w.dims[2] || w.strides[0] != w.dims[1] * w.dims[2])
+        return h->fail(MK_E_INVALID, "%s: the weight must be contiguous", nm.c_str());
+      const int64_t K = w.dims[2], N = w.dims[1];
+      if (in.dims[in.ndim - 1] != K || out.dims[out.ndim - 1] != N || N % 8 || K % 8)
+        return h->fail(MK_E_INVALID, "%s: input / output widths do not match the weight", nm.c_str());
+      if ((w2 && in.ndim != 3) || (!w2 && in.ndim != 2) || out.ndim != 3 || out.dims[1] != moe_topk)
+        return h->fail(MK_E_INVALID, "%s: input must be [T, K]%s and output [T, k, n]", nm.c_str(), w2 ? " per (token, slot) pair, i.e. [T, k, K]" : "");
+      po.type = mk::OP_MOE_LINEAR;
+      po.flags |= mk::F_ROWS | (w2 ? mk::F_MOE_PAIR_IN : 0);
+      po.in = op.t[0]; po.w = op.t[1]; po.out = op.t[4];
+      po.n = (int)N;
+      po.k = (int)K;
+      po.aux0 = moe_topk;
+      po.aux1 = (int)w.dims[0];
+    } else if (nm == "moe_silu_mul") {
+      // [T, k, 2 * inter] in [gate | up] halves -> [T, k, inter]: the dense silu_mul op over T * k rows
+      if (op.t.size() != 2) return h->fail(MK_E_INVALID, "moe_silu_mul takes (input, output)");
+      const Tensor &in = h->tensors[op.t[0]], &out = h->tensors[op.t[1]];
+      if (in.ndim != 3 || out.ndim != 3 || in.dims[2] != 2 * out.dims[2] || out.dims[2] % 8 || in.dtype != MK_BF16)
+        return h->fail(MK_E_INVALID, "moe_silu_mul: input [T, k, 2 * inter], output [T, k, inter], bf16");
+      po.type = mk::OP_SILU_MUL;
+      po.in = op.t[0]; po.out = op.t[1];
+      po.n = (int)out.dims[2];
+      po.aux0 = (int)out.dims[2];
+      po.aux1 = (int)out.dims[1];  // rows per token
+    } else if (starts_with(nm, "moe_mul_sum_add")) {
+      // (input [T, k, n], weight [T, k], residual [T, n], output [T, n])
+      if (op.t.size() != 4) return h->fail(MK_E_INVALID, "moe_mul_sum_add takes (input, weight, residual, output)");
+      const Tensor &in = h->tensors[op.t[0]], &out = h->tensors[op.t[3]];
+      if (in.ndim != 3 || out.ndim != 2 || in.dims[2] != out.dims[1] || out.dims[1] % 8)
+        return h->fail(MK_E_INVALID, "moe_mul_sum_add: input [T, k, n], output [T, n]");
+      if (int e = check_2d_bf16(h, op.t[2], nm.c_str())) return e;
+      po.type = mk::OP_MOE_COMBINE;
+      po.in = op.t[0]; po.res = op.t[2]; po.out = op.t[3];
+      po.n = (int)out.dims[1];
+      po.aux0 = (int)in.dims[1];
     } else {
       return h->fail(MK_E_UNSUPPORTED, "unknown layer '%s'", nm.c_str());
     }
@@ -715,6 +777,9 @@ const char* op_type_name(int t) {
     case mk::OP_ARGMAX_PARTIAL: return "argmax_partial";
     case mk::OP_ARGMAX_REDUCE: return "argmax_reduce";
     case mk::OP_ALLREDUCE: return "allreduce";
+    case mk::OP_MOE_ROUTE: return "moe_route";
+    case mk::OP_MOE_LINEAR: return "moe_linear";
+    case mk::OP_MOE_COMBINE: return "moe_combine";
   }
   return "?";
 }
@@ -1074,6 +1139,7 @@ static int compile_program(mk_handle* h, bool first) {
   int x_budget = rows_mode ? kRowsXBudget : kFastSmem - fixed0 - want_stages * stage_bytes;
   int x_bytes = std::max(cfg.max_num_pages * 4, wide ? sums_bytes : 0);
   int max_nblk = 1, n_linear = 0, min_tpp = rows_mode ? 2 : x_rows;
+  bool has_moe = false;
   const int kpad_to = rows_mode ? mk::kRowsStageK : mk::kTileK;  // the staged rows are padded to whole stages
   for (int attempt = 0; attempt < 2; ++attempt) {
     bool fits = true;
@@ -1104,6 +1170,19 @@ static int compile_program(mk_handle* h, bool first) {
       p.aux3 = tpp;
       min_tpp = std::min(min_tpp, tpp);
       x_bytes = std::max(x_bytes, tpp * row_bytes + 16);
+    } else if (p.type == mk::OP_MOE_LINEAR) {
+      // a CTA stages the input rows of the pairs its share of the virtual row space (pairs x n rows) touches
+      ++n_linear;
+      has_moe = true;
+      const int kp = (p.k + mk::kRowsStageK - 1) / mk::kRowsStageK * mk::kRowsStageK;
+      const int64_t pairs = (int64_t)nt * p.aux0;
+      const int64_t units = pairs * (p.n / mk::kUnitRows);
+      const int g = (int)std::min<int64_t>(h->num_sms, units);
+      const int64_t rows_per_cta = ((units + g - 1) / g) * mk::kUnitRows;
+      const int spans = (int)((rows_per_cta + p.n - 1) / p.n + 1);
+      if (spans > 8) return h->fail(MK_E_UNSUPPORTED, "moe linear: %d rows per expert are too few for the row-owner split", p.n);
+      if (spans * (kp + 8) * 2 + 16 > x_budget) return h->fail(MK_E_UNSUPPORTED, "moe linear: K=%d is too wide", p.k);
+      x_bytes = std::max(x_bytes, spans * (kp + 8) * 2 + 16);
     } else if (p.type == mk::OP_RMSNORM) {
       x_bytes = std::max(x_bytes, ((p.n + 63) / 64 * 64 + 8) * 2 + 16);
     } else if (p.type == mk::OP_ATTN) {
@@ -1226,6 +1305,16 @@ static int compile_program(mk_handle* h, bool first) {
   h->weight_bytes = 0;
   float* last_amax_val = nullptr;
   int* last_amax_idx = nullptr;
+  // mixture of experts: the routing tables [tokens, top-k] (renormalised softmax weight, expert id)
+  float* route_w = nullptr;
+  int* route_idx = nullptr;
+  if (has_moe) {
+    void* q = nullptr;
+    if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * 32 * 4)) return e;
+    route_w = (float*)q;
+    if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * 32 * 4)) return e;
+    route_idx = (int*)q;
+  }
   for (size_t i = 0; i < h->plan.size(); ++i) {
     const PlanOp& po = h->plan[i];
     mk::OpDesc& d = descs[i];
@@ -1316,6 +1405,39 @@ static int compile_program(mk_handle* h, bool first) {
         if (int e = h->dmalloc(&q, (size_t)h->plan_tokens * po.amax_n * 4)) return e;
         d.amax_idx = last_amax_idx = (int*)q;
       }
+    } else if (po.type == mk::OP_MOE_LINEAR) {
+      // the [experts, n, K] weight as one 2-D [experts * n, K] tensor: four maps, for chunks of 8, 16, 24 and 32 rows
+      const Tensor& w = h->tensors[po.w];
+      const Tensor &ti = h->tensors[po.in], &to = h->tensors[po.out];
+      d.ld_in = (int)ti.strides[ti.ndim - 2];
+      d.ld_out = (int)to.strides[to.ndim - 2];
+      d.nkt = (po.k + mk::kRowsStageK - 1) / mk::kRowsStageK;
+      d.amax_idx = route_idx;
+      if (((uintptr_t)w.ptr) & 15) return h->fail(MK_E_INVALID, "weight %s is not 16-byte aligned", w.name.c_str());
+      map_of[i] = (int)maps.size();
+      for (int rows = mk::kUnitRows; rows <= mk::kChunkRows; rows += mk::kUnitRows) {
+        CUtensorMap m;
+        cuuint64_t gdim[2] = {(cuuint64_t)po.k, (cuuint64_t)((int64_t)po.aux1 * po.n)};
+        cuuint64_t gstr[1] = {(cuuint64_t)po.k * 2};
+        cuuint32_t box[2] = {(cuuint32_t)mk::kBoxK, (cuuint32_t)rows};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w.ptr, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return h->fail(MK_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %s", (int)r, w.name.c_str());
+        maps.push_back(m);
+      }
+      h->weight_bytes += (int64_t)po.aux0 * po.n * d.nkt * mk::kRowsStageK * 2;  // per token
+    } else if (po.type == mk::OP_MOE_ROUTE) {
+      d.amax_val = route_w;
+      d.amax_idx = route_idx;
+    } else if (po.type == mk::OP_MOE_COMBINE) {
+      const Tensor& ti = h->tensors[po.in];
+      d.ld_in = (int)ti.strides[ti.ndim - 2];
+      d.amax_val = route_w;
+    } else if (po.type == mk::OP_SILU_MUL && po.aux1 > 0) {
+      const Tensor &ti = h->tensors[po.in], &to = h->tensors[po.out];
+      d.ld_in = (int)ti.strides[ti.ndim - 2];
+      d.ld_out = (int)to.strides[to.ndim - 2];
     } else if (po.type == mk::OP_ATTN) {
       d.k_cache = tp(po.kc);
       d.v_cache = tp(po.vc);
@@ -1388,7 +1510,9 @@ static int compile_program(mk_handle* h, bool first) {
   // L2 look-ahead of the weight stream, in 32 KB stages: on by default (512 KB per CTA, the
   // measured optimum with evict-first weight loads) for the row-owner path, off elsewhere (it measured slower there);
   // prefetch_kb > 0 sets it, < 0 turns it off
-  const int pf_kb = cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 512 : 0);
+  kp.has_moe = has_moe ? 1 : 0;
+  // (no look-ahead with expert layers: which weights come next is only known after routing)
+  const int pf_kb = has_moe ? 0 : (cfg.prefetch_kb != 0 ? cfg.prefetch_kb : (h->rows_mode ? 512 : 0));
   kp.prefetch_tiles = pf_kb > 0 ? std::max(1, pf_kb * 1024 / mk::kStageBytes) : 0;
   if (h->prof_ptr && first) {  // (the trace describes the primary program's ops)
     const int64_t need = ((int64_t)descs.size() + 1) * G * 4 + (int64_t)G * 16;

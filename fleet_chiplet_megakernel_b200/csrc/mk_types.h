@@ -40,6 +40,10 @@ enum OpType : int {
   OP_ARGMAX_PARTIAL = 6,
   OP_ARGMAX_REDUCE = 7,
   OP_ALLREDUCE = 8,
+  // mixture of experts (one or two batched tokens: every (token, expert slot) pair is a row-owner GEMV)
+  OP_MOE_ROUTE = 9,    // router logits [T, experts] -> top-k expert ids and renormalised softmax weights
+  OP_MOE_LINEAR = 10,  // out[pair] = W[expert of the pair] * in[token or pair]; n = rows per expert, aux1 = experts
+  OP_MOE_COMBINE = 11, // out[t] = sum over the token's slots of weight * in[pair] (+ residual)
 };
 
 enum OpFlags : int {
@@ -59,6 +63,7 @@ enum OpFlags : int {
   F_PUSH = 1 << 12,         // linear: the epilogue stores its fp32 sums into every rank's exchange slots instead of `out`
   F_GATHER_IN = 1 << 13,    // linear / rmsnorm: the input rows are the rank-order sum of the latest exchange's slots
   F_GATHER_RES = 1 << 14,   // linear: the residual is the rank-order sum of the latest exchange's slots
+  F_MOE_PAIR_IN = 1 << 17,  // MoE linear: the input has one row per (token, slot) pair (the down projection), not one per token
   F_XRANK = 1 << 16,        // argmax reduce: the per-rank (value, index) pairs of a vocabulary-sharded LM head are exchanged and the global best is taken
   F_SILU4 = 1 << 15,        // linear with F_SILU_MUL on the tile paths: rows are [4 gate | 4 up] per 8-row unit (the row-owner layout)
 };
@@ -193,6 +198,7 @@ struct KParams {
   int trace_op;     // op whose inner phases are stamped: prof[(num_ops + 1) * grid * 4 + cta * 16 + k]; -1 none
   int debug_flags;  // bit 0: linear tasks skip the arithmetic
   int prefetch_tiles;  // weight tiles per CTA requested into L2 ahead of the ring (0 = off)
+  int has_moe;         // the program holds mixture-of-experts ops: the host launches the build of the kernel that has them
   // shared-memory carve-up (bytes from the 1024-aligned base)
   int num_stages;
   int stage_bytes;  // weights (kStageBytes) + the activation boxes of a wide-batch stage

@@ -539,6 +539,71 @@ class PersistentKernel:
         self._gang_linear("gang_splitk_linear_res_mi300", input, weight, residual, output, (output_stride, tile_n, k_splits), block_dim,
                           workspace=workspace)
 
+    # -- mixture of experts (persistent_kernel.py:1183-1435) ---------------------------------
+    def tensor_init_layer(self, input: DTensor, dummy_input: DTensor, dummy_output: DTensor, grid_dim: tuple,
+                          block_dim: tuple):
+        """persistent_kernel.py:1183-1201: the reference zeroes a buffer its expert tasks accumulate into.
+        Accepted and dropped: nothing accumulates in place in this runtime."""
+        assert input.num_dims == 2
+        self._op("tensor_init", [input, dummy_input, dummy_output], (), grid_dim, block_dim)
+
+    def moe_topk_softmax_routing_layer(self, input: DTensor, output: tuple, grid_dim: tuple, block_dim: tuple):
+        """persistent_kernel.py:1203-1227: router logits [tokens, experts] -> softmax, top-k, renormalised weights.
+        ``output`` = (topk weights [tokens, k], routing indices [experts, tokens], mask [experts + 1]); the last two
+        describe the reference's grouping of tokens per expert and are accepted, not written."""
+        assert input.num_dims == 2
+        assert len(output) == 3
+        moe_topk_weight, moe_routing_indices, moe_masks = output
+        assert moe_topk_weight.num_dims == 2
+        assert moe_routing_indices.num_dims == 2
+        assert moe_masks.num_dims == 1
+        self._op("moe_topk_softmax_sm100", [input, moe_topk_weight, moe_routing_indices, moe_masks], (), grid_dim, block_dim)
+
+    def moe_w13_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                             output: DTensor, grid_dim: tuple, block_dim: tuple):
+        """persistent_kernel.py:1229-1260: per (token, slot): [gate | up] = W13[expert] x."""
+        assert input.num_dims == 2
+        assert weight.num_dims == 3
+        assert moe_routing_indices.num_dims == 2
+        assert moe_mask.num_dims == 1
+        assert output.num_dims == 3
+        self._op("moe_w13_linear_sm100", [input, weight, moe_routing_indices, moe_mask, output], (), grid_dim, block_dim)
+
+    def moe_silu_mul_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
+        """persistent_kernel.py:1262-1276."""
+        assert input.num_dims == 3
+        assert output.num_dims == 3
+        self._op("moe_silu_mul", [input, output], (), grid_dim, block_dim)
+
+    def moe_w2_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                            output: DTensor, grid_dim: tuple, block_dim: tuple):
+        """persistent_kernel.py:1278-1309: per (token, slot): W2[expert] act."""
+        assert input.num_dims == 3
+        assert weight.num_dims == 3
+        assert moe_routing_indices.num_dims == 2
+        assert moe_mask.num_dims == 1
+        assert output.num_dims == 3
+        self._op("moe_w2_linear_sm100", [input, weight, moe_routing_indices, moe_mask, output], (), grid_dim, block_dim)
+
+    def gang_moe_w13_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                                  output: DTensor, block_dim: tuple = (256, 1, 1)):
+        """persistent_kernel.py:1311-1359 (Fleet's per-XCD expert ganging: the plain layer here)."""
+        self.moe_w13_linear_layer(input, weight, moe_routing_indices, moe_mask, output, (8, 1, 1), block_dim)
+
+    def gang_moe_w2_linear_layer(self, input: DTensor, weight: DTensor, moe_routing_indices: DTensor, moe_mask: DTensor,
+                                 output: DTensor, block_dim: tuple = (256, 1, 1)):
+        """persistent_kernel.py:1361-1409."""
+        self.moe_w2_linear_layer(input, weight, moe_routing_indices, moe_mask, output, (8, 1, 1), block_dim)
+
+    def moe_mul_sum_add_layer(self, input: DTensor, weight: DTensor, residual: DTensor, output: DTensor, grid_dim: tuple,
+                              block_dim: tuple):
+        """persistent_kernel.py:1411-1435: out[t] = sum over slots of weight[t, slot] * input[t, slot] + residual[t]."""
+        assert input.num_dims == 3
+        assert weight.num_dims == 2
+        assert residual.num_dims == 2
+        assert output.num_dims == 2
+        self._op("moe_mul_sum_add_sm100", [input, weight, residual, output], (), grid_dim, block_dim)
+
     def argmax_layer(self, input: DTensor, output: DTensor, grid_dim: tuple, block_dim: tuple):
         assert input.num_dims == 2
         assert output.num_dims == 2

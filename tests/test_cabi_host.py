@@ -127,7 +127,7 @@ def test_error_behaviour_follows_the_reference_api(native_lib):
     k.finalize()
     k = _kernel()
     with pytest.raises(NotImplementedError, match="unknown layer"):
-        k._op("moe_topk_softmax_sm100", [k.new_tensor(dims=(2, 64), name="z")])
+        k._op("sampling_sm100", [k.new_tensor(dims=(2, 64), name="z")])
         k.plan()
     k.finalize()
 

@@ -1,0 +1,115 @@
+"""Mixture-of-experts decode (the reference's Qwen3-30B-A3B demo path) on a B200: routing, per-expert linears
+and the weighted combine per op against the oracle, and the whole model teacher-forced against the fixture
+that transformers' Qwen3MoeForCausalLM produced (tests/golden/make_golden_moe.py).  Tolerances as elsewhere:
+logits within 2e-2 of the step's largest |logit|, per-op outputs within 1e-2."""
+import os
+
+import pytest
+import torch
+
+import fleet_chiplet_megakernel_b200 as mk
+from oracle import qwen3_oracle as O
+from tests.helpers import onepass_kernel, bf16_close
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+BF = torch.bfloat16
+TOL = 2e-2
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(BF)
+
+
+def _moe_block(k, T, E, K, H, I, x, router, w13, w2, res, od):
+    """Record router linear -> routing -> w13 -> silu_mul -> w2 -> weighted sum on kernel k; returns the intermediates."""
+    xt = k.attach_input(x.cuda(), "x")
+    gate_out = k.new_tensor(dims=(T, E), name="moe_gate_out")
+    topk_w = k.new_tensor(dims=(T, K), dtype=mk.float32, name="moe_topk_weight")
+    ridx = k.new_tensor(dims=(E, T), dtype=mk.int32, name="moe_routing_indices")
+    mask = k.new_tensor(dims=(E + 1,), dtype=mk.int32, name="moe_mask")
+    mid = k.new_tensor(dims=(T, K, 2 * I), name="mlp_mid")
+    act = k.new_tensor(dims=(T, K, I), name="silu_mul_out")
+    out = k.new_tensor(dims=(T, K, H), name="mlp_out")
+    k.linear_layer(input=xt, weight=k.attach_input(router.cuda(), "router"), output=gate_out, grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+    k.moe_topk_softmax_routing_layer(input=gate_out, output=(topk_w, ridx, mask), grid_dim=(1, 1, 1), block_dim=(256, 1, 1))
+    k.moe_w13_linear_layer(input=xt, weight=k.attach_input(w13.cuda(), "w13"), moe_routing_indices=ridx, moe_mask=mask,
+                           output=mid, grid_dim=(10, 2 * I // 64, 1), block_dim=(256, 1, 1))
+    k.moe_silu_mul_layer(input=mid, output=act, grid_dim=(T, K, 1), block_dim=(256, 1, 1))
+    k.moe_w2_linear_layer(input=act, weight=k.attach_input(w2.cuda(), "w2"), moe_routing_indices=ridx, moe_mask=mask,
+                          output=out, grid_dim=(8, H // 64, 1), block_dim=(256, 1, 1))
+    k.moe_mul_sum_add_layer(input=out, weight=topk_w, residual=k.attach_input(res.cuda(), "res"), output=k.attach_input(od, "o"),
+                            grid_dim=(T, max(1, H // 256), 1), block_dim=(256, 1, 1))
+    return gate_out, mid, act, out
+
+
+@pytest.mark.parametrize("T,E,K,H,I", [(1, 16, 4, 512, 256), (2, 128, 8, 2048, 768), (1, 128, 8, 2048, 768), (2, 32, 2, 256, 64)])
+def test_moe_block_matches_oracle(T, E, K, H, I):
+    x = _rand((T, H), 71)
+    router = _rand((E, H), 72, 1.0 / H ** 0.5)
+    w13, w2, res = _rand((E, 2 * I, H), 73, 0.05), _rand((E, H, I), 74, 0.05), _rand((T, H), 75)
+    k, meta, _ = onepass_kernel(T)
+    od = torch.zeros(T, H, dtype=BF, device="cuda")
+    gate_out, mid, act, out = _moe_block(k, T, E, K, H, I, x, router, w13, w2, res, od)
+    kinds = [ln.split()[1] for ln in k.plan().strip().splitlines()]
+    assert kinds == ["linear", "moe_route", "moe_linear", "silu_mul", "moe_linear", "moe_combine"]
+    k.compile()
+    k()
+    # the oracle's block on the router logits the kernel itself produced (routing is discontinuous in them)
+    logits = k.read_tensor(gate_out)
+    bf16_close(logits, O.mpk_linear(x, router), 1e-2, "router logits")
+    val, idx = O.moe_route(logits, K)
+    mid_ref = torch.stack([torch.stack([O.mpk_linear(x[t], w13[idx[t, s]]) for s in range(K)]) for t in range(T)])
+    bf16_close(k.read_tensor(mid).reshape(T * K, -1), mid_ref.reshape(T * K, -1), 1e-2, "w13")
+    act_ref = O.mpk_silu_mul(mid_ref[..., :I], mid_ref[..., I:])
+    out_ref = torch.stack([torch.stack([O.mpk_linear(act_ref[t, s], w2[idx[t, s]]) for s in range(K)]) for t in range(T)])
+    bf16_close(k.read_tensor(out).reshape(T * K, -1), out_ref.reshape(T * K, -1), 1e-2, "w2")
+    y = ((out_ref.float() * val[..., None]).sum(1) + res.float()).to(BF)
+    bf16_close(od, y, 1e-2, "weighted sum + residual")
+    k.finalize()
+
+
+def _geom(g):
+    return mk.Qwen3MoeGeometry(hidden=g.hidden, n_q=g.n_q, n_kv=g.n_kv, head_dim=g.head_dim, experts=g.experts, top_k=g.top_k,
+                               moe_mlp=g.moe_mlp, layers=g.layers, vocab=g.vocab, rope_theta=g.rope_theta)
+
+
+def test_moe_generate_matches_transformers_fixture():
+    fx = torch.load(os.path.join(GOLD, "moe_tiny_generate.pt"))
+    g = O.MoeGeometry(**fx["geometry"])
+    w = O.make_moe_weights(g, fx["seed"], norm_jitter=fx["norm_jitter"])
+    P, n_new = len(fx["prompt"]), 24
+    dec = mk.Qwen3MoeDecoder(_geom(g), {k: v.cuda() for k, v in w.items()}, max_seq_length=P + n_new + 1, max_requests=1,
+                             page_size=16, numerics="mpk", keep_logits=True, max_iterations=1)
+    dec.set_prompts([fx["prompt"]])
+    ref_tok, ref_lg = fx["tokens"], fx["logits"]
+    worst, firm = 0.0, 0
+    for it in range(P + n_new - 1):
+        dec.run()
+        if it >= P - 1:
+            j = it - (P - 1)
+            ours, ref = dec.logits[0].float().cpu(), ref_lg[j].float()
+            scale = float(ref.abs().max())
+            worst = max(worst, float((ours - ref).abs().max()) / scale)
+            top2 = ref.topk(2).values
+            if float(top2[0] - top2[1]) > TOL * scale:
+                firm += 1
+                assert int(dec.tokens[0, P + j]) == int(ref_tok[P + j]), f"step {j}"
+            dec.tokens[0, P + j] = int(ref_tok[P + j])
+    dec.finalize()
+    print(f"MoE tiny: max logit error {worst:.4g}, {firm}/{n_new} firm steps")
+    assert worst <= TOL, worst
+
+
+def test_moe_two_identical_requests_give_identical_rows():
+    g = O.MOE_TINY
+    w = O.make_moe_weights(g, 0, norm_jitter=0.1)
+    p = O.make_prompt(O.Geometry(vocab=g.vocab), 5, 1)
+    dec = mk.Qwen3MoeDecoder(_geom(g), {k: v.cuda() for k, v in w.items()}, max_seq_length=5 + 12, max_requests=2, page_size=16,
+                             numerics="mpk")
+    dec.set_prompts([p, p])
+    dec.run()
+    a, b = dec.generated(0).cpu().tolist(), dec.generated(1).cpu().tolist()
+    dec.finalize()
+    assert a == b and len(a) == 17
