@@ -419,6 +419,67 @@ def run_ours(args):
     return main.get("tokens")
 
 
+def run_moe(args):
+    """Config 5 of the benchmark list, single GPU, batch 1: Qwen3-30B-A3B geometry (48 layers, hidden 2048, 32 q /
+    4 kv heads, 128 experts, top-8, expert MLP 768), seeded random weights, 64-token prompt, greedy decode.  The
+    expert layers are built for one or two batched tokens and one GPU; prompts advance one token per iteration."""
+    import fleet_chiplet_megakernel_b200 as mk
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = mk.Qwen3MoeGeometry(layers=args.layers if args.layers != 36 else 48)
+    K, W = args.steps, args.warmup
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, std=0.02):
+        return (torch.randn(shape, generator=gen, dtype=torch.float32, device=dev) * std).to(torch.bfloat16)
+
+    w = {"embed": rnd(g.vocab, g.hidden), "lm_head": rnd(g.vocab, g.hidden), "norm": torch.ones(g.hidden, dtype=torch.bfloat16, device=dev)}
+    for i in range(g.layers):
+        w[f"l{i}.q"], w[f"l{i}.k"], w[f"l{i}.v"] = rnd(g.n_q * 128, g.hidden), rnd(g.n_kv * 128, g.hidden), rnd(g.n_kv * 128, g.hidden)
+        w[f"l{i}.o"] = rnd(g.hidden, g.n_q * 128)
+        w[f"l{i}.router"] = rnd(g.experts, g.hidden, std=2.0 / g.hidden ** 0.5)
+        w[f"l{i}.w13"], w[f"l{i}.w2"] = rnd(g.experts, 2 * g.moe_mlp, g.hidden), rnd(g.experts, g.hidden, g.moe_mlp)
+        for n, d in (("ln1", g.hidden), ("ln2", g.hidden), ("qn", 128), ("kn", 128)):
+            w[f"l{i}.{n}"] = torch.ones(d, dtype=torch.bfloat16, device=dev)
+    iters = PROMPT_LEN + W + K - 1
+    dec = mk.Qwen3MoeDecoder(g, w, max_seq_length=MAX_SEQ, max_requests=1, page_size=PAGE, device=dev, max_iterations=iters,
+                             numerics="mpk")
+    prompt = make_prompts(g, 1)
+    for _ in range(2):
+        dec.set_prompts(prompt)
+        dec.run()
+    torch.cuda.synchronize()
+    stamps = dec.mpk.get_event_timing()
+    t = stamps[:, 0].astype("float64")
+    first = iters - K
+    step_ns = t[first + 1: first + K + 1] - t[first: first + K]
+    tpot_ms = float(step_ns.sum() / K / 1e6)
+    t0 = time.perf_counter()
+    dec.set_prompts([p.pin_memory() for p in prompt])
+    dec.run()
+    toks = dec.tokens[:, : PROMPT_LEN + W + K].cpu()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / (W + K)
+    per_layer = 2 * ((g.n_q + 2 * g.n_kv) * 128 * g.hidden + g.hidden * g.n_q * 128 + g.experts * g.hidden +
+                     g.top_k * 3 * g.moe_mlp * g.hidden) + 2 * (2 * g.hidden + 256)
+    ctx = PROMPT_LEN + W + K // 2
+    nbytes = g.layers * per_layer + 2 * g.vocab * g.hidden + 2 * g.layers * g.n_kv * 128 * 2 * (ctx + 1)
+    peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs", 6650.0)) if \
+        os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else 6650.0
+    ach = nbytes / (tpot_ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "Qwen3-30B-A3B bf16 MoE decode TPOT", "value": tpot_ms, "unit": "ms/token", "n_gpus": 1, "steps": K,
+                      "warmup": W, "ms_per_step": tpot_ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+                      "dtype": "bf16", "data": "synthetic (seeded random weights, uniform-random 64-token prompt)",
+                      "config": {"workload": f"Qwen3-30B-A3B geometry, {g.layers} layers, {g.experts} experts top-{g.top_k}, batch 1, "
+                                             f"64-token prompt, {K} greedy decode steps, single GPU", "batch": 1,
+                                 "l2": "inputs larger than L2 (6 GB of weights per step)", "grid": dec.mpk.grid_size()},
+                      "e2e": {"value": e2e_ms, "unit": "ms/token", "h2d_bytes_per_step": PROMPT_LEN * 8 / (W + K),
+                              "d2h_bytes_per_step": toks.numel() * 8 / (W + K)},
+                      "gpu_launches": 2,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                                   "traffic": None, "algorithmic_bytes_per_step": nbytes}}), flush=True)
+    dec.finalize()
+
+
 def run_reference(args):
     """The reference's own CPU implementation of the path (its PyTorch model, restated in
     oracle/), timed on the host cores with all threads: the full-depth model, a 64-token prefill
@@ -450,6 +511,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="dense", choices=["dense", "moe"], help="dense: Qwen3-8B geometry (the headline); moe: Qwen3-30B-A3B geometry, batch 1")
     ap.add_argument("--numerics", default="torch", choices=["torch", "mpk"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch sweep (single GPU)")
@@ -460,6 +522,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.model == "moe":
+        run_moe(args)
     else:
         run_ours(args)
 

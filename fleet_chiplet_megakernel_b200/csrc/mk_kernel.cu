@@ -2102,170 +2102,6 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
   }
 }
 
-// The tasks of an attention op (everything behind the per-iteration plan).  CHUNKED: the iteration
-// carries a prompt chunk, so all new K/V are appended behind a barrier of their own before any row is
-// read and nothing is fetched ahead of the op's barrier.  Two instances, so that the decode iterations
-// run exactly the code they ran before prompt chunks existed; the chunked one is kept out of line.
-template <bool CHUNKED>
-__device__ __forceinline__ void attention_tasks(Ctx& c, const OpDesc& op, AttnPlan& pl, const int* lens, int* pgc, int* pgs,
-                                                int* geom, bool fill, int T) {
-  const KParams& p = c.p;
-  const int G = gridDim.x;
-  const int l16 = c.lane & 15;
-  // Half-warp hw serves q head (hw % qpk) of the kv-head group for the positions of group
-  // (hw / qpk): one head per thread keeps the row loop and the combine small (this code runs
-  // once per layer out of a cold instruction cache), and the two halves of a warp read the
-  // same K/V rows, so their loads share a request.
-  const int hw = 2 * c.warp + (c.lane >> 4);
-  const int head = hw % pl.qpk;
-  pl.ngroups = 16 / pl.qpk;
-  pl.gi = hw / pl.qpk;
-  const int part_stride = pl.qpk * (kHeadDim + 2);
-  const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
-  uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off);     // [8 heads][16 lanes]: q after norm and RoPE
-  uint4* sm_k = sm_q + 8 * 16;                                  // [16 lanes]: the new k
-  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [16 half-warps][128]
-  float* sm_m = sm_o + 16 * kHeadDim;                           // [16 half-warps]
-  float* sm_l = sm_m + 16;
-  const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
-  const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
-
-  bool first = true;
-  if (CHUNKED) {
-    // A prompt chunk: its tokens attend to each other's K/V, which only exist once every token's K has been
-    // normalised, rotated and appended.  So this iteration appends first, for all tokens, behind the op's
-    // own barrier, and meets at one more grid barrier before any row is read (nothing is fetched early).
-    if (attn_barrier_then_append(c, op, pl, lens, T)) return;
-    first = false;
-  }
-#pragma unroll 1
-  for (int task = blockIdx.x;; task += G) {
-    AttnTask a;
-    attn_prepare(c, op, pl, lens, task, l16, a, (first && !CHUNKED) ? pgc : nullptr, fill, (first && !CHUNKED) ? geom : nullptr);
-    if (first) {
-      // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
-      first = false;
-      if (a.valid) {
-        if (fill && c.tid < 16) {  // (read only after the barrier's CTA-wide sync)
-          const int slot = (a.p0 >> p.page_shift) + c.tid;
-          if ((slot << p.page_shift) < a.p1) pgs[c.tid] = __ldcg(p.kv_indices + a.kv_base + slot);
-        }
-        attn_l2_ahead(c, op, pl, a, l16, fill ? nullptr : pgs);
-      }
-      MK_STAMP(c, 1);
-      if (op.flags & F_SYNC_BEFORE) {  // op_barrier, with the wait inlined
-        grid_wait(c);
-        if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
-        c.dead = c.flags()[3] != 0;
-        if (c.dead) return;
-      } else if (op_barrier(c, op)) {
-        return;
-      }
-    }
-    if (task >= pl.ntasks) break;
-    if (!a.valid) continue;
-    const int L = a.L;
-    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
-                               (size_t)a.h * (pl.qpk + 2) * kHeadDim;
-    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
-    // norm + RoPE once per CTA: warp w < qpk prepares q head w, one warp the new k
-    if (c.warp < pl.qpk) {
-      F8 q;
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
-      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
-      if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
-    }
-    if (c.warp == kw) {
-      F8 kf;
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
-      const uint4 kn = pack8(kf.v);
-      if (c.lane < 16) {
-        sm_k[l16] = kn;
-        if (a.p1 == L && !CHUNKED) {  // the last chunk appends the new token's K and V to the cache
-          const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
-          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
-          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
-        }
-      }
-    }
-    consumer_sync();
-    const uint4 qv = sm_q[head * 16 + l16];
-    const uint4 knew = sm_k[l16];
-    MK_STAMP(c, 2);
-    float m, l, o[8];
-    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, (task == (int)blockIdx.x && !CHUNKED) ? pgs : nullptr);
-    MK_STAMP(c, 3);
-    // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
-    // elements then combines the position groups of each head
-    {
-      float* dst = sm_o + hw * kHeadDim + l16 * 8;
-      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
-      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
-      if (l16 == 0) {
-        sm_m[hw] = m;
-        sm_l[hw] = l;
-      }
-    }
-    consumer_sync();
-    float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
-                         (size_t)a.h * pl.qpk * kHeadDim;
-#pragma unroll 1
-    for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
-      const int eh = e >> 7, d = e & 127;
-      float M = -INFINITY;
-#pragma unroll 1
-      for (int g = 0; g < pl.ngroups; ++g) M = fmaxf(M, sm_m[g * pl.qpk + eh]);
-      float Ls = 0.f, O = 0.f;
-#pragma unroll 1
-      for (int g = 0; g < pl.ngroups; ++g) {
-        const int w = g * pl.qpk + eh;
-        const float mw = sm_m[w];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        Ls += f * sm_l[w];
-        O += f * sm_o[w * kHeadDim + d];
-      }
-      if (a.nch == 1) {
-        out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
-      } else {
-        part[e] = O;
-        if (d == 0) {
-          part[pl.qpk * kHeadDim + eh] = M;
-          part[pl.qpk * kHeadDim + pl.qpk + eh] = Ls;
-        }
-      }
-    }
-    MK_STAMP(c, 4);
-    if (a.nch > 1) {
-      consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
-      MK_STAMP(c, 5);
-      volatile int* fl = c.flags();
-      unsigned* cnt = p.attn_count + (size_t)a.t * pl.HKV + a.h;
-      const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
-      if (c.tid == 0) {
-        unsigned old;
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
-        fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
-      }
-      consumer_sync();
-      MK_STAMP(c, 6);
-      // The chunk that arrives last merges all of them.  (A fixed merger per kv head, polling the
-      // counter, measured slower: the last arriver knows at once that it is the last.)
-      if (fl[2] != 0) {
-        attn_merge(c, base, out, a.nch, pl.qpk, part_stride);
-        if (c.tid == 0) *cnt = 0u;
-      }
-    }
-    consumer_sync();
-    MK_STAMP(c, 7);
-  }
-}
-__device__ __noinline__ void attention_tasks_chunked(Ctx& c, const OpDesc& op, AttnPlan& pl, const int* lens, int* pgc,
-                                                     int* pgs, int* geom, bool fill, int T) {
-  attention_tasks<true>(c, op, pl, lens, pgc, pgs, geom, fill, T);
-}
-
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
 // request, token t == request slot t.
 template <int PATH>
@@ -2346,8 +2182,156 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       return;
     }
   }
-  if (*multi != 0) attention_tasks_chunked(c, op, pl, lens, pgc, pgs, geom, fill, T);
-  else attention_tasks<false>(c, op, pl, lens, pgc, pgs, geom, fill, T);
+  const int l16 = c.lane & 15;
+  // Half-warp hw serves q head (hw % qpk) of the kv-head group for the positions of group
+  // (hw / qpk): one head per thread keeps the row loop and the combine small (this code runs
+  // once per layer out of a cold instruction cache), and the two halves of a warp read the
+  // same K/V rows, so their loads share a request.
+  const int hw = 2 * c.warp + (c.lane >> 4);
+  const int head = hw % pl.qpk;
+  pl.ngroups = 16 / pl.qpk;
+  pl.gi = hw / pl.qpk;
+  const int part_stride = pl.qpk * (kHeadDim + 2);
+  const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+  uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off);     // [8 heads][16 lanes]: q after norm and RoPE
+  uint4* sm_k = sm_q + 8 * 16;                                  // [16 lanes]: the new k
+  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [16 half-warps][128]
+  float* sm_m = sm_o + 16 * kHeadDim;                           // [16 half-warps]
+  float* sm_l = sm_m + 16;
+  const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
+  const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
+
+  bool first = true;
+  const bool chunked = *multi != 0;
+  if (chunked) {
+    // A prompt chunk: its tokens attend to each other's K/V, which only exist once every token's K has been
+    // normalised, rotated and appended.  So this iteration appends first, for all tokens, behind the op's
+    // own barrier, and meets at one more grid barrier before any row is read (nothing is fetched early).
+    if (attn_barrier_then_append(c, op, pl, lens, T)) return;
+    first = false;
+  }
+#pragma unroll 1
+  for (int task = blockIdx.x;; task += G) {
+    AttnTask a;
+    attn_prepare(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
+    if (first) {
+      // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
+      first = false;
+      if (a.valid) {
+        if (fill && c.tid < 16) {  // (read only after the barrier's CTA-wide sync)
+          const int slot = (a.p0 >> p.page_shift) + c.tid;
+          if ((slot << p.page_shift) < a.p1) pgs[c.tid] = __ldcg(p.kv_indices + a.kv_base + slot);
+        }
+        attn_l2_ahead(c, op, pl, a, l16, fill ? nullptr : pgs);
+      }
+      MK_STAMP(c, 1);
+      if (op.flags & F_SYNC_BEFORE) {  // op_barrier, with the wait inlined
+        grid_wait(c);
+        if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+        c.dead = c.flags()[3] != 0;
+        if (c.dead) return;
+      } else if (op_barrier(c, op)) {
+        return;
+      }
+    }
+    if (task >= pl.ntasks) break;
+    if (!a.valid) continue;
+    const int L = a.L;
+    const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
+                               (size_t)a.h * (pl.qpk + 2) * kHeadDim;
+    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+    // norm + RoPE once per CTA: warp w < qpk prepares q head w, one warp the new k
+    if (c.warp < pl.qpk) {
+      F8 q;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
+      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+      if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
+    }
+    if (c.warp == kw) {
+      F8 kf;
+      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
+      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+      const uint4 kn = pack8(kf.v);
+      if (c.lane < 16) {
+        sm_k[l16] = kn;
+        if (a.p1 == L && !chunked) {  // the last chunk appends the new token's K and V to the cache
+          const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
+          reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.v_cache) + dst)[l16] = vnew;
+        }
+      }
+    }
+    consumer_sync();
+    const uint4 qv = sm_q[head * 16 + l16];
+    const uint4 knew = sm_k[l16];
+    MK_STAMP(c, 2);
+    float m, l, o[8];
+    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, (task == (int)blockIdx.x && !chunked) ? pgs : nullptr);
+    MK_STAMP(c, 3);
+    // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
+    // elements then combines the position groups of each head
+    {
+      float* dst = sm_o + hw * kHeadDim + l16 * 8;
+      reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (l16 == 0) {
+        sm_m[hw] = m;
+        sm_l[hw] = l;
+      }
+    }
+    consumer_sync();
+    float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
+                         (size_t)a.h * pl.qpk * kHeadDim;
+#pragma unroll 1
+    for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
+      const int eh = e >> 7, d = e & 127;
+      float M = -INFINITY;
+#pragma unroll 1
+      for (int g = 0; g < pl.ngroups; ++g) M = fmaxf(M, sm_m[g * pl.qpk + eh]);
+      float Ls = 0.f, O = 0.f;
+#pragma unroll 1
+      for (int g = 0; g < pl.ngroups; ++g) {
+        const int w = g * pl.qpk + eh;
+        const float mw = sm_m[w];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        Ls += f * sm_l[w];
+        O += f * sm_o[w * kHeadDim + d];
+      }
+      if (a.nch == 1) {
+        out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
+      } else {
+        part[e] = O;
+        if (d == 0) {
+          part[pl.qpk * kHeadDim + eh] = M;
+          part[pl.qpk * kHeadDim + pl.qpk + eh] = Ls;
+        }
+      }
+    }
+    MK_STAMP(c, 4);
+    if (a.nch > 1) {
+      consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
+      MK_STAMP(c, 5);
+      volatile int* fl = c.flags();
+      unsigned* cnt = p.attn_count + (size_t)a.t * pl.HKV + a.h;
+      const float* base = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks) * part_stride;
+      if (c.tid == 0) {
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt) : "memory");
+        fl[2] = (old == (unsigned)(a.nch - 1)) ? 1 : 0;
+      }
+      consumer_sync();
+      MK_STAMP(c, 6);
+      // The chunk that arrives last merges all of them.  (A fixed merger per kv head, polling the
+      // counter, measured slower: the last arriver knows at once that it is the last.)
+      if (fl[2] != 0) {
+        attn_merge(c, base, out, a.nch, pl.qpk, part_stride);
+        if (c.tid == 0) *cnt = 0u;
+      }
+    }
+    consumer_sync();
+    MK_STAMP(c, 7);
+  }
 }
 
 // ------------------------------------------------------------------------------------

@@ -379,8 +379,8 @@ def top2_margin(logits):
 # The PyTorch side of that demo is transformers' Qwen3MoeForCausalLM (demo_30B_A3B.py:1, 381-392), a
 # third-party dependency whose source is not part of the reference tree (pinned transformers==4.57.1 in
 # requirements.txt; this image has 5.5.0).  TorchMoeRefModel restates its published algorithm
-# (models/qwen3_moe/modeling_qwen3_moe.py of transformers: Qwen3MoeRMSNorm, Qwen3MoeAttention with eager
-# attention, Qwen3MoeTopKRouter, Qwen3MoeExperts, Qwen3MoeSparseMoeBlock, Qwen3MoeDecoderLayer) and is
+# (models/qwen3_moe/modeling_qwen3_moe.py of transformers: Qwen3MoeRMSNorm, Qwen3MoeAttention with the default
+# sdpa attention, Qwen3MoeTopKRouter, Qwen3MoeExperts, Qwen3MoeSparseMoeBlock, Qwen3MoeDecoderLayer) and is
 # pinned by tests/golden/make_golden_moe.py, which runs the installed transformers model on the same seeded
 # weights and commits ITS outputs as the fixture.
 @dataclass(frozen=True)
@@ -417,7 +417,7 @@ def moe_weight_names(g: MoeGeometry):
     return names
 
 
-def make_moe_weights(g: MoeGeometry, seed: int = 0, device: str = "cpu", norm_jitter: float = 0.0, router_std: float = 1.0):
+def make_moe_weights(g: MoeGeometry, seed: int = 0, device: str = "cpu", norm_jitter: float = 0.0, router_std: float = 2.0):
     """bf16 weights ~ N(0, init_std) in the order of ``moe_weight_names``; the router rows are scaled by
     ``router_std / init_std`` so that the routing logits spread (with N(0, 0.02) rows every expert scores the
     same to within bf16 noise and the top-k would be decided by rounding)."""
@@ -458,7 +458,7 @@ def moe_route(logits, top_k):
 
 
 class TorchMoeRefModel:
-    """Batch-1 restatement of transformers' Qwen3MoeForCausalLM (eager attention) with a contiguous KV cache."""
+    """Batch-1 restatement of transformers' Qwen3MoeForCausalLM (sdpa attention) with a contiguous KV cache."""
 
     def __init__(self, g: MoeGeometry, weights: dict, max_seq: int, layers: int | None = None, device: str = "cpu"):
         self.g, self.w, self.device = g, weights, device
@@ -484,21 +484,20 @@ class TorchMoeRefModel:
         self.k_cache[i, :, pos0:pos0 + n] = k
         self.v_cache[i, :, pos0:pos0 + n] = v
         L = pos0 + n
-        rep = g.n_q // g.n_kv
-        kk = self.k_cache[i, :, :L].repeat_interleave(rep, dim=0)
-        vv = self.v_cache[i, :, :L].repeat_interleave(rep, dim=0)
-        s = torch.matmul(q, kk.transpose(1, 2)) * (g.head_dim ** -0.5)
-        if n > 1:  # causal mask of a multi-token prefill
-            mask = torch.full((n, L), float("-inf"), device=s.device).triu(diagonal=L - n + 1)
-            s = s + mask.to(s.dtype)[None]
-        p = torch.softmax(s, dim=-1, dtype=torch.float32).to(q.dtype)
-        o = torch.matmul(p, vv).transpose(0, 1).reshape(n, g.n_q * g.head_dim)
+        # sdpa_attention_forward of transformers: torch's scaled_dot_product_attention, causal for a multi-token prefill
+        o = F.scaled_dot_product_attention(q[None], self.k_cache[i, :, :L][None], self.v_cache[i, :, :L][None],
+                                           is_causal=(n > 1), enable_gqa=True)[0]
+        o = o.transpose(0, 1).reshape(n, g.n_q * g.head_dim)
         return F.linear(o, w[f"l{i}.o"])
 
     def _moe(self, i, h):
         g, w = self.g, self.w
         x = hf_rmsnorm(h, w[f"l{i}.ln2"], g.eps)
-        val, idx = moe_route(F.linear(x, w[f"l{i}.router"]), g.top_k)
+        router_logits = F.linear(x, w[f"l{i}.router"])
+        val, idx = moe_route(router_logits, g.top_k)
+        # how decisively the last token's top-k set was chosen: the gap between the k-th and the (k+1)-th logit
+        top = router_logits[-1].float().topk(g.top_k + 1).values
+        self.route_margin = min(self.route_margin, float(top[g.top_k - 1] - top[g.top_k]))
         out = torch.zeros_like(x)
         for e in sorted(set(idx.flatten().tolist())):  # Qwen3MoeExperts.forward: experts in index order
             slot, tok = torch.where((idx == e).t())
@@ -511,7 +510,10 @@ class TorchMoeRefModel:
 
     @torch.inference_mode()
     def forward(self, token_ids, pos0):
+        """Logits of the given tokens; ``self.route_margin`` is left at the smallest routing gap, over the layers,
+        of the LAST token (a small gap means another arithmetic may pick a different expert set there)."""
         h = F.embedding(token_ids.to(self.device), self.w["embed"])
+        self.route_margin = float("inf")
         for i in range(self.n_layers):
             h = h + self._attention(i, h, pos0)
             h = h + self._moe(i, h)
@@ -521,11 +523,12 @@ class TorchMoeRefModel:
     def generate(self, prompt, n_new, forced=None):
         toks = prompt.clone().tolist()
         P = len(toks)
-        logits_out = []
+        logits_out, self.margins = [], []
         lg = self.forward(torch.tensor(toks), 0)
         for j in range(n_new):
             last = lg[-1]
             logits_out.append(last.clone().cpu())
+            self.margins.append(self.route_margin)
             toks.append(int(last.argmax(-1)) if forced is None else int(forced[j]))
             if j + 1 < n_new:
                 lg = self.forward(torch.tensor([toks[-1]]), P + j)

@@ -2,7 +2,8 @@
 
 The reference's MoE demo (demo/qwen3/demo_30B_A3B.py:1, 381-392) takes its PyTorch model from the
 transformers package (pinned 4.57.1 in the reference's requirements.txt; this image holds 5.5.0), so that
-model, run here on the oracle's seeded weights with eager attention, is the reference output:
+model, run here on the oracle's seeded weights with its default attention (torch's scaled_dot_product_attention)
+and its per-expert loop, is the reference output:
 
   python tests/golden/make_golden_moe.py      ->  tests/golden/moe_tiny_generate.pt
 
@@ -25,7 +26,7 @@ def build_hf(g, w):
                          num_experts_per_tok=g.top_k, norm_topk_prob=True, rope_theta=g.rope_theta,
                          max_position_embeddings=4096, tie_word_embeddings=False, decoder_sparse_step=1,
                          mlp_only_layers=[], attention_bias=False, rms_norm_eps=g.eps)
-    cfg._attn_implementation = "eager"
+    cfg._attn_implementation = "sdpa"       # the library's default, what the reference's demo runs
     cfg._experts_implementation = "eager"   # the published per-expert loop (5.x would otherwise pick a grouped GEMM)
     m = Qwen3MoeForCausalLM(cfg).to(torch.bfloat16).eval()
     # .to(bfloat16) also rounds the rotary embedding's inv_freq buffer; a checkpoint loaded with
@@ -76,6 +77,7 @@ def main():
           f"max error {err:.3e} of the step's largest |logit|, tokens equal {toks == toks2}")
     torch.save({"geometry": g.asdict(), "seed": 0, "norm_jitter": 0.1, "prompt": prompt, "tokens": torch.tensor(toks),
                 "logits": logits, "max_seq": P + n_new + 2, "restatement_bit_exact": exact,
+                "route_margin": torch.tensor(mine.margins),  # per generated step: smallest top-k routing gap over the layers
                 "transformers_version": __import__("transformers").__version__}, os.path.join(HERE, name))
 
 

@@ -60,11 +60,22 @@ def test_moe_block_matches_oracle(T, E, K, H, I):
     logits = k.read_tensor(gate_out)
     bf16_close(logits, O.mpk_linear(x, router), 1e-2, "router logits")
     val, idx = O.moe_route(logits, K)
+    # Two experts whose bf16 logits tie may come out in either slot order (the set and the weights are the
+    # same): the kernel's rows of a token are matched to the oracle's rows of that token, slot by nearest row.
+    def rows_match(got, ref, what):
+        got, ref = got.reshape(T, K, -1).float().cpu(), ref.reshape(T, K, -1).float()
+        for t in range(T):
+            left = list(range(K))
+            for s_ in range(K):
+                d = [float((got[t, s_] - ref[t, j]).abs().max()) for j in left]
+                j = left.pop(d.index(min(d)))
+                bf16_close(got[t, s_][None], ref[t, j][None], 1e-2, f"{what}, token {t} slot {s_}")
+
     mid_ref = torch.stack([torch.stack([O.mpk_linear(x[t], w13[idx[t, s]]) for s in range(K)]) for t in range(T)])
-    bf16_close(k.read_tensor(mid).reshape(T * K, -1), mid_ref.reshape(T * K, -1), 1e-2, "w13")
+    rows_match(k.read_tensor(mid), mid_ref, "w13")
     act_ref = O.mpk_silu_mul(mid_ref[..., :I], mid_ref[..., I:])
     out_ref = torch.stack([torch.stack([O.mpk_linear(act_ref[t, s], w2[idx[t, s]]) for s in range(K)]) for t in range(T)])
-    bf16_close(k.read_tensor(out).reshape(T * K, -1), out_ref.reshape(T * K, -1), 1e-2, "w2")
+    rows_match(k.read_tensor(out), out_ref, "w2")
     y = ((out_ref.float() * val[..., None]).sum(1) + res.float()).to(BF)
     bf16_close(od, y, 1e-2, "weighted sum + residual")
     k.finalize()
@@ -75,31 +86,44 @@ def _geom(g):
                                moe_mlp=g.moe_mlp, layers=g.layers, vocab=g.vocab, rope_theta=g.rope_theta)
 
 
-def test_moe_generate_matches_transformers_fixture():
+@pytest.mark.parametrize("numerics", ["torch", "mpk"])
+def test_moe_generate_matches_transformers_fixture(numerics):
     fx = torch.load(os.path.join(GOLD, "moe_tiny_generate.pt"))
     g = O.MoeGeometry(**fx["geometry"])
     w = O.make_moe_weights(g, fx["seed"], norm_jitter=fx["norm_jitter"])
     P, n_new = len(fx["prompt"]), 24
     dec = mk.Qwen3MoeDecoder(_geom(g), {k: v.cuda() for k, v in w.items()}, max_seq_length=P + n_new + 1, max_requests=1,
-                             page_size=16, numerics="mpk", keep_logits=True, max_iterations=1)
+                             page_size=16, numerics=numerics, keep_logits=True, max_iterations=1)
     dec.set_prompts([fx["prompt"]])
-    ref_tok, ref_lg = fx["tokens"], fx["logits"]
-    worst, firm = 0.0, 0
+    ref_tok, ref_lg, margins = fx["tokens"], fx["logits"], fx["route_margin"]
+    # Routing is discontinuous: where the reference's k-th and (k+1)-th router logits of some layer are within a
+    # few bf16 steps of each other, another summation order may pick the other expert, and the logits of that
+    # step then differ by more than rounding.  The 2e-2 bound is asserted on the steps whose routing is firm in
+    # every layer (gap > 0.06); the others are only reported.
+    worst, worst_loose, firm, routed_firm = 0.0, 0.0, 0, 0
     for it in range(P + n_new - 1):
         dec.run()
         if it >= P - 1:
             j = it - (P - 1)
             ours, ref = dec.logits[0].float().cpu(), ref_lg[j].float()
             scale = float(ref.abs().max())
-            worst = max(worst, float((ours - ref).abs().max()) / scale)
-            top2 = ref.topk(2).values
-            if float(top2[0] - top2[1]) > TOL * scale:
-                firm += 1
-                assert int(dec.tokens[0, P + j]) == int(ref_tok[P + j]), f"step {j}"
+            err = float((ours - ref).abs().max()) / scale
+            if float(margins[j]) > 0.06:
+                routed_firm += 1
+                worst = max(worst, err)
+                top2 = ref.topk(2).values
+                if float(top2[0] - top2[1]) > TOL * scale:
+                    firm += 1
+                    assert int(dec.tokens[0, P + j]) == int(ref_tok[P + j]), f"step {j}"
+            else:
+                worst_loose = max(worst_loose, err)
             dec.tokens[0, P + j] = int(ref_tok[P + j])
     dec.finalize()
-    print(f"MoE tiny: max logit error {worst:.4g}, {firm}/{n_new} firm steps")
+    print(f"MoE tiny ({numerics}): max logit error {worst:.4g} over {routed_firm}/{n_new} steps with firm routing "
+          f"({firm} of them with a firm token margin, tokens identical); {worst_loose:.4g} over the others")
+    assert routed_firm >= n_new // 2
     assert worst <= TOL, worst
+    assert worst_loose <= 0.25, worst_loose
 
 
 def test_moe_two_identical_requests_give_identical_rows():
