@@ -38,6 +38,15 @@
 #ifndef MK_HIER_BARRIER
 #define MK_HIER_BARRIER 0
 #endif
+#ifndef MK_LL_STAGE
+#define MK_LL_STAGE 1
+#endif
+#ifndef MK_LL_EPI
+#define MK_LL_EPI 1
+#endif
+#ifndef MK_LL_ATTN
+#define MK_LL_ATTN 1
+#endif
 #ifndef MK_WITH_MOE
 #define MK_WITH_MOE 0
 #endif
@@ -518,6 +527,83 @@ __device__ __forceinline__ unsigned xchg_cur(const Ctx& c) { return xchg_seq(c.p
 __device__ __forceinline__ unsigned xchg_next(const Ctx& c) { return xchg_seq(c.p.xchg_seq_base, c.ar_seq + 1u); }
 
 // ------------------------------------------------------------------------------------
+// Tagged activations between the ops of the row-owner path.  A producer stores every pair of adjacent
+// bf16 outputs as one 8-byte word {pair, tag}; 8-byte stores are single-copy atomic, so a word that
+// carries the awaited tag carries its data: the consumer needs no grid barrier, no fence and no second
+// round trip, it simply polls the words it is going to read anyway.  Eight columns are four words,
+// read as two 16-byte loads.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_gpu_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_gpu_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_gpu_v2(uint2* p, uint32_t a, uint32_t b) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ bool ll_ok(const uint4& a, const uint4& b, unsigned tag) {
+  return a.y == tag && a.w == tag && b.y == tag && b.w == tag;
+}
+// Eight columns whose words have not all arrived: poll them (bounded).  Zeros after the abort flag went up.
+__device__ __noinline__ uint4 ll_wait8(const Ctx& c, const uint4* src, unsigned tag) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    const uint4 a = ld_gpu_v4(src), b = ld_gpu_v4(src + 1);
+    if (ll_ok(a, b, tag)) return make_uint4(a.x, a.z, b.x, b.z);
+    if (((++spins) & 63u) == 0) {
+      if (aborted(c)) return make_uint4(0, 0, 0, 0);
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2 * c.p.timeout_ns) {
+        raise_abort(c, ST_TIMEOUT_DATA, (int)tag, (int)a.y);
+        return make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+}
+__device__ __forceinline__ uint4 ll_take8(const Ctx& c, const uint4* src, const uint4& a, const uint4& b, unsigned tag) {
+  return ll_ok(a, b, tag) ? make_uint4(a.x, a.z, b.x, b.z) : ll_wait8(c, src, tag);
+}
+// eight columns from column `col` (a multiple of 8) of the row that starts at word `row`
+__device__ __forceinline__ uint4 ll_gather8(const Ctx& c, const uint2* row, int col, unsigned tag) {
+  const uint4* src = reinterpret_cast<const uint4*>(row + (col >> 1));
+  const uint4 a = ld_gpu_v4(src), b = ld_gpu_v4(src + 1);
+  return ll_take8(c, src, a, b, tag);
+}
+// one column, as a float
+__device__ __noinline__ float ll_gather1(const Ctx& c, const uint2* row, int col, unsigned tag) {
+  const uint2* w = row + (col >> 1);
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    const uint2 q = ld_gpu_v2(w);
+    if (q.y == tag) return (col & 1) ? bf_hi(q.x) : bf_lo(q.x);
+    if (((++spins) & 63u) == 0) {
+      if (aborted(c)) return 0.f;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2 * c.p.timeout_ns) {
+        raise_abort(c, ST_TIMEOUT_DATA, (int)tag, (int)q.y);
+        return 0.f;
+      }
+    }
+  }
+}
+__device__ __forceinline__ const uint2* ll_row(const void* base, int ld, int tok) {
+  return reinterpret_cast<const uint2*>(base) + (size_t)tok * (size_t)(ld >> 1);
+}
+// the tag of what program op `op` stores in the current iteration
+__device__ __forceinline__ unsigned ll_tag_of(const Ctx& c, int op) { return ll_tag(c.iter, c.p.num_ops, op); }
+
+// ------------------------------------------------------------------------------------
 __device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
 
 // activations -> shared memory, with the optional fused RMSNorm
@@ -711,6 +797,96 @@ __device__ __noinline__ void stage_x_rows(Ctx& c, const void* in, int ld_in, int
     for (int i = 0; i < kMaxV; ++i) {
       const int v = v0 + i * vstep;
       if (v < nvec) xs[t * pitch + v] = raw[i];
+    }
+  }
+  __syncwarp();
+}
+
+// The same two stagings for an input that arrives as tagged words (no barrier stands before the op):
+// every lane first issues all its loads, then polls whatever has not arrived.  They are separate
+// functions on purpose: folded into the plain ones above they slowed those down by 8 % of a step
+// (registers and stack of code that runs once per op).
+template <int NV>
+__device__ __forceinline__ void stage_ll_regs(Ctx& c, const uint4* ll, uint4* dst, const uint4* pre_w, const uint4* wv, int K,
+                                              int nvec, int v0, int vstep, bool active, bool valid, int red_first, int wpr,
+                                              unsigned tag) {
+  const int kvec = K >> 3;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
+  float* red = c.red();
+  uint4 qa[NV], qb[NV], raw[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = v0 + vstep * i;
+    const bool ok = valid && v < kvec;
+    qa[i] = ok ? ld_gpu_v4(ll + 2 * v) : make_uint4(0, 0, 0, 0);
+    qb[i] = ok ? ld_gpu_v4(ll + 2 * v + 1) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = v0 + vstep * i;
+    raw[i] = (valid && v < kvec) ? ll_take8(c, ll + 2 * v, qa[i], qb[i], tag) : make_uint4(0, 0, 0, 0);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) ss = sumsq8(raw[i], torch_num, ss);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (c.lane == 0) red[c.warp] = ss;
+  consumer_sync();
+  if (active) {
+    const float r = row_rms_scale(red, red_first, wpr, K, torch_num);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = v0 + vstep * i;
+      if (v < nvec) dst[v] = scale8(raw[i], pre_w != nullptr ? pre_w[i] : (v < kvec ? __ldg(wv + v) : make_uint4(0, 0, 0, 0)), r, torch_num);
+    }
+  }
+  consumer_sync();
+}
+// fused norm; the host only plans it for rows of at most four vectors per lane
+__device__ __noinline__ void stage_x_ll(Ctx& c, const void* ll_in, int ld_in, int K, int kp, const void* norm_w, int tok0,
+                                        int rows, int T, const uint4* pre_w, unsigned tag) {
+  uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
+  const int pitch = (kp >> 3) + 1;
+  const int nvec = kp >> 3;
+  const int wpr = stage_warps_per_row(rows);
+  const int tb = c.warp / wpr, part = c.warp % wpr;
+  const bool active = tb < rows;
+  const bool valid = active && tok0 + tb < T;
+  const uint4* ll = reinterpret_cast<const uint4*>(ll_row(ll_in, ld_in, valid ? tok0 + tb : 0));
+  uint4* dst = xs + tb * pitch;
+  const int v0 = part * 32 + c.lane, vstep = 32 * wpr;
+  if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);
+  if (active && part == 0 && c.lane == 0) dst[nvec] = make_uint4(0, 0, 0, 0);
+  const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
+  if (nvec <= 2 * vstep) stage_ll_regs<2>(c, ll, dst, pre_w, wv, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, tag);
+  else stage_ll_regs<4>(c, ll, dst, pre_w, wv, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, tag);
+}
+// no norm: every warp stages the k slices it multiplies (see stage_x_rows)
+__device__ __noinline__ void stage_rows_ll(Ctx& c, const void* ll_in, int ld_in, int K, int kp, int tok0, int rows, int T, unsigned tag) {
+  constexpr int kMaxV = 6;
+  uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
+  const int pitch = (kp >> 3) + 1;
+  const int v0 = ((c.lane >> 3) * kRowsStageK + c.warp * 64 + (c.lane & 7) * 8) >> 3;
+  constexpr int vstep = 4 * kRowsStageK / 8;
+  const int kvec = K >> 3, nvec = kp >> 3;
+  if (c.lane == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+  for (int t = 0; t < rows; ++t) {
+    const bool live = tok0 + t < T;
+    const uint4* ll = reinterpret_cast<const uint4*>(ll_row(ll_in, ld_in, live ? tok0 + t : 0));
+    uint4 qa[kMaxV], qb[kMaxV];
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = v0 + i * vstep;
+      const bool ok = live && v < kvec;
+      qa[i] = ok ? ld_gpu_v4(ll + 2 * v) : make_uint4(0, 0, 0, 0);
+      qb[i] = ok ? ld_gpu_v4(ll + 2 * v + 1) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = v0 + i * vstep;
+      if (v < nvec) xs[t * pitch + v] = (live && v < kvec) ? ll_take8(c, ll + 2 * v, qa[i], qb[i], tag) : make_uint4(0, 0, 0, 0);
     }
   }
   __syncwarp();
@@ -1383,7 +1559,10 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int kp = nks * kRowsStageK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN) && !MK_XF(op, F_GATHER_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
+  if (MK_LL_STAGE && (op.flags & F_LL_IN)) {
+    if (op.flags & F_NORM_IN) stage_x_ll(c, op.ll_in, op.ld_in, op.k, kp, op.norm_w, tok0, ntok, T, pre_w, ll_tag_of(c, op.ll_in_op));
+    else stage_rows_ll(c, op.ll_in, op.ld_in, op.k, kp, tok0, ntok, T, ll_tag_of(c, op.ll_in_op));
+  } else if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN) && !MK_XF(op, F_GATHER_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
   else stage_x(c, op.in, op.ld_in, op.k, kp, (op.flags & F_NORM_IN) ? op.norm_w : nullptr, tok0, ntok, T, pre_w,
                MK_XF(op, F_GATHER_IN) != 0);
   MK_STAMP(c, 1);
@@ -1430,9 +1609,11 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     // the residual of this thread's output is requested a whole chunk ahead of its use
     float res0 = 0.f;
     const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
-    if (with_res && e_live)
-      res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
-                                       : __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
+    if (with_res && e_live) {
+      if (MK_LL_STAGE && (op.flags & F_LL_RES)) res0 = ll_gather1(c, ll_row(op.ll_res, op.ld_res, tok0 + e_tok), r0 + e_row, ll_tag_of(c, op.ll_res_op));
+      else res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
+                                            : __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
+    }
     float acc[4][4];  // [2 * tile + (k step & 1)]: two chains per tile, added up at the end
 #pragma unroll
     for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
@@ -1487,7 +1668,10 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     consumer_sync();
     if (op.flags & F_SILU_MUL) {
       // units are [4 gate rows | 4 up rows]: the thread of a gate row also adds up its partner
-      if ((e_row & 7) < 4 && e_live) {
+      const int col = ((r0 + e_row) >> 3) * 4 + (e_row & 3);
+      const bool mine = (e_row & 7) < 4 && e_live && col < (op.n >> 1);
+      __nv_bfloat16 y = __float2bfloat16_rn(0.f);
+      if (mine) {
         float g = 0.f, u = 0.f;
 #pragma unroll
         for (int w = 0; w < kNumConsumerWarps; ++w) {
@@ -1497,8 +1681,15 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
         g = rbf(g);  // the linear output is bf16 before the activation
         u = rbf(u);
         const float sv = rbf(__fdividef(g, 1.0f + __expf(-g)));
-        const int col = ((r0 + e_row) >> 3) * 4 + (e_row & 3);
-        if (col < (op.n >> 1)) out[(size_t)(tok0 + e_tok) * op.ld_out + col] = __float2bfloat16_rn(sv * u);
+        y = __float2bfloat16_rn(sv * u);
+        out[(size_t)(tok0 + e_tok) * op.ld_out + col] = y;
+      }
+      if (MK_LL_EPI && (op.flags & F_LL_OUT)) {  // the pair (col, col + 1) sits in two neighbouring lanes
+        const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
+        const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+        if (mine && !(e_row & 1))
+          st_gpu_v2(reinterpret_cast<uint2*>(op.ll_out) + (size_t)(tok0 + e_tok) * (size_t)(op.ld_out >> 1) + (col >> 1), lo | (hi << 16),
+                    ll_tag_of(c, c.cur_op));
       }
     } else {
       float v = 0.f;
@@ -1508,6 +1699,13 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
         if (with_res) v = (p.numerics == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
         if (MK_XF(op, F_PUSH)) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
         else out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
+      }
+      if (MK_LL_EPI && (op.flags & F_LL_OUT)) {  // rows come in units of 8: the pair (row, row + 1) sits in two neighbouring lanes
+        const uint32_t lo = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+        const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+        if (e_live && !(e_row & 1))
+          st_gpu_v2(reinterpret_cast<uint2*>(op.ll_out) + (size_t)(tok0 + e_tok) * (size_t)(op.ld_out >> 1) + ((r0 + e_row) >> 1),
+                    lo | (hi << 16), ll_tag_of(c, c.cur_op));
       }
       if (op.flags & F_ARGMAX) {
         ArgBest b;
@@ -1544,7 +1742,13 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
       }
     }
   }
-  if (op_barrier(c, op)) return;
+  if (op.flags & F_LL_IN) {
+    // No barrier, and no look at the abort flag either (a round trip to L2 per op): the polls of the
+    // tagged input and the stage waits watch it, and an aborted iteration ends at its closing barrier.
+    if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+  } else if (op_barrier(c, op)) {
+    return;
+  }
   c.lin_seq += 1;
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the activation producer may now read this op's input
   const int passes = linear_passes(op, T);
@@ -1725,7 +1929,8 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
 // handful of CTAs per layer ever run it.  One round of loads: every thread fetches, for its
 // output elements, the chunks' values together with their (max, sum) pairs and rescales as it
 // goes, eight chunks at a time (more loads in flight per thread measured slower).
-__device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride) {
+__device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16* out, int nch, int qpk, int part_stride,
+                                        uint2* ll_out, unsigned tag) {
   const int nout = qpk * kHeadDim;
   constexpr int kMergeBatch = 8;
 #pragma unroll 1
@@ -1757,7 +1962,13 @@ __device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16
       }
       M = Mb;
     }
-    out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
+    const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls));
+    out[e] = y;
+    if (MK_LL_ATTN && ll_out != nullptr) {  // (the loop's trip count is the same for all lanes of a warp: nout is a multiple of 128)
+      const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
+      const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+      if (!(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
+    }
   }
 }
 
@@ -1942,6 +2153,12 @@ __device__ __noinline__ bool attn_barrier_then_append(Ctx& c, const OpDesc& op, 
   const KParams& p = c.p;
   if (op.flags & F_SYNC_BEFORE) {
     grid_wait(c);
+    if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
+    c.dead = c.flags()[3] != 0;
+    if (c.dead) return true;
+  } else if (op.flags & F_LL_IN) {
+    // no barrier stands before this op, but a prompt chunk reads the plain rows of every token: a full one here
+    grid_sync(c);
     if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
     c.dead = c.flags()[3] != 0;
     if (c.dead) return true;
@@ -2230,6 +2447,10 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
         c.dead = c.flags()[3] != 0;
         if (c.dead) return;
+      } else if (MK_LL_ATTN && (op.flags & F_LL_IN)) {
+        // (no look at the abort flag: the polls of the tagged input watch it)
+        consumer_sync();
+        if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
       } else if (op_barrier(c, op)) {
         return;
       }
@@ -2239,17 +2460,24 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     const int L = a.L;
     const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
                                (size_t)a.h * (pl.qpk + 2) * kHeadDim;
-    const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+    // tagged input: the task polls the words of its own kv-head group only (a prompt chunk has had its barrier)
+    const bool ll_in = MK_LL_ATTN && (op.flags & F_LL_IN) && !chunked;
+    const uint2* llr = ll_row(op.ll_in, op.ld_in, a.t) + ((a.h * (pl.qpk + 2) * kHeadDim) >> 1);
+    const unsigned tag_in = ll_tag_of(c, op.ll_in_op);
+    const uint4 vnew = ll_in ? ll_gather8(c, llr, (pl.qpk + 1) * kHeadDim + l16 * 8, tag_in)
+                             : __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
     // norm + RoPE once per CTA: warp w < qpk prepares q head w, one warp the new k
     if (c.warp < pl.qpk) {
       F8 q;
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
+      unpack8(ll_in ? ll_gather8(c, llr, c.warp * kHeadDim + l16 * 8, tag_in)
+                    : __ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
       q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
       if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
     }
     if (c.warp == kw) {
       F8 kf;
-      unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
+      unpack8(ll_in ? ll_gather8(c, llr, pl.qpk * kHeadDim + l16 * 8, tag_in)
+                    : __ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
       kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
@@ -2283,6 +2511,9 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
+    uint2* ll_out = (MK_LL_ATTN && (op.flags & F_LL_OUT)) ? reinterpret_cast<uint2*>(op.ll_out) + (size_t)a.t * (size_t)(op.ld_out >> 1) +
+                                                ((a.h * pl.qpk * kHeadDim) >> 1)
+                                          : nullptr;
 #pragma unroll 1
     for (int e = c.tid; e < pl.qpk * kHeadDim; e += kNumConsumers) {
       const int eh = e >> 7, d = e & 127;
@@ -2299,7 +2530,13 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         O += f * sm_o[w * kHeadDim + d];
       }
       if (a.nch == 1) {
-        out[e] = __float2bfloat16_rn(__fdividef(O, Ls));
+        const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls));
+        out[e] = y;
+        if (MK_LL_ATTN && (op.flags & F_LL_OUT)) {  // (whole warps run this loop: its bound is a multiple of 128)
+          const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
+          const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+          if (!(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), ll_tag_of(c, c.cur_op));
+        }
       } else {
         part[e] = O;
         if (d == 0) {
@@ -2325,7 +2562,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       // The chunk that arrives last merges all of them.  (A fixed merger per kv head, polling the
       // counter, measured slower: the last arriver knows at once that it is the last.)
       if (fl[2] != 0) {
-        attn_merge(c, base, out, a.nch, pl.qpk, part_stride);
+        attn_merge(c, base, out, a.nch, pl.qpk, part_stride, ll_out, ll_tag_of(c, c.cur_op));
         if (c.tid == 0) *cnt = 0u;
       }
     }

@@ -88,6 +88,7 @@ struct PlanOp {
   int kc = -1, vc = -1, qn = -1, kn = -1, cos = -1, sin = -1;
   int n = 0, k = 0, aux0 = 0, aux1 = 0, aux2 = 0, aux3 = 0;
   int amax_n = 0;
+  int ll_in_op = -1, ll_res_op = -1;  // tagged activations: the ops that produce the input / the residual
   std::string note;
 };
 
@@ -110,6 +111,8 @@ struct Program {
   int64_t weight_bytes = 0;
   int max_nblk = 1;
   size_t attn_count_bytes = 0, piece_count_bytes = 0;  // arrival counters, cleared before every kernel launch
+  void* ll_buf = nullptr;  // tagged activation words of the program, cleared before every kernel launch
+  size_t ll_bytes = 0;
 };
 
 struct mk_handle {
@@ -150,6 +153,8 @@ struct mk_handle {
   bool poisoned = false;        // a tensor-parallel launch aborted: the ranks' exchange sequences may differ
   size_t attn_count_bytes = 0;  // the attention chunk counters, cleared before every launch
   size_t piece_count_bytes = 0; // the split-k arrival counters, cleared before every launch
+  void* ll_buf = nullptr;       // tagged activation words of the program being compiled
+  size_t ll_bytes = 0;
 
   int fail(int code, const char* fmt, ...) {
     char buf[1024];
@@ -851,7 +856,7 @@ mk_handle* mk_create(const mk_config* cfg) {
   mk_handle* h = new mk_handle();
   h->cfg = *cfg;
   if (h->cfg.timeout_ms <= 0) h->cfg.timeout_ms = 4000;
-  if (h->cfg.debug_flags != 0)
+  if ((h->cfg.debug_flags & 15) != 0)
     fprintf(stderr, "b200mk: debug_flags=0x%x: measurement mode, the kernel skips arithmetic and its results are WRONG\n",
             h->cfg.debug_flags);
   return h;
@@ -1244,6 +1249,81 @@ static int compile_program(mk_handle* h, bool first) {
     }
   }
 
+  // Tagged activations (row-owner programs).  Where an op's input is the output of the op right before it,
+  // and both are row-owner linears or attention, the producer also stores its outputs as 8-byte words
+  // {two bf16 columns, tag} and the consumer polls the words it reads instead of waiting at a grid barrier.
+  // Why dropping the barrier is safe: a CTA reads a buffer in an op only to produce outputs of that op, and
+  // every consumer waits for all the outputs it reads (a linear for the whole row, the attention tasks between
+  // them for every column of the QKV row), so whoever overwrites a buffer later has, through the chain of
+  // consumers, waited for everything its earlier readers produced.  A residual is read from the words of its
+  // own producer, or must be older than a barrier that is kept.
+  std::map<int, size_t> ll_off;  // tensor -> byte offset of its words in the program's arena
+  size_t ll_bytes = 0;
+  if (rows_mode && !has_moe && kp.cluster == 1 && !(cfg.debug_flags & 16)) {
+    auto ll_tensor = [&](int id) {
+      if (!ll_off.count(id)) {
+        const Tensor& t = h->tensors[id];
+        ll_off[id] = ll_bytes;
+        ll_bytes += ((size_t)t.dims[0] * (size_t)t.strides[0] * 4 + 255) / 256 * 256;
+      }
+    };
+    auto row_linear = [&](const PlanOp& q) { return q.type == mk::OP_LINEAR && (q.flags & mk::F_ROWS) && q.n % 8 == 0; };
+    auto plain_2d = [&](int id) {
+      if (id < 0) return false;
+      const Tensor& t = h->tensors[id];
+      return t.ndim == 2 && t.dtype == MK_BF16 && t.strides[1] == 1 && t.strides[0] % 8 == 0;
+    };
+    for (size_t i = 1; i < h->plan.size(); ++i) {
+      PlanOp& cur = h->plan[i];
+      PlanOp& prev = h->plan[i - 1];
+      if (!(cur.flags & mk::F_SYNC_BEFORE) || cur.in < 0 || cur.in != prev.out || !plain_2d(cur.in)) continue;
+      bool ok = false;
+      if (row_linear(cur) && !(cur.flags & mk::F_GATHER_IN)) {
+        ok = (row_linear(prev) && !(prev.flags & (mk::F_PUSH | mk::F_ARGMAX))) || prev.type == mk::OP_ATTN;
+        // what the two tagged-input stagings of the kernel cover: a fused norm with at most four 16-byte
+        // vectors per lane, or no norm and at most 24 stages of k
+        const int nkt = (cur.k + mk::kRowsStageK - 1) / mk::kRowsStageK;
+        const int wpr = cur.aux3 <= 1 ? 8 : 4;
+        if (cur.flags & mk::F_NORM_IN) ok = ok && nkt * (mk::kRowsStageK / 8) <= 128 * wpr;
+        else ok = ok && nkt <= 24 && cur.aux3 <= 2;
+      } else if (cur.type == mk::OP_ATTN) {
+        ok = row_linear(prev) && !(prev.flags & (mk::F_PUSH | mk::F_ARGMAX | mk::F_SILU_MUL));
+      }
+      if (!ok) continue;
+      int res_op = -1;
+      if (cur.res >= 0 && !(cur.flags & mk::F_GATHER_RES)) {
+        int wq = -1;
+        for (int q = (int)i - 1; q >= 0; --q)
+          if (h->plan[q].out == cur.res) {
+            wq = q;
+            break;
+          }
+        if (wq >= 0) {
+          if ((h->plan[wq].flags & mk::F_LL_OUT) && plain_2d(cur.res)) {
+            res_op = wq;
+          } else {
+            bool fenced = false;  // a kept barrier between the residual's writer and this op
+            for (int b = wq + 1; b < (int)i; ++b) fenced = fenced || (h->plan[b].flags & mk::F_SYNC_BEFORE);
+            if (!fenced) continue;
+          }
+        }
+      }
+      cur.flags = (cur.flags & ~mk::F_SYNC_BEFORE) | mk::F_LL_IN;
+      cur.ll_in_op = (int)i - 1;
+      prev.flags |= mk::F_LL_OUT;
+      ll_tensor(cur.in);
+      if (res_op >= 0) {
+        cur.flags |= mk::F_LL_RES;
+        cur.ll_res_op = res_op;
+      }
+    }
+  }
+  h->ll_buf = nullptr;
+  h->ll_bytes = ll_bytes;
+  if (ll_bytes > 0) {
+    if (int e = h->dmalloc(&h->ll_buf, ll_bytes)) return e;
+  }
+
   // 3. scratch and state
   const int G = h->grid;
   const int groups = (h->plan_tokens + min_tpp - 1) / min_tpp;
@@ -1333,6 +1413,11 @@ static int compile_program(mk_handle* h, bool first) {
     d.ld_out = ld(po.out);
     d.ld_res = ld(po.res);
     d.amax_n = po.amax_n;
+    d.ll_in_op = po.ll_in_op;
+    d.ll_res_op = po.ll_res_op;
+    if (po.flags & mk::F_LL_IN) d.ll_in = (char*)h->ll_buf + ll_off.at(po.in);
+    if (po.flags & mk::F_LL_OUT) d.ll_out = (char*)h->ll_buf + ll_off.at(po.out);
+    if (po.flags & mk::F_LL_RES) d.ll_res = (char*)h->ll_buf + ll_off.at(po.res);
     if (po.type == mk::OP_EMBED) {
       d.ld_res = ld(po.w);
       d.ld_in = (int)h->tensors[po.in].strides[0];
@@ -1561,6 +1646,7 @@ int mk_compile(mk_handle* h) {
   h->prog[0].kp = h->kp; h->prog[0].smem_bytes = h->smem_bytes; h->prog[0].weight_bytes = h->weight_bytes;
   h->prog[0].max_nblk = h->max_nblk;
   h->prog[0].attn_count_bytes = h->attn_count_bytes; h->prog[0].piece_count_bytes = h->piece_count_bytes;
+  h->prog[0].ll_buf = h->ll_buf; h->prog[0].ll_bytes = h->ll_bytes;
   h->nprog = 1;
   if (two) {
     h->plan_tokens = cfg.max_num_batched_tokens;
@@ -1571,6 +1657,7 @@ int mk_compile(mk_handle* h) {
     h->prog[1].kp = h->kp; h->prog[1].smem_bytes = h->smem_bytes; h->prog[1].weight_bytes = h->weight_bytes;
     h->prog[1].max_nblk = h->max_nblk;
     h->prog[1].attn_count_bytes = h->attn_count_bytes; h->prog[1].piece_count_bytes = h->piece_count_bytes;
+    h->prog[1].ll_buf = h->ll_buf; h->prog[1].ll_bytes = h->ll_bytes;
     h->force_interleave = 0;
     h->nprog = 2;
     h->prog[0].kp.tok_lo = 1;
@@ -1623,6 +1710,10 @@ static int launch_program(mk_handle* h, int idx, void* stream) {
   if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
   ce = cudaMemsetAsync(P.kp.piece_count, 0, P.piece_count_bytes, s);
   if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  if (P.ll_bytes > 0) {  // tags restart with every kernel: no word of an earlier one may look valid
+    ce = cudaMemsetAsync(P.ll_buf, 0, P.ll_bytes, s);
+    if (ce != cudaSuccess) return h->cuda_fail(ce, "state reset");
+  }
   // exchange sequence numbers continue where the last kernel stopped (mk_wait adds what it executed)
   P.kp.xchg_seq_base = h->xchg_total;
   int e = mk_kernel_launch(&P.kp, h->grid, P.smem_bytes, stream);
@@ -1665,12 +1756,13 @@ int mk_wait(mk_handle* h, void* stream) {
     if (st[0] != 0) {
       static const char* names[] = {"ok", "grid barrier timed out", "weight stage never arrived", "weight ring never drained",
                                     "producer never got the next iteration", "peer never arrived", "token id out of range",
-                                    "out of KV pages", "a peer rank never delivered its allreduce share"};
+                                    "out of KV pages", "a peer rank never delivered its allreduce share",
+                                    "an op's tagged input never arrived"};
       const int* s = st + 15;  // status sits 15 words behind the abort flag
       const int code = s[0];
       if (h->cfg.world_size > 1) h->poisoned = true;
       return h->fail(MK_E_DEVICE, "megakernel aborted: %s (code %d) at cta %d op %d iteration %d detail %d/%d thread %d",
-                     (code >= 0 && code < 9) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
+                     (code >= 0 && code < 10) ? names[code] : "?", code, s[1], s[2], s[3], s[4], s[5], s[6]);
     }
     // ctrl[0] (3 words behind the abort flag) == -2: the kernel prepared an iteration that belongs to the
     // handle's other program and ended; that program takes over on the same stream

@@ -66,6 +66,12 @@ enum OpFlags : int {
   F_MOE_PAIR_IN = 1 << 17,  // MoE linear: the input has one row per (token, slot) pair (the down projection), not one per token
   F_XRANK = 1 << 16,        // argmax reduce: the per-rank (value, index) pairs of a vocabulary-sharded LM head are exchanged and the global best is taken
   F_SILU4 = 1 << 15,        // linear with F_SILU_MUL on the tile paths: rows are [4 gate | 4 up] per 8-row unit (the row-owner layout)
+  // Tagged activations (row-owner path): a producer also stores its bf16 outputs as 8-byte words
+  // {two adjacent columns, tag of the producing op in this iteration}; a consumer polls the words
+  // it needs instead of waiting at a grid barrier, so data and "ready" arrive in one load.
+  F_LL_OUT = 1 << 18,       // linear / attention: the outputs are also stored as tagged words (ll_out)
+  F_LL_IN = 1 << 19,        // linear / attention: the input rows are read from tagged words (ll_in, producer op ll_in_op); no barrier
+  F_LL_RES = 1 << 20,       // linear: the residual is read from tagged words (ll_res, producer op ll_res_op)
 };
 
 enum Numerics : int {
@@ -94,6 +100,7 @@ enum Status : int {
   ST_BAD_TOKEN = 6,
   ST_OUT_OF_PAGES = 7,
   ST_TIMEOUT_RANK = 8,
+  ST_TIMEOUT_DATA = 9,
 };
 
 struct alignas(16) OpDesc {
@@ -125,6 +132,11 @@ struct alignas(16) OpDesc {
   int* amax_idx;
   int amax_n;   // number of partials per token
   int pad_;
+  // tagged activations: word (token t, column pair j) of a tensor with row pitch ld sits at [t * (ld / 2) + j]
+  const void* ll_in;
+  void* ll_out;
+  const void* ll_res;
+  int ll_in_op, ll_res_op;  // program indices of the ops that produce ll_in / ll_res
 };
 
 struct KParams {
@@ -221,6 +233,13 @@ __host__ __device__ inline bool xchg_arrived(unsigned word_seq, unsigned seq) { 
 // index (in 8-byte words) of (exchange seq, source rank, token row, column) in a region
 __host__ __device__ inline size_t xchg_word(unsigned seq, int world, int tokens, int cols, int src, int tok, int col) {
   return (((size_t)xchg_half(seq) * world + src) * tokens + tok) * cols + col;
+}
+
+// Tag of the words op `op` stores in iteration `iter` (1-based) of a launch.  The host clears the word
+// buffers before every launch, and tags grow with (iteration, op), so a buffer never holds the awaited
+// tag before its producer in this iteration has stored it.
+__host__ __device__ inline unsigned ll_tag(int iter, int num_ops, int op) {
+  return (unsigned)(iter - 1) * (unsigned)num_ops + (unsigned)op + 1u;
 }
 
 // Weight tiles of a linear op are dealt to `grid` CTAs as contiguous ranges
