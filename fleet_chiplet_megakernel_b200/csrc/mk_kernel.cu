@@ -47,6 +47,12 @@
 #ifndef MK_LL_ATTN
 #define MK_LL_ATTN 1
 #endif
+// (experiments) the numerics mode fixed at compile time: -DMK_FIX_NUM=0 (reference megakernel) or 1 (PyTorch roundings)
+#ifdef MK_FIX_NUM
+#define MK_NUM(p) (MK_FIX_NUM)
+#else
+#define MK_NUM(p) ((p).numerics)
+#endif
 #ifndef MK_WITH_MOE
 #define MK_WITH_MOE 0
 #endif
@@ -668,7 +674,7 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
                                                int v0, int vstep, bool active, bool valid, int red_first, int wpr,
                                                bool gather, int tok) {
   const int kvec = K >> 3;
-  const bool torch_num = c.p.numerics == NUM_TORCH;
+  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
   float* red = c.red();
   uint4 raw[NV];
 #pragma unroll
@@ -708,7 +714,7 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
   uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3, kvec = K >> 3;
-  const bool torch_num = c.p.numerics == NUM_TORCH;
+  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
   const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
   const int wpr = stage_warps_per_row(rows);
   const int tb = c.warp / wpr, part = c.warp % wpr;
@@ -811,7 +817,7 @@ __device__ __forceinline__ void stage_ll_regs(Ctx& c, const uint4* ll, uint4* ds
                                               int nvec, int v0, int vstep, bool active, bool valid, int red_first, int wpr,
                                               unsigned tag) {
   const int kvec = K >> 3;
-  const bool torch_num = c.p.numerics == NUM_TORCH;
+  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
   float* red = c.red();
   uint4 qa[NV], qb[NV], raw[NV];
 #pragma unroll
@@ -1009,7 +1015,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             v[i] = red[(cg * 8 + i) * kRedStride + tb];
-            if (p.numerics == NUM_TORCH) v[i] = rbf(v[i]);
+            if (MK_NUM(p) == NUM_TORCH) v[i] = rbf(v[i]);
             v[i] += r[i];
           }
           *reinterpret_cast<uint4*>(out + (size_t)(tok0 + tb) * op.ld_out + blk * kTileRows + cg * 8) = pack8(v);
@@ -1023,7 +1029,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     const int tok = tok0 + tb, col = blk * kTileRows + row;
     if (col < op.n) {
       float v = red[row * kRedStride + tb];
-      if (p.numerics == NUM_TORCH && !push) v = rbf(v);  // (pushed partial sums stay fp32: they are rounded once, after the ranks are added up)
+      if (MK_NUM(p) == NUM_TORCH && !push) v = rbf(v);  // (pushed partial sums stay fp32: they are rounded once, after the ranks are added up)
       if (with_res) {
         float r;
         if (e < kNumConsumers) r = res0;
@@ -1696,7 +1702,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
       if (e_live) {
 #pragma unroll
         for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + e_tok];
-        if (with_res) v = (p.numerics == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
+        if (with_res) v = (MK_NUM(p) == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
         if (MK_XF(op, F_PUSH)) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
         else out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
       }
@@ -1881,6 +1887,9 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
   }
 }
 
+// NORMW: also fetch the norm weights and the cos/sin row of the task's position (the single-task path fetches
+// them itself, next to the q/k rows: held from here on, they were spilled, and a spill waits for its load).
+template <bool NORMW = true>
 __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int task,
                                           int l16, AttnTask& a, int* pgc = nullptr, bool fill = false,
                                           int* geom = nullptr) {
@@ -1911,11 +1920,13 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
       geom[5] = a.p0; geom[6] = a.p1; geom[7] = a.nch; geom[8] = a.kv_base;
     }
   }
-  const int pos = min(a.L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
-  a.wq = __ldg(reinterpret_cast<const uint4*>(op.q_norm_w) + l16);
-  a.wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
-  a.cs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
-  a.sn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
+  if constexpr (NORMW) {
+    const int pos = min(a.L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
+    a.wq = __ldg(reinterpret_cast<const uint4*>(op.q_norm_w) + l16);
+    a.wk = __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16);
+    a.cs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
+    a.sn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
+  }
   if (pgc != nullptr && !fill) {
     a.new_page = pgc[4];
   } else {
@@ -1933,13 +1944,17 @@ __device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16
                                         uint2* ll_out, unsigned tag) {
   const int nout = qpk * kHeadDim;
   constexpr int kMergeBatch = 8;
+  // a thread merges outputs e and e + 256 side by side: one round of loads for up to eight chunks of both
 #pragma unroll 1
-  for (int e = c.tid; e < nout; e += kNumConsumers) {
+  for (int e = c.tid; e < nout; e += 2 * kNumConsumers) {
+    const bool two = e + kNumConsumers < nout;
+    const int e2 = two ? e + kNumConsumers : e;
     const float* pm = base + nout + (e >> 7);
-    float M = -INFINITY, Ls = 0.f, O = 0.f;
+    const float* pm2 = base + nout + (e2 >> 7);
+    float M = -INFINITY, Ls = 0.f, O = 0.f, M2 = -INFINITY, Ls2 = 0.f, O2 = 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < nch; c0 += kMergeBatch) {
-      float v[kMergeBatch], mm[kMergeBatch], ll[kMergeBatch];
+      float v[kMergeBatch], mm[kMergeBatch], ll[kMergeBatch], v2[kMergeBatch], mm2[kMergeBatch], ll2[kMergeBatch];
 #pragma unroll
       for (int u = 0; u < kMergeBatch; ++u) {
         const bool ok = c0 + u < nch;
@@ -1947,29 +1962,127 @@ __device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16
         v[u] = ok ? __ldcg(base + off + e) : 0.f;
         mm[u] = ok ? __ldcg(pm + off) : -INFINITY;
         ll[u] = ok ? __ldcg(pm + off + qpk) : 0.f;
+        v2[u] = ok ? __ldcg(base + off + e2) : 0.f;
+        mm2[u] = ok ? __ldcg(pm2 + off) : -INFINITY;
+        ll2[u] = ok ? __ldcg(pm2 + off + qpk) : 0.f;
+      }
+      float Mb = M, Mb2 = M2;
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u) {
+        Mb = fmaxf(Mb, mm[u]);
+        Mb2 = fmaxf(Mb2, mm2[u]);
+      }
+      const float r = exp2f(M - Mb), r2 = exp2f(M2 - Mb2);  // 0 for the first batch (every chunk holds at least one position)
+      O *= r;
+      Ls *= r;
+      O2 *= r2;
+      Ls2 *= r2;
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u) {
+        const float f = exp2f(mm[u] - Mb), f2 = exp2f(mm2[u] - Mb2);
+        O = fmaf(f, v[u], O);
+        Ls = fmaf(f, ll[u], Ls);
+        O2 = fmaf(f2, v2[u], O2);
+        Ls2 = fmaf(f2, ll2[u], Ls2);
+      }
+      M = Mb;
+      M2 = Mb2;
+    }
+    const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls)), y2 = __float2bfloat16_rn(__fdividef(O2, Ls2));
+    out[e] = y;
+    if (two) out[e2] = y2;
+    if (MK_LL_ATTN && ll_out != nullptr) {  // (whole warps take the same trips: nout is a multiple of 128)
+      const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y), lo2 = (uint32_t)__bfloat16_as_ushort(y2);
+      const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1), hi2 = __shfl_down_sync(0xffffffffu, lo2, 1);
+      if (!(e & 1)) {
+        st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
+        if (two) st_gpu_v2(ll_out + (e2 >> 1), lo2 | (hi2 << 16), tag);
+      }
+    }
+  }
+}
+
+// The merge without a counter: every chunk stores its partial (output sums, then max and sum per q head) as
+// tagged 8-byte words, and every chunk CTA then merges its own slice of the output elements, polling the
+// words of all chunks it needs: no atomic round trip, no last arriver doing all of it, one output per
+// thread.  (A CTA stores its own partial before it waits for any other, and the chunks of one pair are
+// consecutive tasks, so a wait never depends on a later task of the waiting CTA.)
+__device__ __noinline__ float ll_wait_word(const Ctx& c, const uint2* w, unsigned tag) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    const uint2 q = ld_gpu_v2(w);
+    if (q.y == tag) return __uint_as_float(q.x);
+    if (((++spins) & 63u) == 0) {
+      if (aborted(c)) return 0.f;
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2 * c.p.timeout_ns) {
+        raise_abort(c, ST_TIMEOUT_DATA, (int)tag, (int)q.y);
+        return 0.f;
+      }
+    }
+  }
+}
+__device__ __noinline__ void attn_merge_ll(Ctx& c, const uint2* base, __nv_bfloat16* out, uint2* ll_out, int nch, int ch, int qpk,
+                                           int part_stride, unsigned tag) {
+  const int nout = qpk * kHeadDim;
+  const int S = (((nout + nch - 1) / nch) + 1) & ~1;  // outputs per chunk CTA, even: a bf16 pair never straddles two slices
+  const int e = ch * S + c.tid;
+  const bool act = c.tid < S && e < nout;
+  float y = 0.f;
+  if (act) {
+    constexpr int kBatch = 8;
+    const uint2* pv = base + e;
+    const uint2* pm = base + nout + (e >> 7);
+    float M = -INFINITY, Ls = 0.f, O = 0.f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < nch; c0 += kBatch) {
+      uint2 qv[kBatch], qm[kBatch], ql[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const bool ok = c0 + u < nch;
+        const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
+        qv[u] = ld_gpu_v2(pv + off);
+        qm[u] = ld_gpu_v2(pm + off);
+        ql[u] = ld_gpu_v2(pm + off + qpk);
+      }
+      float v[kBatch], mm[kBatch], ll[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const bool ok = c0 + u < nch;
+        const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
+        v[u] = qv[u].y == tag ? __uint_as_float(qv[u].x) : ll_wait_word(c, pv + off, tag);
+        mm[u] = qm[u].y == tag ? __uint_as_float(qm[u].x) : ll_wait_word(c, pm + off, tag);
+        ll[u] = ql[u].y == tag ? __uint_as_float(ql[u].x) : ll_wait_word(c, pm + off + qpk, tag);
+        if (!ok) {
+          v[u] = 0.f;
+          mm[u] = -INFINITY;
+          ll[u] = 0.f;
+        }
       }
       float Mb = M;
 #pragma unroll
-      for (int u = 0; u < kMergeBatch; ++u) Mb = fmaxf(Mb, mm[u]);
+      for (int u = 0; u < kBatch; ++u) Mb = fmaxf(Mb, mm[u]);
       const float r = exp2f(M - Mb);  // 0 for the first batch (every chunk holds at least one position)
       O *= r;
       Ls *= r;
 #pragma unroll
-      for (int u = 0; u < kMergeBatch; ++u) {
+      for (int u = 0; u < kBatch; ++u) {
         const float f = exp2f(mm[u] - Mb);
         O = fmaf(f, v[u], O);
         Ls = fmaf(f, ll[u], Ls);
       }
       M = Mb;
     }
-    const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls));
-    out[e] = y;
-    if (MK_LL_ATTN && ll_out != nullptr) {  // (the loop's trip count is the same for all lanes of a warp: nout is a multiple of 128)
-      const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
-      const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
-      if (!(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
-    }
+    y = __fdividef(O, Ls);
   }
+  const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+  if (act) out[e] = yb;
+  const uint32_t lo = (uint32_t)__bfloat16_as_ushort(yb);
+  const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+  if (act && ll_out != nullptr && !(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
 }
 
 // The half-warp's pass over its positions of the task: for up to four q heads of the kv-head
@@ -2180,7 +2293,7 @@ __device__ __noinline__ bool attn_barrier_then_append(Ctx& c, const OpDesc& op, 
     const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
     F8 kf;
     unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-    kf = head_norm_rope(kf, wk, cs, sn, l16, op.flags, p.numerics, dbl_k);
+    kf = head_norm_rope(kf, wk, cs, sn, l16, op.flags, MK_NUM(p), dbl_k);
     const int pg = __ldcg(p.kv_indices + lens[kAttnLensMax + t] + ((L - 1) >> p.page_shift));
     if (c.lane < 16) {
       const size_t dst = ((((size_t)pg << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + h) * kHeadDim;
@@ -2250,13 +2363,13 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
     for (int h = lw; h < hq; h += wpg) {  // this warp's share of the q heads
       F8 q;
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + h * kHeadDim) + l16), q.v);
-      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, MK_NUM(p), dbl_q);
       if (c.lane < 16) sm_q[h * 16 + l16] = pack8(q.v);
     }
     if (lw == wpg - 1) {  // the group's last warp also prepares the new k
       F8 kf;
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, MK_NUM(p), dbl_k);
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
@@ -2430,7 +2543,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
 #pragma unroll 1
   for (int task = blockIdx.x;; task += G) {
     AttnTask a;
-    attn_prepare(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
+    attn_prepare<false>(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;
@@ -2464,21 +2577,49 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     const bool ll_in = MK_LL_ATTN && (op.flags & F_LL_IN) && !chunked;
     const uint2* llr = ll_row(op.ll_in, op.ld_in, a.t) + ((a.h * (pl.qpk + 2) * kHeadDim) >> 1);
     const unsigned tag_in = ll_tag_of(c, op.ll_in_op);
-    const uint4 vnew = ll_in ? ll_gather8(c, llr, (pl.qpk + 1) * kHeadDim + l16 * 8, tag_in)
-                             : __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+    const bool do_q = c.warp < pl.qpk, do_k = c.warp == kw;
+    uint4 vnew, xq = make_uint4(0, 0, 0, 0), xk = make_uint4(0, 0, 0, 0);
+    // norm weights and the cos/sin row of the position, for the warps that prepare a head
+    uint4 nw = make_uint4(0, 0, 0, 0), ncs = nw, nsn = nw;
+    if (do_q || do_k) {
+      const int pos = min(L - 1, op.aux2 - 1);  // aux2 = rows of the cos/sin tables
+      nw = __ldg(reinterpret_cast<const uint4*>(do_q ? op.q_norm_w : op.k_norm_w) + l16);
+      ncs = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.cos) + (size_t)pos * kHeadDim) + l16);
+      nsn = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(op.sin) + (size_t)pos * kHeadDim) + l16);
+    }
+    if (ll_in) {  // all loads first, then whatever has not arrived is polled
+      const uint4* sv = reinterpret_cast<const uint4*>(llr + (((pl.qpk + 1) * kHeadDim + l16 * 8) >> 1));
+      const uint4* sq = reinterpret_cast<const uint4*>(llr + ((c.warp * kHeadDim + l16 * 8) >> 1));
+      const uint4* sk = reinterpret_cast<const uint4*>(llr + ((pl.qpk * kHeadDim + l16 * 8) >> 1));
+      const uint4 v0 = ld_gpu_v4(sv), v1 = ld_gpu_v4(sv + 1);
+      uint4 q0 = v0, q1 = v1, k0 = v0, k1 = v1;
+      if (do_q) {
+        q0 = ld_gpu_v4(sq);
+        q1 = ld_gpu_v4(sq + 1);
+      }
+      if (do_k) {
+        k0 = ld_gpu_v4(sk);
+        k1 = ld_gpu_v4(sk + 1);
+      }
+      vnew = ll_take8(c, sv, v0, v1, tag_in);
+      if (do_q) xq = ll_take8(c, sq, q0, q1, tag_in);
+      if (do_k) xk = ll_take8(c, sk, k0, k1, tag_in);
+    } else {
+      vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
+      if (do_q) xq = __ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16);
+      if (do_k) xk = __ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16);
+    }
     // norm + RoPE once per CTA: warp w < qpk prepares q head w, one warp the new k
-    if (c.warp < pl.qpk) {
+    if (do_q) {
       F8 q;
-      unpack8(ll_in ? ll_gather8(c, llr, c.warp * kHeadDim + l16 * 8, tag_in)
-                    : __ldcg(reinterpret_cast<const uint4*>(row + c.warp * kHeadDim) + l16), q.v);
-      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
+      unpack8(xq, q.v);
+      q = head_norm_rope(q, nw, ncs, nsn, l16, op.flags, MK_NUM(p), dbl_q);
       if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
     }
-    if (c.warp == kw) {
+    if (do_k) {
       F8 kf;
-      unpack8(ll_in ? ll_gather8(c, llr, pl.qpk * kHeadDim + l16 * 8, tag_in)
-                    : __ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
+      unpack8(xk, kf.v);
+      kf = head_norm_rope(kf, do_q ? __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16) : nw, ncs, nsn, l16, op.flags, MK_NUM(p), dbl_k);
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
@@ -2509,6 +2650,9 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     }
     consumer_sync();
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
+    // tagged partials (see attn_merge_ll) when the op's output is tagged and the host gave them room
+    const bool ll_part = MK_LL_ATTN && (op.flags & F_LL_OUT) && p.attn_part_ll != nullptr;
+    uint2* partw = p.attn_part_ll + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
     uint2* ll_out = (MK_LL_ATTN && (op.flags & F_LL_OUT)) ? reinterpret_cast<uint2*>(op.ll_out) + (size_t)a.t * (size_t)(op.ld_out >> 1) +
@@ -2537,6 +2681,12 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
           const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
           if (!(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), ll_tag_of(c, c.cur_op));
         }
+      } else if (ll_part) {
+        st_gpu_v2(partw + e, __float_as_uint(O), ll_tag_of(c, c.cur_op));
+        if (d == 0) {
+          st_gpu_v2(partw + pl.qpk * kHeadDim + eh, __float_as_uint(M), ll_tag_of(c, c.cur_op));
+          st_gpu_v2(partw + pl.qpk * kHeadDim + pl.qpk + eh, __float_as_uint(Ls), ll_tag_of(c, c.cur_op));
+        }
       } else {
         part[e] = O;
         if (d == 0) {
@@ -2546,7 +2696,9 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       }
     }
     MK_STAMP(c, 4);
-    if (a.nch > 1) {
+    if (a.nch > 1 && ll_part) {
+      attn_merge_ll(c, partw - (size_t)a.ch * part_stride, out, ll_out, a.nch, a.ch, pl.qpk, part_stride, ll_tag_of(c, c.cur_op));
+    } else if (a.nch > 1) {
       consumer_sync();  // the CTA's partial is complete; thread 0's release below publishes all of it
       MK_STAMP(c, 5);
       volatile int* fl = c.flags();
@@ -2944,7 +3096,7 @@ __device__ void op_moe_combine(Ctx& c, const OpDesc& op, int T) {
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
-  const bool torch_num = c.p.numerics == NUM_TORCH;
+  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
 #pragma unroll 1
   for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
     const int t = u / nvec, v = u % nvec;

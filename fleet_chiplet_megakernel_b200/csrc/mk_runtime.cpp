@@ -1318,11 +1318,28 @@ static int compile_program(mk_handle* h, bool first) {
       }
     }
   }
+  // the attention chunks' partials as tagged words too (merged without a counter), in the same arena.  (The
+  // chunks of a pair must be tasks of one round, or of consecutive CTAs across two: at least 64 CTAs.)
+  size_t ll_part_off = 0;
+  bool ll_part = false;
+  for (const PlanOp& po : h->plan) ll_part = ll_part || (po.type == mk::OP_ATTN && (po.flags & mk::F_LL_OUT));
+  ll_part = ll_part && h->grid >= 64;
+  if (ll_part) {
+    int hkv = 1, qpk = 2;
+    for (const PlanOp& po : h->plan)
+      if (po.type == mk::OP_ATTN) {
+        hkv = std::max(hkv, po.aux0);
+        qpk = std::max(qpk, po.aux1 / po.aux0);
+      }
+    ll_part_off = ll_bytes;
+    ll_bytes += ((size_t)h->plan_tokens * hkv * kAttnMaxChunks * qpk * (mk::kHeadDim + 2) * 8 + 255) / 256 * 256;
+  }
   h->ll_buf = nullptr;
   h->ll_bytes = ll_bytes;
   if (ll_bytes > 0) {
     if (int e = h->dmalloc(&h->ll_buf, ll_bytes)) return e;
   }
+  kp.attn_part_ll = ll_part ? (uint2*)((char*)h->ll_buf + ll_part_off) : nullptr;
 
   // 3. scratch and state
   const int G = h->grid;

@@ -193,6 +193,7 @@ struct KParams {
   float* attn_part;       // [tokens][kv heads][max chunks][qpk*(128+2)]
   unsigned* attn_count;   // [tokens][kv heads]
   int attn_max_chunks;
+  uint2* attn_part_ll;    // the same partials as tagged 8-byte words {fp32, tag}, for the merge without a counter (null: not used)
   // tensor-parallel exchange: every rank's exchange region mapped into this GPU's address space
   // (xchg[rank] is the local one).  A region holds slots [2][world][xchg_tokens][xchg_cols] of 8-byte
   // words {fp32 value, sequence number}: a word is valid for exchange number s once its second half
