@@ -609,6 +609,48 @@ __device__ __forceinline__ const uint2* ll_row(const void* base, int ld, int tok
 // the tag of what program op `op` stores in the current iteration
 __device__ __forceinline__ unsigned ll_tag_of(const Ctx& c, int op) { return ll_tag(c.iter, c.p.num_ops, op); }
 
+#if MK_WITH_XCHG
+// Tensor parallelism, row-owner path: the reader of an exchange does not add up all of it in every CTA
+// (that is `world` dependent round trips per CTA and `world` times the row in loads).  Every CTA adds up
+// its own slice of the columns, in rank order in fp32 with one bf16 rounding (the same value on every
+// rank), and stores it as tagged words; all CTAs then stage the row from those words like any other
+// tagged input: two round trips whatever the number of ranks.
+__device__ __noinline__ void xchg_reduce_slice(Ctx& c, const OpDesc& op, int T) {
+  const KParams& p = c.p;
+  const int pairs = op.k >> 1;
+  const int p0 = (int)((long long)blockIdx.x * pairs / gridDim.x), p1 = (int)((long long)(blockIdx.x + 1) * pairs / gridDim.x);
+  const int w = p1 - p0;
+  const unsigned seq = xchg_cur(c);
+  const unsigned tag = ll_tag_of(c, c.cur_op);
+  uint2* dst = reinterpret_cast<uint2*>(const_cast<void*>(op.ll_in));
+#pragma unroll 1
+  for (int i = c.tid; i < w * T; i += kNumConsumers) {
+    const int tok = i / w, pr = p0 + i % w;
+    uint4 q[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r < p.world)
+        q[r] = ld_sys_v4(reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(p.xchg[p.rank]) +
+                                                        xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, r, tok, 2 * pr)));
+    }
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r < p.world) {
+        if (!xchg_arrived(q[r].y, seq) || !xchg_arrived(q[r].w, seq)) {
+          const uint2* w2 = reinterpret_cast<const uint2*>(p.xchg[p.rank]) + xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, r, tok, 2 * pr);
+          if (!xchg_wait_word(c, w2, seq, r) || !xchg_wait_word(c, w2 + 1, seq, r)) return;
+          q[r] = ld_sys_v4(reinterpret_cast<const uint4*>(w2));
+        }
+        a0 += __uint_as_float(q[r].x);
+        a1 += __uint_as_float(q[r].z);
+      }
+    }
+    st_gpu_v2(dst + (size_t)tok * (size_t)(op.ld_in >> 1) + pr, pack2(a0, a1), tag);
+  }
+}
+#endif
+
 // ------------------------------------------------------------------------------------
 __device__ __noinline__ float torch_rsqrt_bf16(float var, bool dbl);
 
@@ -1748,6 +1790,9 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
       }
     }
   }
+#if MK_WITH_XCHG
+  if (op.flags & F_XRED) xchg_reduce_slice(c, op, T);
+#endif
   if (op.flags & F_LL_IN) {
     // No barrier, and no look at the abort flag either (a round trip to L2 per op): the polls of the
     // tagged input and the stage waits watch it, and an aborted iteration ends at its closing barrier.
