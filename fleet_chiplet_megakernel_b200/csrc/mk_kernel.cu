@@ -1934,7 +1934,7 @@ __device__ __forceinline__ void attn_fetch_rows(const Ctx& c, const OpDesc& op, 
 
 // NORMW: also fetch the norm weights and the cos/sin row of the task's position (the single-task path fetches
 // them itself, next to the q/k rows: held from here on, they were spilled, and a spill waits for its load).
-template <bool NORMW = true>
+template <bool NORMW = true, bool FETCH = true>
 __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const int* lens, int task,
                                           int l16, AttnTask& a, int* pgc = nullptr, bool fill = false,
                                           int* geom = nullptr) {
@@ -1978,7 +1978,7 @@ __device__ __forceinline__ void attn_prepare(const Ctx& c, const OpDesc& op, con
     a.new_page = (a.p1 == a.L) ? __ldcg(c.p.kv_indices + a.kv_base + ((a.L - 1) >> c.p.page_shift)) : 0;
     if (pgc != nullptr) pgc[4] = a.new_page;
   }
-  attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr, pgc, fill);
+  if constexpr (FETCH) attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr, pgc, fill);
 }
 
 // Merge of a (request, kv head)'s chunks by the CTA that arrived last: kept out of line, only a
@@ -2479,6 +2479,153 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
 
 // aux0 = kv heads, aux1 = q heads (q heads per kv head: 1, 2, 4 or 8).  Tokens: one per
 // request, token t == request slot t.
+// The pass of a task over its positions on the tensor cores (wider batches; up to four q heads per kv head).
+// One warp takes 16 positions at a time (tiles warp, warp + 8, ... of the task's range) for all q heads:
+//   S = Q K^T   mma.m16n8k16, M = the q heads (rows 4..15 are padding), N = 8 positions, K = 128 dims in 8 steps
+//   O += P V    M = the q heads, K = 16 positions, N = 128 dims in 16 tiles of 8
+// with the fragments loaded STRAIGHT from the cache rows, no shared-memory staging and no ldmatrix: a dot
+// product does not care in which order the dims are walked, so k step s of lane j of a quad stands for dims
+// 32 (s / 2) + 8 j + 4 (s % 2) + {0..3} (the quad reads 64 contiguous bytes of the K row of position lane / 4
+// per load), and output column n of tile t stands for dim 64 (t / 8) + 8 n + t % 8 (eight lanes read 128
+// contiguous bytes of a V row per load; two rows are paired up per register with byte permutes).  The scalar pass (attn_rows1) issued about twenty times the instructions per position.
+// Leaves (max, sum, output) of slot warp * qpk + head in shared memory for the combine.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+// (rows 8..15 of the M side are padding: their two accumulators are scratch registers shared by all tiles)
+__device__ __forceinline__ void mma_bf16_top(float& c0, float& c1, float& z0, float& z1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1)
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __noinline__ void attn_tc_rows(const Ctx& c, const OpDesc& op, const AttnPlan& pl, const AttnTask& a, const uint4* sm_q,
+                                          const uint4* sm_knew, const uint4* sm_vnew, float sc, float* sm_o, float* sm_m,
+                                          float* sm_l, const int* pgt, bool subst_new) {
+  const int lane = c.lane, g = lane >> 2, j = lane & 3;
+  const int psh = c.p.page_shift, pmask = c.p.page_size - 1;
+  const bool hv = g < pl.qpk;
+  uint32_t qa0[8], qa2[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const uint2 v = hv ? *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(sm_q) + g * 256 + (32 * (s >> 1) + 8 * j + 4 * (s & 1)) * 2)
+                       : make_uint2(0u, 0u);
+    qa0[s] = v.x;
+    qa2[s] = v.y;
+  }
+  float m = -INFINITY, l = 0.f;
+  float oacc[16][2], z0 = 0.f, z1 = 0.f;
+#pragma unroll
+  for (int t = 0; t < 16; ++t) oacc[t][0] = oacc[t][1] = 0.f;
+  const int base_slot = a.p0 >> psh;
+  const int ntiles = (a.p1 - a.p0 + 15) >> 4;
+  const char* kc = reinterpret_cast<const char*>(op.k_cache);
+  const char* vc = reinterpret_cast<const char*>(op.v_cache);
+#pragma unroll 1
+  for (int ti = c.warp; ti < ntiles; ti += kNumConsumerWarps) {
+    const int pos0 = a.p0 + 16 * ti;
+    // K: positions pos0 + g and pos0 + 8 + g, dims [32 j, 32 j + 32)
+    uint4 kr[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int pos = pos0 + 8 * u + g;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kr[u][i] = make_uint4(0u, 0u, 0u, 0u);
+      if (pos < a.p1) {
+        if (subst_new && pos == a.L - 1) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) kr[u][i] = sm_knew[4 * i + j];
+        } else {
+          const int slot = (pos >> psh) - base_slot;
+          const int pg = slot < 32 ? pgt[slot] : __ldcg(c.p.kv_indices + a.kv_base + (pos >> psh));
+          const uint4* src = reinterpret_cast<const uint4*>(kc + ((((size_t)pg << psh) + (pos & pmask)) * pl.HKV + a.h) * (kHeadDim * 2)) + j;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) kr[u][i] = __ldcg(src + 4 * i);  // a quad reads 64 contiguous bytes per load
+        }
+      }
+    }
+    // V: positions pos0 + 2 j + {0, 1} and pos0 + 8 + 2 j + {0, 1}, dims [16 g, 16 g + 16)
+    uint4 vr[4][2];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int pos = pos0 + 2 * j + (r & 1) + 8 * (r >> 1);
+      vr[r][0] = vr[r][1] = make_uint4(0u, 0u, 0u, 0u);
+      if (pos < a.p1) {
+        if (subst_new && pos == a.L - 1) {
+          vr[r][0] = sm_vnew[g];
+          vr[r][1] = sm_vnew[8 + g];
+        } else {
+          const int slot = (pos >> psh) - base_slot;
+          const int pg = slot < 32 ? pgt[slot] : __ldcg(c.p.kv_indices + a.kv_base + (pos >> psh));
+          const uint4* src = reinterpret_cast<const uint4*>(vc + ((((size_t)pg << psh) + (pos & pmask)) * pl.HKV + a.h) * (kHeadDim * 2)) + g;
+          vr[r][0] = __ldcg(src);  // the eight lanes with this j read 128 contiguous bytes per load
+          vr[r][1] = __ldcg(src + 8);
+        }
+      }
+    }
+    // S = Q K^T for the two groups of 8 positions
+    float sv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const uint4& k0 = kr[0][s >> 1];
+      const uint4& k1 = kr[1][s >> 1];
+      mma_bf16_top(sv[0], sv[1], z0, z1, qa0[s], qa2[s], (s & 1) ? k0.z : k0.x, (s & 1) ? k0.w : k0.y);
+      mma_bf16_top(sv[2], sv[3], z0, z1, qa0[s], qa2[s], (s & 1) ? k1.z : k1.x, (s & 1) ? k1.w : k1.y);
+    }
+    // this lane: head g at positions pos0 + 2 j + {0, 1} (sv[0], sv[1]) and pos0 + 8 + 2 j + {0, 1} (sv[2], sv[3])
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int pos = pos0 + 2 * j + (i & 1) + 8 * (i >> 1);
+      sv[i] = pos < a.p1 ? sv[i] * sc : -INFINITY;
+      tmax = fmaxf(tmax, sv[i]);
+    }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const float mn = fmaxf(m, tmax);  // finite: the tile holds at least one position of the range
+    const float alpha = exp2f(m - mn);
+    float pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = exp2f(sv[i] - mn);
+    l = l * alpha + ((pr[0] + pr[1]) + (pr[2] + pr[3]));  // this lane's share of the row sum: the quad adds up at the end
+    m = mn;
+    const uint32_t pa0 = pack2(pr[0], pr[1]), pa2 = pack2(pr[2], pr[3]);
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      oacc[t][0] *= alpha;
+      oacc[t][1] *= alpha;
+      // dim 16 g + t of the four V rows: element t of the lane's 16, two rows per register
+      const uint4& a0 = vr[0][t >> 3];
+      const uint4& a1 = vr[1][t >> 3];
+      const uint4& a2 = vr[2][t >> 3];
+      const uint4& a3 = vr[3][t >> 3];
+      const int w = (t >> 1) & 3;
+      const uint32_t w0 = w == 0 ? a0.x : (w == 1 ? a0.y : (w == 2 ? a0.z : a0.w));
+      const uint32_t w1 = w == 0 ? a1.x : (w == 1 ? a1.y : (w == 2 ? a1.z : a1.w));
+      const uint32_t w2 = w == 0 ? a2.x : (w == 1 ? a2.y : (w == 2 ? a2.z : a2.w));
+      const uint32_t w3 = w == 0 ? a3.x : (w == 1 ? a3.y : (w == 2 ? a3.z : a3.w));
+      const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+      mma_bf16_top(oacc[t][0], oacc[t][1], z0, z1, pa0, pa2, prmt(w0, w1, sel), prmt(w2, w3, sel));
+    }
+  }
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (hv) {
+    const int w = c.warp * pl.qpk + g;
+    if (j == 0) {
+      sm_m[w] = m;
+      sm_l[w] = l;
+    }
+    float* dst = sm_o + w * kHeadDim + 16 * j;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      dst[64 * (t >> 3) + (t & 7)] = oacc[t][0];
+      dst[64 * (t >> 3) + 8 + (t & 7)] = oacc[t][1];
+    }
+  }
+}
+
 template <int PATH>
 __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
@@ -2527,6 +2674,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   pl.qpk = op.aux1 / op.aux0;
   int* plan = pgs + 16;   // [0] chunk size, [1] chunks of the longest request, [2] tasks: the same in every layer of an iteration
   int* geom = plan + 3;   // [9]: the CTA's first task, see attn_prepare
+  bool all_short;         // no sequence of the iteration is longer than 256 tokens (bit 8 of plan[1])
   if (fill) {
     int Lmax = 1;
 #pragma unroll 1
@@ -2540,23 +2688,30 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     pl.CS = bpc * 16;
     pl.nch_max = (nb_max + bpc - 1) / bpc;
     pl.ntasks = T * pl.HKV * pl.nch_max;
+    all_short = Lmax <= 256;
     if (c.tid == 0) {
       plan[0] = pl.CS;
-      plan[1] = pl.nch_max;
+      plan[1] = pl.nch_max | (all_short ? 256 : 0);
       plan[2] = pl.ntasks;
     }
   } else {
     pl.CS = plan[0];
-    pl.nch_max = plan[1];
+    pl.nch_max = plan[1] & 255;
+    all_short = (plan[1] & 256) != 0;
     pl.ntasks = plan[2];
   }
-  // More (request, kv head) pairs than CTAs and no sequence that needs splitting: several pairs per CTA at a time.
+  // More (request, kv head) pairs than CTAs, all of them short: several pairs side by side per CTA (the fixed
+  // cost of a pair, about 12 us, dominates; measured at 64 requests of 100 tokens: 48 us against 68 us one
+  // pair at a time).
   if constexpr (PATH == PATH_UMMA) {
-    if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4) {
+    if (pl.nch_max == 1 && pl.ntasks > G && pl.qpk <= 4 && all_short) {
       attention_groups(c, op, pl, lens, pl.ntasks > 2 * G ? 2 : 4, T, *multi != 0);
       return;
     }
   }
+  // wider batches: the pass over the positions runs on the tensor cores (up to four q heads per kv head; measured
+  // at 16 requests: 20 us against 24 us at 100 tokens, 33 us against 83 us at 600; slower below 9 batched tokens)
+  const bool tc = PATH != PATH_ROWS && pl.qpk <= 4 && p.x_rows >= 16;
   const int l16 = c.lane & 15;
   // Half-warp hw serves q head (hw % qpk) of the kv-head group for the positions of group
   // (hw / qpk): one head per thread keeps the row loop and the combine small (this code runs
@@ -2564,15 +2719,18 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
   // same K/V rows, so their loads share a request.
   const int hw = 2 * c.warp + (c.lane >> 4);
   const int head = hw % pl.qpk;
-  pl.ngroups = 16 / pl.qpk;
+  pl.ngroups = tc ? kNumConsumerWarps : 16 / pl.qpk;  // slots per head in the combine: warps, or half-warp groups
   pl.gi = hw / pl.qpk;
   const int part_stride = pl.qpk * (kHeadDim + 2);
   const float sc = 1.4426950408889634f * 0.08838834764831845f;  // log2(e) / sqrt(128)
   uint4* sm_q = reinterpret_cast<uint4*>(c.smem + p.x_off);     // [8 heads][16 lanes]: q after norm and RoPE
   uint4* sm_k = sm_q + 8 * 16;                                  // [16 lanes]: the new k
-  float* sm_o = reinterpret_cast<float*>(sm_k + 16);            // [16 half-warps][128]
-  float* sm_m = sm_o + 16 * kHeadDim;                           // [16 half-warps]
-  float* sm_l = sm_m + 16;
+  uint4* sm_v = sm_k + 16;                                      // [16 lanes]: the new v (tensor-core pass)
+  const int nslots = tc ? kNumConsumerWarps * pl.qpk : 16;
+  float* sm_o = reinterpret_cast<float*>(sm_v + 16);            // [slots][128]: 16 half-warps, or warp x head
+  float* sm_m = sm_o + nslots * kHeadDim;                       // [slots]
+  float* sm_l = sm_m + nslots;
+  int* pgt = reinterpret_cast<int*>(sm_l + nslots);             // [32]: page numbers of the task's range (tensor-core pass)
   const bool dbl_q = op.aux1 < 32, dbl_k = op.aux0 < 32;
   const int kw = pl.qpk & 7;  // the warp that prepares the new k (warp 0 when all eight prepare q heads)
 
@@ -2588,7 +2746,10 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
 #pragma unroll 1
   for (int task = blockIdx.x;; task += G) {
     AttnTask a;
-    attn_prepare<false>(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
+    if constexpr (PATH == PATH_ROWS)
+      attn_prepare<false>(c, op, pl, lens, task, l16, a, (first && !chunked) ? pgc : nullptr, fill, (first && !chunked) ? geom : nullptr);
+    else
+      attn_prepare<false, false>(c, op, pl, lens, task, l16, a, nullptr, true, nullptr);
     if (first) {
       // everything above is independent of this layer's QKV rows: fetched ahead of the barrier
       first = false;
@@ -2597,7 +2758,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
           const int slot = (a.p0 >> p.page_shift) + c.tid;
           if ((slot << p.page_shift) < a.p1) pgs[c.tid] = __ldcg(p.kv_indices + a.kv_base + slot);
         }
-        attn_l2_ahead(c, op, pl, a, l16, fill ? nullptr : pgs);
+        if constexpr (PATH == PATH_ROWS) attn_l2_ahead(c, op, pl, a, l16, fill ? nullptr : pgs);
       }
       MK_STAMP(c, 1);
       if (op.flags & F_SYNC_BEFORE) {  // op_barrier, with the wait inlined
@@ -2668,6 +2829,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
+        sm_v[l16] = vnew;
         if (a.p1 == L && !chunked) {  // the last chunk appends the new token's K and V to the cache
           const size_t dst = ((((size_t)a.new_page << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + a.h) * kHeadDim;
           reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(op.k_cache) + dst)[l16] = kn;
@@ -2675,16 +2837,27 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         }
       }
     }
+    if (PATH != PATH_ROWS && tc && c.tid < 32) {  // the page numbers of the task's range, for the tensor-core pass
+      const int slot = (a.p0 >> p.page_shift) + c.tid;
+      if ((slot << p.page_shift) < a.p1) pgt[c.tid] = __ldcg(p.kv_indices + a.kv_base + slot);
+    }
     consumer_sync();
-    const uint4 qv = sm_q[head * 16 + l16];
-    const uint4 knew = sm_k[l16];
     MK_STAMP(c, 2);
-    float m, l, o[8];
-    attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, (task == (int)blockIdx.x && !chunked) ? pgs : nullptr);
-    MK_STAMP(c, 3);
-    // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
-    // elements then combines the position groups of each head
-    {
+    bool done_rows = false;
+    if constexpr (PATH != PATH_ROWS) {
+      if (tc) {
+        attn_tc_rows(c, op, pl, a, sm_q, sm_k, sm_v, sc, sm_o, sm_m, sm_l, pgt, !chunked);
+        done_rows = true;
+      }
+    }
+    if (!done_rows) {
+      const uint4 qv = sm_q[head * 16 + l16];
+      const uint4 knew = sm_k[l16];
+      float m, l, o[8];
+      if constexpr (PATH != PATH_ROWS) attn_fetch_rows(c, op, pl, a, 0, l16, a.kr, a.vr);  // (nothing was fetched ahead)
+      attn_rows1(c, op, pl, a, l16, qv, knew, vnew, sc, m, l, o, (task == (int)blockIdx.x && !chunked) ? pgs : nullptr);
+      // every half-warp leaves its (max, sum, output) in shared memory; one pass over the output
+      // elements then combines the position groups of each head
       float* dst = sm_o + hw * kHeadDim + l16 * 8;
       reinterpret_cast<float4*>(dst)[0] = make_float4(o[0], o[1], o[2], o[3]);
       reinterpret_cast<float4*>(dst)[1] = make_float4(o[4], o[5], o[6], o[7]);
@@ -2693,6 +2866,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         sm_l[hw] = l;
       }
     }
+    MK_STAMP(c, 3);
     consumer_sync();
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     // tagged partials (see attn_merge_ll) when the op's output is tagged and the host gave them room

@@ -1196,6 +1196,8 @@ static int compile_program(mk_handle* h, bool first) {
       // above 16 tokens several (request, kv head) pairs run side by side in a CTA: q/k per group
       // (4 x 1280 B) and one combine slot per warp (8 x 4 heads x 128 floats + (max, sum) pairs)
       if (x_rows >= 32) x_bytes = std::max(x_bytes, 4 * 1280 + 8 * 4 * mk::kHeadDim * 4 + 8 * 4 * 2 * 4);
+      // the tensor-core pass of the wider paths: q heads, new k and v, (warp x head) combine slots, page numbers
+      if (!rows_mode) x_bytes = std::max(x_bytes, 10 * 256 + 8 * 4 * (mk::kHeadDim + 2) * 4 + 128 + 256);
     }
   }
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
