@@ -41,6 +41,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--context", type=int, default=100, help="tokens in the KV cache at the traced iteration")
     ap.add_argument("--cluster", type=int, default=0, help="CTAs per cluster for the hierarchical grid barrier (0/1: flat)")
+    ap.add_argument("--debug-flags", type=int, default=0,
+                    help="measurement switches of the library (16: no tagged activations, every op keeps its grid barrier)")
     args = ap.parse_args()
     g = Qwen3Geometry(layers=args.layers)
     dev = torch.device("cuda")
@@ -48,7 +50,7 @@ def main():
     prompt_len = 16
     iters = args.context
     dec = Qwen3Decoder(g, w, max_seq_length=max(1200, iters + 8), max_requests=args.batch, page_size=64,
-                       max_iterations=iters, trace=True, cluster_size=args.cluster)
+                       max_iterations=iters, trace=True, cluster_size=args.cluster, debug_flags=args.debug_flags)
     gen = torch.Generator().manual_seed(1000)
     prompts = [torch.randint(0, g.vocab, (prompt_len,), generator=gen) for _ in range(args.batch)]
     for _ in range(2):
