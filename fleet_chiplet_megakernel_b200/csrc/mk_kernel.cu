@@ -38,21 +38,6 @@
 #ifndef MK_HIER_BARRIER
 #define MK_HIER_BARRIER 0
 #endif
-#ifndef MK_LL_STAGE
-#define MK_LL_STAGE 1
-#endif
-#ifndef MK_LL_EPI
-#define MK_LL_EPI 1
-#endif
-#ifndef MK_LL_ATTN
-#define MK_LL_ATTN 1
-#endif
-// (experiments) the numerics mode fixed at compile time: -DMK_FIX_NUM=0 (reference megakernel) or 1 (PyTorch roundings)
-#ifdef MK_FIX_NUM
-#define MK_NUM(p) (MK_FIX_NUM)
-#else
-#define MK_NUM(p) ((p).numerics)
-#endif
 #ifndef MK_WITH_MOE
 #define MK_WITH_MOE 0
 #endif
@@ -714,9 +699,9 @@ __device__ __forceinline__ float row_rms_scale(const float* red, int first, int 
 template <int NV>
 __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* dst, const uint4* pre_w, int K, int nvec,
                                                int v0, int vstep, bool active, bool valid, int red_first, int wpr,
-                                               bool gather, int tok) {
+                                               bool gather, int tok, uint4* sum_row) {
   const int kvec = K >> 3;
-  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
   float* red = c.red();
   uint4 raw[NV];
 #pragma unroll
@@ -725,10 +710,61 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
     raw[i] = (valid && v < kvec && !gather) ? __ldcg(src + v) : make_uint4(0, 0, 0, 0);
   }
   if (gather) {  // (kept apart from the plain loads above: a call between them would serialise them)
+#if MK_WITH_XCHG
+    if constexpr (NV == 2) {
+      // both vectors of a rank in flight together, the ranks one after the other: `world` round trips, not 2 x world
+      const KParams& p = c.p;
+      const unsigned seq = xchg_cur(c);
+      float acc[2][8];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int v = v0 + vstep * i;
-      if (valid && v < kvec) raw[i] = xchg_gather8(c, xchg_cur(c), tok, v * 8);
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+#pragma unroll 1
+      for (int r = 0; r < p.world; ++r) {
+        uint4 q[2][4];
+        const uint4* src4[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int v = min(v0 + vstep * i, kvec - 1);
+          src4[i] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(p.xchg[p.rank]) +
+                                                   xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, r, tok, v * 8));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) q[i][k] = (valid && v0 + vstep * i < kvec) ? ld_sys_v4(src4[i] + k) : make_uint4(0u, seq, 0u, seq);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (!(valid && v0 + vstep * i < kvec)) continue;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (!xchg_arrived(q[i][k].y, seq) || !xchg_arrived(q[i][k].w, seq)) {
+              const uint2* w2 = reinterpret_cast<const uint2*>(src4[i] + k);
+              if (xchg_wait_word(c, w2, seq, r) && xchg_wait_word(c, w2 + 1, seq, r)) q[i][k] = ld_sys_v4(src4[i] + k);
+            }
+            acc[i][2 * k] += __uint_as_float(q[i][k].x);
+            acc[i][2 * k + 1] += __uint_as_float(q[i][k].z);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int v = v0 + vstep * i;
+        if (valid && v < kvec) {
+          raw[i] = pack8(acc[i]);
+          if (sum_row != nullptr) sum_row[v] = raw[i];  // the reduced row, for a later reader of the tensor itself (a residual)
+        }
+      }
+    } else
+#endif
+    {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = v0 + vstep * i;
+        if (valid && v < kvec) {
+          raw[i] = xchg_gather8(c, xchg_cur(c), tok, v * 8);
+          if (sum_row != nullptr) sum_row[v] = raw[i];
+        }
+      }
     }
   }
   float ss = 0.f;
@@ -751,12 +787,12 @@ __device__ __forceinline__ void stage_row_regs(Ctx& c, const uint4* src, uint4* 
 
 // `gather`: the rows are not read from `in` but summed over the ranks' slots of the latest exchange.
 __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, int kp, const void* norm_w, int tok0,
-                                     int rows, int T, const uint4* pre_w, bool gather = false) {
+                                     int rows, int T, const uint4* pre_w, bool gather = false, void* sums_out = nullptr) {
   if (!MK_WITH_XCHG) gather = false;  // (compiled out of the single-GPU build)
   uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
   const int nvec = kp >> 3, kvec = K >> 3;
-  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
   const uint4* wv = reinterpret_cast<const uint4*>(norm_w);
   const int wpr = stage_warps_per_row(rows);
   const int tb = c.warp / wpr, part = c.warp % wpr;
@@ -769,8 +805,10 @@ __device__ __noinline__ void stage_x(Ctx& c, const void* in, int ld_in, int K, i
   if (c.tid == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);  // the chunk absent tokens point at
   if (active && part == 0 && c.lane == 0) dst[nvec] = make_uint4(0, 0, 0, 0);  // the row's padding vector
   if (wv != nullptr && pre_w != nullptr && nvec <= 4 * vstep) {
-    if (nvec <= 2 * vstep) stage_row_regs<2>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb);
-    else stage_row_regs<4>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb);
+    uint4* sum_row = (gather && sums_out != nullptr && valid) ? reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(sums_out) + (size_t)(tok0 + tb) * ld_in)
+                                                              : nullptr;
+    if (nvec <= 2 * vstep) stage_row_regs<2>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb, sum_row);
+    else stage_row_regs<4>(c, src, dst, pre_w, K, nvec, v0, vstep, active, valid, tb * wpr, wpr, gather, tok0 + tb, sum_row);
     return;
   }
   float ss = 0.f;
@@ -859,7 +897,7 @@ __device__ __forceinline__ void stage_ll_regs(Ctx& c, const uint4* ll, uint4* ds
                                               int nvec, int v0, int vstep, bool active, bool valid, int red_first, int wpr,
                                               unsigned tag) {
   const int kvec = K >> 3;
-  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
   float* red = c.red();
   uint4 qa[NV], qb[NV], raw[NV];
 #pragma unroll
@@ -1033,7 +1071,8 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
   // 16-byte store), four such units per round with their loads issued together: one dependent 2-byte load
   // per element made the block's finisher the slowest CTA of the op by far (at 64 tokens: 32 round trips).
   // Lanes of a warp take different tokens, so the sums block is read without bank conflicts.
-  const bool vec = !push && !MK_XF(op, F_GATHER_RES) && ntok > 2 && (op.ld_out & 7) == 0 && (!with_res || (op.ld_res & 7) == 0) &&
+  // (a pushing linear stores the eight sums of a unit as four 16-byte stores {value, number, value, number} per rank)
+  const bool vec = !MK_XF(op, F_GATHER_RES) && ntok > 2 && (push || (op.ld_out & 7) == 0) && (!with_res || (op.ld_res & 7) == 0) &&
                    ((blk + 1) * kTileRows <= op.n);
   if (vec) {
     const int nunits = (kTileRows / 8) * ntok;
@@ -1057,9 +1096,22 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             v[i] = red[(cg * 8 + i) * kRedStride + tb];
-            if (MK_NUM(p) == NUM_TORCH) v[i] = rbf(v[i]);
+            if (p.numerics == NUM_TORCH && !push) v[i] = rbf(v[i]);  // (pushed sums stay fp32: rounded once, after the ranks are added up)
             v[i] += r[i];
           }
+#if MK_WITH_XCHG
+          if (push) {
+            const unsigned seq = xchg_next(c);
+            const size_t w = xchg_word(seq, p.world, p.xchg_tokens, p.xchg_cols, p.rank, tok0 + tb, blk * kTileRows + cg * 8);
+#pragma unroll 1
+            for (int rk = 0; rk < p.world; ++rk) {
+              uint4* dstw = reinterpret_cast<uint4*>(reinterpret_cast<uint2*>(p.xchg[rk]) + w);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) st_sys_v4(dstw + i, __float_as_uint(v[2 * i]), seq, __float_as_uint(v[2 * i + 1]), seq);
+            }
+            continue;
+          }
+#endif
           *reinterpret_cast<uint4*>(out + (size_t)(tok0 + tb) * op.ld_out + blk * kTileRows + cg * 8) = pack8(v);
         }
       }
@@ -1071,7 +1123,7 @@ __device__ void linear_epilogue(Ctx& c, const OpDesc& op, int blk, int tok0, int
     const int tok = tok0 + tb, col = blk * kTileRows + row;
     if (col < op.n) {
       float v = red[row * kRedStride + tb];
-      if (MK_NUM(p) == NUM_TORCH && !push) v = rbf(v);  // (pushed partial sums stay fp32: they are rounded once, after the ranks are added up)
+      if (p.numerics == NUM_TORCH && !push) v = rbf(v);  // (pushed partial sums stay fp32: they are rounded once, after the ranks are added up)
       if (with_res) {
         float r;
         if (e < kNumConsumers) r = res0;
@@ -1607,7 +1659,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
   const int kp = nks * kRowsStageK;
   const int ntok = min(op.aux3, T - tok0);
   MK_STAMP(c, 0);
-  if (MK_LL_STAGE && (op.flags & F_LL_IN)) {
+  if (op.flags & F_LL_IN) {
     if (op.flags & F_NORM_IN) stage_x_ll(c, op.ll_in, op.ld_in, op.k, kp, op.norm_w, tok0, ntok, T, pre_w, ll_tag_of(c, op.ll_in_op));
     else stage_rows_ll(c, op.ll_in, op.ld_in, op.k, kp, tok0, ntok, T, ll_tag_of(c, op.ll_in_op));
   } else if (nks <= 24 && ntok <= 2 && !(op.flags & F_NORM_IN) && !MK_XF(op, F_GATHER_IN)) stage_x_rows(c, op.in, op.ld_in, op.k, kp, tok0, ntok, T);
@@ -1658,7 +1710,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
     float res0 = 0.f;
     const bool e_live = e_row < R && e_tok < ntok && r0 + e_row < op.n;
     if (with_res && e_live) {
-      if (MK_LL_STAGE && (op.flags & F_LL_RES)) res0 = ll_gather1(c, ll_row(op.ll_res, op.ld_res, tok0 + e_tok), r0 + e_row, ll_tag_of(c, op.ll_res_op));
+      if (op.flags & F_LL_RES) res0 = ll_gather1(c, ll_row(op.ll_res, op.ld_res, tok0 + e_tok), r0 + e_row, ll_tag_of(c, op.ll_res_op));
       else res0 = MK_XF(op, F_GATHER_RES) ? xchg_gather1(c, xchg_cur(c), tok0 + e_tok, r0 + e_row)
                                             : __bfloat162float(__ldcg(res + (size_t)(tok0 + e_tok) * op.ld_res + r0 + e_row));
     }
@@ -1732,7 +1784,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
         y = __float2bfloat16_rn(sv * u);
         out[(size_t)(tok0 + e_tok) * op.ld_out + col] = y;
       }
-      if (MK_LL_EPI && (op.flags & F_LL_OUT)) {  // the pair (col, col + 1) sits in two neighbouring lanes
+      if (op.flags & F_LL_OUT) {  // the pair (col, col + 1) sits in two neighbouring lanes
         const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
         const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
         if (mine && !(e_row & 1))
@@ -1744,11 +1796,11 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
       if (e_live) {
 #pragma unroll
         for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + e_tok];
-        if (with_res) v = (MK_NUM(p) == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
+        if (with_res) v = (p.numerics == NUM_TORCH && !MK_XF(op, F_PUSH)) ? rbf(v) + res0 : v + res0;
         if (MK_XF(op, F_PUSH)) xchg_push1(p, xchg_next(c), tok0 + e_tok, r0 + e_row, v);
         else out[(size_t)(tok0 + e_tok) * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
       }
-      if (MK_LL_EPI && (op.flags & F_LL_OUT)) {  // rows come in units of 8: the pair (row, row + 1) sits in two neighbouring lanes
+      if (op.flags & F_LL_OUT) {  // rows come in units of 8: the pair (row, row + 1) sits in two neighbouring lanes
         const uint32_t lo = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
         const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
         if (e_live && !(e_row & 1))
@@ -2036,7 +2088,7 @@ __device__ __noinline__ void attn_merge(Ctx& c, const float* base, __nv_bfloat16
     const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls)), y2 = __float2bfloat16_rn(__fdividef(O2, Ls2));
     out[e] = y;
     if (two) out[e2] = y2;
-    if (MK_LL_ATTN && ll_out != nullptr) {  // (whole warps take the same trips: nout is a multiple of 128)
+    if (ll_out != nullptr) {  // (whole warps take the same trips: nout is a multiple of 128)
       const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y), lo2 = (uint32_t)__bfloat16_as_ushort(y2);
       const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1), hi2 = __shfl_down_sync(0xffffffffu, lo2, 1);
       if (!(e & 1)) {
@@ -2338,7 +2390,7 @@ __device__ __noinline__ bool attn_barrier_then_append(Ctx& c, const OpDesc& op, 
     const uint4 vnew = __ldcg(reinterpret_cast<const uint4*>(row + (pl.qpk + 1) * kHeadDim) + l16);
     F8 kf;
     unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-    kf = head_norm_rope(kf, wk, cs, sn, l16, op.flags, MK_NUM(p), dbl_k);
+    kf = head_norm_rope(kf, wk, cs, sn, l16, op.flags, p.numerics, dbl_k);
     const int pg = __ldcg(p.kv_indices + lens[kAttnLensMax + t] + ((L - 1) >> p.page_shift));
     if (c.lane < 16) {
       const size_t dst = ((((size_t)pg << p.page_shift) + ((L - 1) & (p.page_size - 1))) * pl.HKV + h) * kHeadDim;
@@ -2408,13 +2460,13 @@ __device__ __noinline__ void attention_groups(Ctx& c, const OpDesc& op, const At
     for (int h = lw; h < hq; h += wpg) {  // this warp's share of the q heads
       F8 q;
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + h * kHeadDim) + l16), q.v);
-      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, MK_NUM(p), dbl_q);
+      q = head_norm_rope(q, a.wq, a.cs, a.sn, l16, op.flags, p.numerics, dbl_q);
       if (c.lane < 16) sm_q[h * 16 + l16] = pack8(q.v);
     }
     if (lw == wpg - 1) {  // the group's last warp also prepares the new k
       F8 kf;
       unpack8(__ldcg(reinterpret_cast<const uint4*>(row + pl.qpk * kHeadDim) + l16), kf.v);
-      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, MK_NUM(p), dbl_k);
+      kf = head_norm_rope(kf, a.wk, a.cs, a.sn, l16, op.flags, p.numerics, dbl_k);
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
@@ -2766,7 +2818,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
         if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
         c.dead = c.flags()[3] != 0;
         if (c.dead) return;
-      } else if (MK_LL_ATTN && (op.flags & F_LL_IN)) {
+      } else if (op.flags & F_LL_IN) {
         // (no look at the abort flag: the polls of the tagged input watch it)
         consumer_sync();
         if (c.pr != nullptr && c.tid == 0) c.pr[1] = globaltimer();
@@ -2780,7 +2832,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)a.t * op.ld_in +
                                (size_t)a.h * (pl.qpk + 2) * kHeadDim;
     // tagged input: the task polls the words of its own kv-head group only (a prompt chunk has had its barrier)
-    const bool ll_in = MK_LL_ATTN && (op.flags & F_LL_IN) && !chunked;
+    const bool ll_in = (op.flags & F_LL_IN) && !chunked;
     const uint2* llr = ll_row(op.ll_in, op.ld_in, a.t) + ((a.h * (pl.qpk + 2) * kHeadDim) >> 1);
     const unsigned tag_in = ll_tag_of(c, op.ll_in_op);
     const bool do_q = c.warp < pl.qpk, do_k = c.warp == kw;
@@ -2819,13 +2871,13 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     if (do_q) {
       F8 q;
       unpack8(xq, q.v);
-      q = head_norm_rope(q, nw, ncs, nsn, l16, op.flags, MK_NUM(p), dbl_q);
+      q = head_norm_rope(q, nw, ncs, nsn, l16, op.flags, p.numerics, dbl_q);
       if (c.lane < 16) sm_q[c.warp * 16 + l16] = pack8(q.v);  // exact: the values are bf16 already
     }
     if (do_k) {
       F8 kf;
       unpack8(xk, kf.v);
-      kf = head_norm_rope(kf, do_q ? __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16) : nw, ncs, nsn, l16, op.flags, MK_NUM(p), dbl_k);
+      kf = head_norm_rope(kf, do_q ? __ldg(reinterpret_cast<const uint4*>(op.k_norm_w) + l16) : nw, ncs, nsn, l16, op.flags, p.numerics, dbl_k);
       const uint4 kn = pack8(kf.v);
       if (c.lane < 16) {
         sm_k[l16] = kn;
@@ -2870,11 +2922,11 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
     consumer_sync();
     float* part = p.attn_part + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     // tagged partials (see attn_merge_ll) when the op's output is tagged and the host gave them room
-    const bool ll_part = MK_LL_ATTN && (op.flags & F_LL_OUT) && p.attn_part_ll != nullptr;
+    const bool ll_part = (op.flags & F_LL_OUT) && p.attn_part_ll != nullptr;
     uint2* partw = p.attn_part_ll + (((size_t)a.t * pl.HKV + a.h) * p.attn_max_chunks + a.ch) * part_stride;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out) + (size_t)a.t * op.ld_out +
                          (size_t)a.h * pl.qpk * kHeadDim;
-    uint2* ll_out = (MK_LL_ATTN && (op.flags & F_LL_OUT)) ? reinterpret_cast<uint2*>(op.ll_out) + (size_t)a.t * (size_t)(op.ld_out >> 1) +
+    uint2* ll_out = (op.flags & F_LL_OUT) ? reinterpret_cast<uint2*>(op.ll_out) + (size_t)a.t * (size_t)(op.ld_out >> 1) +
                                                 ((a.h * pl.qpk * kHeadDim) >> 1)
                                           : nullptr;
 #pragma unroll 1
@@ -2895,7 +2947,7 @@ __device__ __noinline__ void op_attention(Ctx& c, const OpDesc& op, int T) {
       if (a.nch == 1) {
         const __nv_bfloat16 y = __float2bfloat16_rn(__fdividef(O, Ls));
         out[e] = y;
-        if (MK_LL_ATTN && (op.flags & F_LL_OUT)) {  // (whole warps run this loop: its bound is a multiple of 128)
+        if (op.flags & F_LL_OUT) {  // (whole warps run this loop: its bound is a multiple of 128)
           const uint32_t lo = (uint32_t)__bfloat16_as_ushort(y);
           const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
           if (!(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), ll_tag_of(c, c.cur_op));
@@ -2978,7 +3030,9 @@ __device__ void op_rmsnorm(Ctx& c, const OpDesc& op, int T) {
   }
   if (op_barrier(c, op)) return;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
-    if (MK_XF(op, F_GATHER_IN)) stage_x(c, nullptr, 0, op.n, kp, op.w, tok, 1, tok + 1, pre ? pre_w : nullptr, true);
+    // (the sums are also stored into the gathered tensor's own rows when the host asked for it: aux0)
+    if (MK_XF(op, F_GATHER_IN)) stage_x(c, nullptr, op.ld_in, op.n, kp, op.w, tok, 1, tok + 1, pre ? pre_w : nullptr, true,
+                                         (op.aux0 && pre) ? const_cast<void*>(op.in) : nullptr);
     else stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)tok * op.ld_in, op.ld_in, op.n, kp, op.w, 0, 1, 1,
                  pre ? pre_w : nullptr);
     const uint4* xs = reinterpret_cast<const uint4*>(c.smem + c.p.x_off);
@@ -3315,7 +3369,7 @@ __device__ void op_moe_combine(Ctx& c, const OpDesc& op, int T) {
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
   const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
-  const bool torch_num = MK_NUM(c.p) == NUM_TORCH;
+  const bool torch_num = c.p.numerics == NUM_TORCH;
 #pragma unroll 1
   for (int u = blockIdx.x * kNumConsumers + c.tid; u < T * nvec; u += gridDim.x * kNumConsumers) {
     const int t = u / nvec, v = u % nvec;

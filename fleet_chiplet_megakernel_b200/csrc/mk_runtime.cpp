@@ -361,6 +361,7 @@ int plan_graph(mk_handle* h) {
   // input rows (F_GATHER_IN) or fetch their residual (F_GATHER_RES).  virt maps such a tensor to the
   // ordinal of its exchange in the iteration; exchanges counts the exchanges planned so far.
   std::map<int, int> virt;
+  std::map<int, int> materialised;  // virtual tensor -> exchange whose sums a stand-alone norm has stored into the tensor itself
   int exchanges = 0;
   int moe_topk = 0;  // experts per token of the latest routing layer
   // Can the output `tid` of the allreduce layer at position i stay virtual?  Every reader up to the
@@ -436,6 +437,15 @@ int plan_graph(mk_handle* h) {
         if (virt[po.in] != exchanges) return h->fail(MK_E_STATE, "internal: rmsnorm reads a stale exchange");
         po.flags |= mk::F_GATHER_IN;
         po.note = "input gathered from the ranks";
+        // The stand-alone norm also stores the sums it gathers into the tensor's own rows (one CTA per row), so
+        // that a later residual reads them with plain 16-byte loads behind the barriers in between, instead of
+        // adding the ranks' words up again element by element.  (Rows of at most 8192 columns: the kernel's
+        // register path.)
+        if (po.n <= 8192 && h->tensors[po.in].owned) {
+          po.aux0 = 1;
+          materialised[po.in] = exchanges;
+          po.note += ", sums stored";
+        }
       }
     } else if (is_linear(nm)) {
       const bool rl = nm == "rmsnorm_linear";
@@ -545,8 +555,12 @@ int plan_graph(mk_handle* h) {
       }
       if (po.res >= 0 && virt.count(po.res)) {
         if (virt[po.res] != exchanges) return h->fail(MK_E_STATE, "internal: a residual reads a stale exchange");
-        po.flags |= mk::F_GATHER_RES;
-        po.note += po.note.empty() ? "residual gathered from the ranks" : ", residual gathered from the ranks";
+        if (materialised.count(po.res) && materialised[po.res] == exchanges) {
+          po.note += po.note.empty() ? "residual: the sums a norm stored" : ", residual: the sums a norm stored";
+        } else {
+          po.flags |= mk::F_GATHER_RES;
+          po.note += po.note.empty() ? "residual gathered from the ranks" : ", residual gathered from the ranks";
+        }
       }
       // SiLU*up fused into the epilogue of a gate/up linear
       if (fuse && !with_res && !(po.flags & mk::F_SILU_MUL) && i + 1 < nops && h->nops[i + 1].name == "silu_mul" && h->nops[i + 1].t.size() == 2 &&
