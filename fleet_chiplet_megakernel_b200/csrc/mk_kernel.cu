@@ -2126,60 +2126,64 @@ __device__ __noinline__ void attn_merge_ll(Ctx& c, const uint2* base, __nv_bfloa
                                            int part_stride, unsigned tag) {
   const int nout = qpk * kHeadDim;
   const int S = (((nout + nch - 1) / nch) + 1) & ~1;  // outputs per chunk CTA, even: a bf16 pair never straddles two slices
-  const int e = ch * S + c.tid;
-  const bool act = c.tid < S && e < nout;
-  float y = 0.f;
-  if (act) {
-    constexpr int kBatch = 8;
-    const uint2* pv = base + e;
-    const uint2* pm = base + nout + (e >> 7);
-    float M = -INFINITY, Ls = 0.f, O = 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < nch; c0 += kBatch) {
-      uint2 qv[kBatch], qm[kBatch], ql[kBatch];
+  for (int el0 = 0; el0 < S; el0 += kNumConsumers) {  // (one round for up to four q heads per kv head)
+    const int el = el0 + c.tid;
+    const int e = ch * S + el;
+    const bool act = el < S && e < nout;
+    float y = 0.f;
+    if (act) {
+      constexpr int kBatch = 8;
+      const uint2* pv = base + e;
+      const uint2* pm = base + nout + (e >> 7);
+      float M = -INFINITY, Ls = 0.f, O = 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < nch; c0 += kBatch) {
+        uint2 qv[kBatch], qm[kBatch], ql[kBatch];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const bool ok = c0 + u < nch;
-        const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
-        qv[u] = ld_gpu_v2(pv + off);
-        qm[u] = ld_gpu_v2(pm + off);
-        ql[u] = ld_gpu_v2(pm + off + qpk);
-      }
-      float v[kBatch], mm[kBatch], ll[kBatch];
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const bool ok = c0 + u < nch;
-        const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
-        v[u] = qv[u].y == tag ? __uint_as_float(qv[u].x) : ll_wait_word(c, pv + off, tag);
-        mm[u] = qm[u].y == tag ? __uint_as_float(qm[u].x) : ll_wait_word(c, pm + off, tag);
-        ll[u] = ql[u].y == tag ? __uint_as_float(ql[u].x) : ll_wait_word(c, pm + off + qpk, tag);
-        if (!ok) {
-          v[u] = 0.f;
-          mm[u] = -INFINITY;
-          ll[u] = 0.f;
+        for (int u = 0; u < kBatch; ++u) {
+          const bool ok = c0 + u < nch;
+          const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
+          qv[u] = ld_gpu_v2(pv + off);
+          qm[u] = ld_gpu_v2(pm + off);
+          ql[u] = ld_gpu_v2(pm + off + qpk);
         }
-      }
-      float Mb = M;
+        float v[kBatch], mm[kBatch], ll[kBatch];
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) Mb = fmaxf(Mb, mm[u]);
-      const float r = exp2f(M - Mb);  // 0 for the first batch (every chunk holds at least one position)
-      O *= r;
-      Ls *= r;
+        for (int u = 0; u < kBatch; ++u) {
+          const bool ok = c0 + u < nch;
+          const size_t off = (size_t)(ok ? c0 + u : c0) * part_stride;
+          v[u] = qv[u].y == tag ? __uint_as_float(qv[u].x) : ll_wait_word(c, pv + off, tag);
+          mm[u] = qm[u].y == tag ? __uint_as_float(qm[u].x) : ll_wait_word(c, pm + off, tag);
+          ll[u] = ql[u].y == tag ? __uint_as_float(ql[u].x) : ll_wait_word(c, pm + off + qpk, tag);
+          if (!ok) {
+            v[u] = 0.f;
+            mm[u] = -INFINITY;
+            ll[u] = 0.f;
+          }
+        }
+        float Mb = M;
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const float f = exp2f(mm[u] - Mb);
-        O = fmaf(f, v[u], O);
-        Ls = fmaf(f, ll[u], Ls);
+        for (int u = 0; u < kBatch; ++u) Mb = fmaxf(Mb, mm[u]);
+        const float r = exp2f(M - Mb);  // 0 for the first batch (every chunk holds at least one position)
+        O *= r;
+        Ls *= r;
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const float f = exp2f(mm[u] - Mb);
+          O = fmaf(f, v[u], O);
+          Ls = fmaf(f, ll[u], Ls);
+        }
+        M = Mb;
       }
-      M = Mb;
+      y = __fdividef(O, Ls);
     }
-    y = __fdividef(O, Ls);
+    const __nv_bfloat16 yb = __float2bfloat16_rn(y);
+    if (act) out[e] = yb;
+    const uint32_t lo = (uint32_t)__bfloat16_as_ushort(yb);
+    const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
+    if (act && ll_out != nullptr && !(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
   }
-  const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-  if (act) out[e] = yb;
-  const uint32_t lo = (uint32_t)__bfloat16_as_ushort(yb);
-  const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 1);
-  if (act && ll_out != nullptr && !(e & 1)) st_gpu_v2(ll_out + (e >> 1), lo | (hi << 16), tag);
 }
 
 // The half-warp's pass over its positions of the task: for up to four q heads of the kv-head

@@ -46,12 +46,14 @@ def _free_run(geom, w, prompts, n_new, numerics="torch", fuse=True, page_size=16
     return out, timing
 
 
-def _teacher_forced(geom, w, prompt, ref_tokens, n_new, numerics="torch", fuse=True, page_size=16, num_layers=None):
+def _teacher_forced(geom, w, prompt, ref_tokens, n_new, numerics="torch", fuse=True, page_size=16, num_layers=None,
+                    debug_flags=0):
     """One launch per iteration; after each, the reference's token replaces ours.
     Returns our per-step logits [n_new, vocab] and our greedy tokens."""
     P = len(prompt)
     dec = mk.Qwen3Decoder(_geom(geom), _cuda(w), max_seq_length=P + n_new + 1, max_requests=1, page_size=page_size,
-                          numerics=numerics, fuse=fuse, keep_logits=True, max_iterations=1, num_layers=num_layers)
+                          numerics=numerics, fuse=fuse, keep_logits=True, max_iterations=1, num_layers=num_layers,
+                          debug_flags=debug_flags)
     dec.set_prompts([prompt])
     logits, toks = [], []
     for it in range(P + n_new - 1):
@@ -431,6 +433,27 @@ def test_chunked_prefill_prompt_lengths_against_oracle(P):
     assert launches == -(-P // 64) + n_new - 1
     err, firm = _check_against(logits, toks, ref_logits, torch.tensor(ref_tokens), P, f"prompt of {P} tokens")
     print(f"prompt {P}: max logit error {err:.4g}, {firm}/{n_new} firm steps")
+
+
+@pytest.mark.parametrize("n_q,n_kv", [(8, 1), (16, 2), (4, 1)])
+def test_tagged_activations_give_the_bits_the_barriers_give(n_q, n_kv):
+    """Batch 1 with a context long enough for several chunks per kv head, four and eight q heads per kv head (the
+    latter is the Qwen3-30B-A3B attention shape: the chunk CTAs merge slices of 1024 output elements between
+    them).  Tagged activations change how an op learns that its input is there, not what it computes: the logits
+    must be bit-identical to a run in which every op keeps its grid barrier.  16/2 heads also against the host
+    oracle (the 2e-2 floor of this comparison is 0.017-0.024 on these seeds whichever way the ops synchronise)."""
+    geom = O.Geometry(hidden=1024, n_q=n_q, n_kv=n_kv, mlp=2048, layers=2, vocab=2048)
+    w = O.make_weights(geom, 6)
+    P, n_new = 70, 8
+    prompt = O.make_prompt(geom, P, 6)
+    ref = O.TorchRefModel(geom, w, P + n_new + 2)
+    ref_tokens, ref_logits = ref.generate(prompt, n_new)
+    tagged, toks = _teacher_forced(geom, w, prompt, torch.tensor(ref_tokens), n_new, page_size=16)
+    barriers, _ = _teacher_forced(geom, w, prompt, torch.tensor(ref_tokens), n_new, page_size=16, debug_flags=16)
+    assert torch.equal(tagged, barriers)
+    if (n_q, n_kv) == (16, 2):
+        err, firm = _check_against(tagged, toks, ref_logits, torch.tensor(ref_tokens), P, f"{n_q} q heads on {n_kv} kv heads")
+        print(f"{n_q}/{n_kv} heads: max logit error {err:.4g}, {firm}/{n_new} firm steps")
 
 
 def test_chunked_prefill_with_more_requests_than_slots():
