@@ -118,8 +118,13 @@ class PersistentKernel:
         self._h = None
         if mode not in valid_persistent_kernel_modes:
             raise ValueError(f"Invalid persistent kernel mode: {mode}")
-        if mode in ("online", "online_multi_turn"):
-            raise NotImplementedError(f"mode '{mode}' is not built; use 'offline' or 'online_notoken'")
+        if mode == "online":
+            # the reference's single-request loop that advances `step` by new_token_nums[0] and never touches the
+            # paging metadata (persistent_kernel.cuh:538-567): superseded there by offline / online_notoken
+            raise NotImplementedError("mode 'online' is not built; use 'offline' or 'online_notoken'")
+        # 'online_multi_turn' is one pass per call over the caller's metadata, like 'online_notoken': the reference's
+        # runtime reads its MODE_MULTI_TURN switch only beside MODE_ONLINE_NOTOKEN (runtime_header.h:43) and gives it
+        # no batching code of its own
         if spec_decode_config is not None:
             raise NotImplementedError("speculative decoding is outside the greedy decode path")
         self.mode = mode

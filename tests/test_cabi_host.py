@@ -104,6 +104,12 @@ def test_lowering_without_fusion_keeps_every_layer(native_lib):
 def test_error_behaviour_follows_the_reference_api(native_lib):
     with pytest.raises(ValueError, match="Invalid persistent kernel mode"):
         _kernel(mode="bogus")
+    with pytest.raises(NotImplementedError, match="'online' is not built"):
+        _kernel(mode="online")
+    for one_pass in ("online_notoken", "onepass", "online_multi_turn"):  # one pass per call over the caller's metadata
+        k = _kernel(mode=one_pass)
+        assert k.mode == one_pass
+        k.finalize()
     k = _kernel()
     with pytest.raises(RuntimeError, match="Invalid io_category"):
         k.new_tensor(dims=(2, 8), name="t", io_category="host_tensor")
