@@ -183,7 +183,7 @@ class Qwen3Decoder:
                  max_iterations: int = 0, num_layers=None, timeout_ms: int = 0, trace: bool = False,
                  trace_op: int = -1, debug_flags: int = 0, world_size: int = 1, rank: int = 0, cluster_size: int = 0,
                  test_barrier_epoch: int = 0, max_num_batched_tokens: int | None = None,
-                 max_tokens_per_request: int = 0):
+                 max_tokens_per_request: int = 0, prefetch_kb: int = 0, max_stages: int = 0):
         """``weights`` are this rank's shard (see ``shard_qwen3_weights``) when world_size > 1.
         ``max_num_batched_tokens`` (default: max_requests, one token per request and iteration) is the
         token budget of an iteration: above max_requests, a request that is still inside its prompt is fed
@@ -225,7 +225,8 @@ class Qwen3Decoder:
             profiler_tensor=self.profiler, trace_name="", spec_decode_config=None, use_cutlass_kernel=True,
             eos_token_id=eos_token_id, numerics=numerics, fuse=fuse, max_iterations=max_iterations,
             timeout_ms=timeout_ms, trace_op=trace_op, debug_flags=debug_flags, cluster_size=cluster_size,
-            test_barrier_epoch=test_barrier_epoch, max_tokens_per_request=max_tokens_per_request)
+            test_barrier_epoch=test_barrier_epoch, max_tokens_per_request=max_tokens_per_request,
+            prefetch_kb=prefetch_kb, max_stages=max_stages)
         build_qwen3_graph(self.mpk, geom, weights, self.k_cache, self.v_cache, self.cos, self.sin,
                           self.input_tokens, self.output_tokens, logits=self.logits, num_layers=num_layers)
         self.mpk.compile()

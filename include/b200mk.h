@@ -60,7 +60,7 @@ typedef struct mk_config {
   int32_t trace_op;                 /* device op whose inner phases are stamped into the profiler buffer (stored +1: 0 = none) */
   int32_t debug_flags;              /* bit 0: linear tasks skip the arithmetic (weight-stream timing only); bit 1: attention tasks keep their barrier and do nothing else.  RESULTS ARE WRONG with either bit.  bit 4: no tagged activations: every op of the row-owner path keeps its grid barrier (results unchanged) */
   int32_t max_stages;               /* cap on the weight ring depth, 0 = default */
-  int32_t prefetch_kb;              /* KB of weights per CTA requested into L2 ahead of the shared-memory ring; 0 = default (512 for one or two batched tokens, off otherwise), < 0 = off */
+  int32_t prefetch_kb;              /* KB of weights per CTA requested into L2 ahead of the shared-memory ring; 0 = default (512 for a row-owner program that keeps its grid barriers, off otherwise), < 0 = off */
   int32_t cluster_size;             /* CTAs per thread-block cluster of the launch: 0 = default, 1 = flat grid barrier, 2 or 4 = hierarchical (cluster-first) grid barrier */
   uint32_t test_barrier_epoch;      /* tests only: barrier epoch every launch starts at (e.g. just below the 32-bit wrap of the counter) */
   int32_t reserved[2];
