@@ -41,7 +41,7 @@ PAGE = 64
 # DRAM read+write bytes per step over the algorithmic bytes, from an ncu capture of a 4-layer case of
 # the same kernel at batch 1 (dram__bytes_read.sum + dram__bytes_write.sum of one launch, divided by
 # the launch's iterations); traffic grows in proportion to the bytes a step streams.
-DRAM_TRAFFIC_RATIO = 1.045
+DRAM_TRAFFIC_RATIO = 1.004
 
 
 def geometry(layers):
