@@ -3187,59 +3187,63 @@ __device__ void op_argmax_reduce(Ctx& c, const OpDesc& op, int T) {
 // routing tables [T, top-k] (fp32 weight, expert id).  One warp per token: fp32 softmax over the experts,
 // k rounds of (largest probability, lowest index), weights renormalised over the k picked
 // (transformers' Qwen3MoeTopKRouter with norm_topk_prob; reference task: topk_softmax_sm100.cuh:61-290).
+// One token, by one warp: `w_out` / `idx_out` (may be null) receive the k weights and expert ids.
+__device__ __noinline__ void moe_route_token(Ctx& c, const __nv_bfloat16* logits, int E, int K, float* w_out, int* idx_out, int* idx_out2) {
+  float v[8];  // up to 256 experts: 8 per lane
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int e = c.lane + 32 * i;
+    v[i] = e < E ? __bfloat162float(__ldcg(logits + e)) : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[i] = (c.lane + 32 * i) < E ? expf(v[i] - mx) : 0.f;
+    sum += v[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / sum;
+  float picked_sum = 0.f, my_w = 0.f;
+  int my_e = 0;
+#pragma unroll 1
+  for (int k = 0; k < K; ++k) {
+    ArgBest b;
+    b.v = -INFINITY;
+    b.i = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ArgBest x;
+      x.v = v[i] * inv;
+      x.i = c.lane + 32 * i;
+      if (x.i < E && v[i] >= 0.f) b = arg_better(b, x);
+    }
+    b = warp_argmax(b);
+    picked_sum += b.v;
+    if (c.lane == k) {
+      my_w = b.v;
+      my_e = b.i;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c.lane + 32 * i == b.i) v[i] = -1.f;  // taken
+  }
+  if (c.lane < K) {
+    if (w_out != nullptr) w_out[c.lane] = my_w / picked_sum;
+    if (idx_out != nullptr) idx_out[c.lane] = my_e;
+    if (idx_out2 != nullptr) idx_out2[c.lane] = my_e;
+  }
+}
 __device__ __noinline__ void op_moe_route(Ctx& c, const OpDesc& op, int T) {
   const int E = op.aux1, K = op.aux0;
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.in);
 #pragma unroll 1
-  for (int t = blockIdx.x * kNumConsumerWarps + c.warp; t < T; t += gridDim.x * kNumConsumerWarps) {
-    float v[8];  // up to 256 experts: 8 per lane
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = c.lane + 32 * i;
-      v[i] = e < E ? __bfloat162float(__ldcg(in + (size_t)t * op.ld_in + e)) : -INFINITY;
-      mx = fmaxf(mx, v[i]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[i] = (c.lane + 32 * i) < E ? expf(v[i] - mx) : 0.f;
-      sum += v[i];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.0f / sum;
-    float picked_sum = 0.f, my_w = 0.f;
-    int my_e = 0;
-#pragma unroll 1
-    for (int k = 0; k < K; ++k) {
-      ArgBest b;
-      b.v = -INFINITY;
-      b.i = 0x7fffffff;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        ArgBest x;
-        x.v = v[i] * inv;
-        x.i = c.lane + 32 * i;
-        if (x.i < E && v[i] >= 0.f) b = arg_better(b, x);
-      }
-      b = warp_argmax(b);
-      picked_sum += b.v;
-      if (c.lane == k) {
-        my_w = b.v;
-        my_e = b.i;
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (c.lane + 32 * i == b.i) v[i] = -1.f;  // taken
-    }
-    if (c.lane < K) {
-      op.amax_val[(size_t)t * K + c.lane] = my_w / picked_sum;
-      op.amax_idx[(size_t)t * K + c.lane] = my_e;
-    }
-  }
+  for (int t = blockIdx.x * kNumConsumerWarps + c.warp; t < T; t += gridDim.x * kNumConsumerWarps)
+    moe_route_token(c, in + (size_t)t * op.ld_in, E, K, op.amax_val + (size_t)t * K, op.amax_idx + (size_t)t * K, nullptr);
 }
 
 // The CTA's share of the virtual row space of a MoE linear and its walk: pairs x n rows, contiguous ranges
@@ -3266,9 +3270,21 @@ __device__ __forceinline__ MoeWalk moe_walk(const OpDesc& op, int pairs) {
 __device__ __noinline__ void op_moe_linear(Ctx& c, const OpDesc& op, int T) {
   const KParams& p = c.p;
   if (op_barrier(c, op)) return;
+  const int topk = op.aux0;
+  if (op.flags & F_MOE_ROUTE) {
+    // The routing folded into this op: warp t of EVERY CTA routes token t from the router logits (one or two
+    // tokens) and leaves the expert ids in shared memory for this CTA's producer; CTA 0 also stores the
+    // runtime's tables, which the later ops of the layer read behind their barriers.
+    int* rt = reinterpret_cast<int*>(c.smem + p.x_off + p.x_bytes - 512);
+    if (c.warp < T)
+      moe_route_token(c, reinterpret_cast<const __nv_bfloat16*>(op.res) + (size_t)c.warp * op.ld_res, op.aux1, topk,
+                      blockIdx.x == 0 ? op.amax_val + (size_t)c.warp * topk : nullptr,
+                      blockIdx.x == 0 ? op.amax_idx + (size_t)c.warp * topk : nullptr, rt + c.warp * topk);
+    consumer_sync();
+    __threadfence_block();
+  }
   c.lin_seq += 1;
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the routing is visible: the producer may pick this op's expert rows
-  const int topk = op.aux0;
   const int pairs = T * topk;
   const MoeWalk wk = moe_walk(op, pairs);
   if (!wk.any || wk.row0 >= wk.row1) return;
@@ -3280,8 +3296,8 @@ __device__ __noinline__ void op_moe_linear(Ctx& c, const OpDesc& op, int T) {
   const int in_first = pair_in ? p_first : p_first / topk;
   const int in_last = pair_in ? p_last : p_last / topk;
   const int nrows = in_last - in_first + 1;  // at most 8 (the host admits MoE graphs for one or two tokens)
-  stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)in_first * op.ld_in, op.ld_in, op.k, kp, nullptr, 0, nrows,
-          nrows, nullptr);
+  stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)in_first * op.ld_in, op.ld_in, op.k, kp,
+          (op.flags & F_NORM_IN) ? op.norm_w : nullptr, 0, nrows, nrows, nullptr);
   const int S = p.num_stages;
   const int lane = c.lane, warp = c.warp;
   const int pitch_b = (kp + 8) * 2;
@@ -3749,7 +3765,8 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           if (!wk.any || wk.row0 >= wk.row1) continue;
           const int p_first = wk.row0 / wk.n, p_last = (wk.row1 - 1) / wk.n;
           for (int pr = p_first; pr <= p_last && !dead; ++pr) {
-            const int expert = __ldcg(rop.amax_idx + pr);
+            const int expert = (rop.flags & F_MOE_ROUTE) ? reinterpret_cast<volatile int*>(c.smem + p.x_off + p.x_bytes - 512)[pr]
+                                                         : __ldcg(rop.amax_idx + pr);
             const int seg0 = max(wk.row0, pr * wk.n), seg1 = min(wk.row1, (pr + 1) * wk.n);
             const int nch = rows_num_chunks(seg0, seg1);
             for (int ci = 0; ci < nch && !dead; ++ci) {

@@ -353,6 +353,33 @@ int plan_graph(mk_handle* h) {
     }
     return true;
   };
+  // A norm whose output feeds the router linear right behind it AND the gate/up expert linear (the MoE layer):
+  // both stage their input rows themselves, so both can apply the norm while staging.
+  auto next_and_moe_w13_read = [&](int i, int tid) {
+    if (!h->tensors[tid].owned) return false;
+    bool seen_w13 = false;
+    for (int step = 1; step < nops_all; ++step) {
+      const RecOp& o = h->nops[(i + step) % nops_all];
+      const int nout = n_outputs(o);
+      const int nin = (int)o.t.size() - nout;
+      bool reads = false, writes = false, as_input = false;
+      for (int a = 0; a < (int)o.t.size(); ++a) {
+        if (o.t[a] != tid) continue;
+        if (a < nin) reads = true; else writes = true;
+        if (a == 0) as_input = true;
+      }
+      if (reads) {
+        const std::string& on = o.name;  // (nops hold canonical names)
+        const bool w13 = (starts_with(on, "moe_w13_linear") || on == "gang_moe_w13") && as_input;
+        if (step != 1 && !w13) return false;
+        if (w13) seen_w13 = true;
+      }
+      if (writes) return seen_w13;
+    }
+    return seen_w13;
+  };
+  std::map<int, std::pair<int, int>> moe_norm;  // normalised tensor -> (its unnormalised source, the norm weight)
+  int pending_route_logits = -1;                // router logits of a routing layer folded into the expert linear behind it
   int pending_norm_in = -1, pending_norm_w = -1, pending_norm_out = -1;
   const int nops = (int)h->nops.size();
   // Tensor parallelism: an allreduce layer behind a row-parallel linear is folded away.  The linear's
@@ -428,6 +455,14 @@ int plan_graph(mk_handle* h) {
         pending_norm_in = op.t[0];
         pending_norm_w = op.t[1];
         pending_norm_out = op.t[2];
+        continue;
+      }
+      if (fuse_norm && rows_mode && i + 1 < nops && is_linear(h->nops[i + 1].name) && h->nops[i + 1].name != "rmsnorm_linear" &&
+          h->nops[i + 1].t[0] == op.t[2] && next_and_moe_w13_read(i, op.t[2])) {
+        pending_norm_in = op.t[0];
+        pending_norm_w = op.t[1];
+        pending_norm_out = op.t[2];
+        moe_norm[op.t[2]] = std::make_pair(op.t[0], op.t[1]);
         continue;
       }
       po.type = mk::OP_RMSNORM;
@@ -708,12 +743,18 @@ int plan_graph(mk_handle* h) {
       const Tensor &in = h->tensors[op.t[0]], &tw = h->tensors[op.t[1]];
       if (tw.ndim != 2 || tw.dims[1] < 1 || tw.dims[1] > 32 || in.dims[1] > 256 || tw.dims[1] > in.dims[1])
         return h->fail(MK_E_UNSUPPORTED, "moe routing: at most 256 experts and 32 experts per token");
+      moe_topk = (int)tw.dims[1];
+      // routing right in front of the gate/up expert linear: that op routes the tokens itself (no op, no barrier)
+      if (fuse && rows_mode && i + 1 < nops &&
+          (starts_with(h->nops[i + 1].name, "moe_w13_linear") || h->nops[i + 1].name == "gang_moe_w13")) {
+        pending_route_logits = op.t[0];
+        continue;
+      }
       po.type = mk::OP_MOE_ROUTE;
       po.in = op.t[0];
       po.out = op.t[1];
       po.aux0 = (int)tw.dims[1];
       po.aux1 = (int)in.dims[1];
-      moe_topk = po.aux0;
     } else if (starts_with(nm, "moe_w13_linear") || starts_with(nm, "moe_w2_linear") || starts_with(nm, "gang_moe_w")) {
       // (input, weight [experts, n, K], routing_indices, mask, output [T, k, n])
       if (op.t.size() != 5) return h->fail(MK_E_INVALID, "%s takes (input, weight, routing_indices, mask, output)", nm.c_str());
@@ -733,6 +774,18 @@ int plan_graph(mk_handle* h) {
       po.type = mk::OP_MOE_LINEAR;
       po.flags |= mk::F_ROWS | (w2 ? mk::F_MOE_PAIR_IN : 0);
       po.in = op.t[0]; po.w = op.t[1]; po.out = op.t[4];
+      if (!w2 && pending_route_logits >= 0) {
+        po.res = pending_route_logits;
+        po.flags |= mk::F_MOE_ROUTE;
+        po.note += po.note.empty() ? "routing folded in" : ", routing folded in";
+        pending_route_logits = -1;
+      }
+      if (!w2 && moe_norm.count(op.t[0])) {  // the norm in front of the layer is applied while the rows are staged
+        po.in = moe_norm[op.t[0]].first;
+        po.norm_w = moe_norm[op.t[0]].second;
+        po.flags |= mk::F_NORM_IN;
+        po.note += po.note.empty() ? "rmsnorm fused" : ", rmsnorm fused";
+      }
       po.n = (int)N;
       po.k = (int)K;
       po.aux0 = moe_topk;
@@ -1214,6 +1267,7 @@ static int compile_program(mk_handle* h, bool first) {
       if (!rows_mode) x_bytes = std::max(x_bytes, 10 * 256 + 8 * 4 * (mk::kHeadDim + 2) * 4 + 128 + 256);
     }
   }
+  if (has_moe) x_bytes += 512;  // the expert ids of the pairs, for the producer (routing folded into the expert linear)
   x_bytes = (x_bytes + 1023) / 1024 * 1024;
   const int fixed = fixed0 + x_bytes;
   const int s_fast = (kFastSmem - fixed) / stage_bytes, s_max = (kMaxSmem - fixed) / stage_bytes;
@@ -1549,6 +1603,7 @@ static int compile_program(mk_handle* h, bool first) {
       d.ld_out = (int)to.strides[to.ndim - 2];
       d.nkt = (po.k + mk::kRowsStageK - 1) / mk::kRowsStageK;
       d.amax_idx = route_idx;
+      d.amax_val = route_w;
       if (((uintptr_t)w.ptr) & 15) return h->fail(MK_E_INVALID, "weight %s is not 16-byte aligned", w.name.c_str());
       map_of[i] = (int)maps.size();
       for (int rows = mk::kUnitRows; rows <= mk::kChunkRows; rows += mk::kUnitRows) {

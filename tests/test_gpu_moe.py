@@ -44,16 +44,20 @@ def _moe_block(k, T, E, K, H, I, x, router, w13, w2, res, od):
     return gate_out, mid, act, out
 
 
+@pytest.mark.parametrize("fuse", [True, False])
 @pytest.mark.parametrize("T,E,K,H,I", [(1, 16, 4, 512, 256), (2, 128, 8, 2048, 768), (1, 128, 8, 2048, 768), (2, 32, 2, 256, 64)])
-def test_moe_block_matches_oracle(T, E, K, H, I):
+def test_moe_block_matches_oracle(T, E, K, H, I, fuse):
     x = _rand((T, H), 71)
     router = _rand((E, H), 72, 1.0 / H ** 0.5)
     w13, w2, res = _rand((E, 2 * I, H), 73, 0.05), _rand((E, H, I), 74, 0.05), _rand((T, H), 75)
-    k, meta, _ = onepass_kernel(T)
+    k, meta, _ = onepass_kernel(T, fuse=fuse)
     od = torch.zeros(T, H, dtype=BF, device="cuda")
     gate_out, mid, act, out = _moe_block(k, T, E, K, H, I, x, router, w13, w2, res, od)
     kinds = [ln.split()[1] for ln in k.plan().strip().splitlines()]
-    assert kinds == ["linear", "moe_route", "moe_linear", "silu_mul", "moe_linear", "moe_combine"]
+    if fuse:  # the routing is folded into the gate/up expert linear (no op, no barrier of its own)
+        assert kinds == ["linear", "moe_linear", "silu_mul", "moe_linear", "moe_combine"] and "routing folded in" in k.plan()
+    else:
+        assert kinds == ["linear", "moe_route", "moe_linear", "silu_mul", "moe_linear", "moe_combine"]
     k.compile()
     k()
     # the oracle's block on the router logits the kernel itself produced (routing is discontinuous in them)
