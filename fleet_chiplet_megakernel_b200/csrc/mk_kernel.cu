@@ -3264,6 +3264,8 @@ __device__ __forceinline__ MoeWalk moe_walk(const OpDesc& op, int pairs) {
   return w;
 }
 
+__device__ __noinline__ void op_moe_down_combine(Ctx& c, const OpDesc& op, int T);
+
 // aux0 = top-k, aux1 = experts, n = rows per expert, k = K.  w: [experts * n, K] bf16 (tmap_w: the four maps of
 // the row-owner path over that 2-D view).  in: [T, K] (one row per token) or, with F_MOE_PAIR_IN, [T * top-k, K];
 // out: [T * top-k, n].  amax_idx: the routing table.
@@ -3285,6 +3287,10 @@ __device__ __noinline__ void op_moe_linear(Ctx& c, const OpDesc& op, int T) {
   }
   c.lin_seq += 1;
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the routing is visible: the producer may pick this op's expert rows
+  if (op.flags & F_MOE_COMBINE) {
+    op_moe_down_combine(c, op, T);
+    return;
+  }
   const int pairs = T * topk;
   const MoeWalk wk = moe_walk(op, pairs);
   if (!wk.any || wk.row0 >= wk.row1) return;
@@ -3375,6 +3381,116 @@ __device__ __noinline__ void op_moe_linear(Ctx& c, const OpDesc& op, int T) {
         out[(size_t)pr * op.ld_out + (r0 - pr * wk.n) + e_row] = __float2bfloat16_rn(v);
       }
       consumer_sync();
+    }
+  }
+  c.cons_idx += consumed;
+}
+
+// The down projection of the experts with the weighted sum folded in (F_MOE_COMBINE).  A CTA owns a range of the n
+// OUTPUT rows for all expert slots of a token: per token it stages the token's top-k input rows, then per chunk of
+// rows walks the slots (the weight rows are the slot's expert's rows of that chunk), rounds each slot's sums to bf16
+// like the linear's output would be, and adds them up slot by slot exactly as the stand-alone weighted sum does
+// (bf16 roundings of the PyTorch model, or fp32 fused multiply-adds), + residual.  The per-slot sums of the warps
+// alternate between the two token slots of the sums block, so that one CTA-wide sync per slot is enough.
+__device__ __noinline__ void op_moe_down_combine(Ctx& c, const OpDesc& op, int T) {
+  const KParams& p = c.p;
+  const int topk = op.aux0;
+  int row0, row1;
+  bool any;
+  rows_range(op, row0, row1, any);
+  if (!any || row0 >= row1) return;
+  const int nks = op.nkt;
+  const int kp = nks * kRowsStageK;
+  const int S = p.num_stages;
+  const int lane = c.lane, warp = c.warp;
+  const int pitch_b = (kp + 8) * 2;
+  const uint32_t xs0 = c.smem_addr + p.x_off;
+  const uint32_t x_zero = xs0 + (uint32_t)(topk * pitch_b);
+  const uint32_t w_off = (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * 128);
+  const uint32_t w_xor = (uint32_t)(lane & 7);
+  const uint32_t w_hi = (uint32_t)(lane >> 4);
+  const uint32_t bar_full0 = c.full_bar(0), bar_empty0 = c.empty_bar(0);
+  const int TP = p.sums_stride;  // 2
+  float* sums = c.sums();
+  const bool torch_num = p.numerics == NUM_TORCH;
+  const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(op.res);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.out);
+  const int e_row = c.tid & 31;
+  int s = (int)(c.cons_idx % (unsigned)S);
+  uint32_t parity = (c.cons_idx / (unsigned)S) & 1u;
+  unsigned consumed = 0;
+  const int nch = rows_num_chunks(row0, row1);
+#pragma unroll 1
+  for (int t = 0; t < T; ++t) {
+    stage_x(c, reinterpret_cast<const __nv_bfloat16*>(op.in) + (size_t)t * topk * op.ld_in, op.ld_in, op.k, kp, nullptr, 0, topk, topk, nullptr);
+#pragma unroll 1
+    for (int ci = 0; ci < nch; ++ci) {
+      const int r0 = rows_chunk_begin(row0, row1, nch, ci);
+      const int R = rows_chunk_begin(row0, row1, nch, ci + 1) - r0;
+      const int ntile = (R + 15) >> 4;
+      const uint32_t box_bytes = (uint32_t)R * 128u;
+      float comb = 0.f;  // (threads 0..R-1: the running weighted sum of output row r0 + tid)
+      float rr = 0.f;
+      if (c.tid < R && res != nullptr) rr = __bfloat162float(__ldcg(res + (size_t)t * op.ld_res + r0 + e_row));
+#pragma unroll 1
+      for (int sl = 0; sl < topk; ++sl) {
+        const bool a_real = (lane & 7) == 0;
+        const uint32_t a_row = a_real ? xs0 + (uint32_t)(sl * pitch_b + (lane >> 3) * 16 + warp * 128) : x_zero;
+        float acc[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+#pragma unroll 1
+        for (int ks = 0; ks < nks; ++ks) {
+          mbar_wait(c, bar_full0 + 8 * s, parity, ST_TIMEOUT_FULL);
+          const uint32_t wb = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes + (uint32_t)warp * box_bytes + w_off;
+          const uint32_t xa = a_row + (a_real ? (uint32_t)(ks * kRowsStageK * 2) : 0u);
+          uint32_t x[2][4];
+          ldmatrix_x4(xa, x[0][0], x[0][1], x[0][2], x[0][3]);
+          ldmatrix_x4(xa + (a_real ? 64u : 0u), x[1][0], x[1][1], x[1][2], x[1][3]);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (q < ntile) {
+#pragma unroll
+              for (int st = 0; st < 4; ++st) {
+                uint32_t w0, w1, w2, w3;
+                ldmatrix_x4(wb + (uint32_t)q * 2048u + ((((uint32_t)(2 * st) + w_hi) ^ w_xor) << 4), w0, w1, w2, w3);
+                mma_bf16(acc[2 * q + (st & 1)], w0, w1, w2, w3, x[st >> 1][2 * (st & 1)], x[st >> 1][2 * (st & 1) + 1]);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_empty0 + 8 * s);
+          ++consumed;
+          if (++s == S) {
+            s = 0;
+            parity ^= 1u;
+          }
+        }
+        const int half = sl & 1;
+        if ((lane & 3) == 0) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float* d = sums + ((warp * kChunkRows + 16 * q + (lane >> 2)) * TP) + half;
+            d[0] = acc[2 * q][0] + acc[2 * q + 1][0];
+            d[8 * TP] = acc[2 * q][2] + acc[2 * q + 1][2];
+          }
+        }
+        consumer_sync();
+        if (c.tid < R) {
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < kNumConsumerWarps; ++w) v += sums[(w * kChunkRows + e_row) * TP + half];
+          const float f = rbf(v);  // the down projection's output is bf16
+          const float wgt = __ldcg(op.amax_val + (size_t)t * topk + sl);
+          comb = torch_num ? rbf(comb + rbf(f * wgt)) : fmaf(f, wgt, comb);
+        }
+      }
+      if (c.tid < R) {
+        float v = comb;
+        if (res != nullptr) v = (torch_num ? rbf(v) : v) + rr;
+        out[(size_t)t * op.ld_out + r0 + e_row] = __float2bfloat16_rn(v);
+      }
+      consumer_sync();  // (the next chunk's or token's first slot writes the half the last slot may still be read from)
     }
   }
   c.cons_idx += consumed;
@@ -3761,6 +3877,43 @@ __device__ __noinline__ void producer_loop(Ctx& c) {
           if (dead) break;
           __threadfence();
           const int topk = rop.aux0;
+          if (rop.flags & F_MOE_COMBINE) {
+            // output rows owned for all slots: token, chunk of rows, slot, k stage (the consumers' order)
+            int row0, row1;
+            bool any;
+            rows_range(rop, row0, row1, any);
+            if (!any || row0 >= row1) continue;
+            const int nch = rows_num_chunks(row0, row1);
+            for (int t = 0; t < T && !dead; ++t)
+              for (int ci = 0; ci < nch && !dead; ++ci) {
+                const int r0 = rows_chunk_begin(row0, row1, nch, ci);
+                const int R = rows_chunk_begin(row0, row1, nch, ci + 1) - r0;
+                const void* tmap = reinterpret_cast<const unsigned char*>(rop.tmap_w) + ((R >> 3) - 1) * 128;
+                const uint32_t box_bytes = (uint32_t)R * 128u;
+                for (int sl = 0; sl < topk && !dead; ++sl) {
+                  const int wrow = __ldcg(rop.amax_idx + t * topk + sl) * rop.n + r0;
+                  for (int ks = 0; ks < rop.nkt; ++ks) {
+                    if (!mbar_wait(c, bar_empty0 + 8 * s, empty_parity, ST_TIMEOUT_EMPTY)) {
+                      dead = true;
+                      break;
+                    }
+                    const uint32_t full = bar_full0 + 8 * s;
+                    const uint32_t dst = c.smem_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+                    mbar_arrive_expect_tx(full, 8u * box_bytes);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                      tma_load_2d_hint(dst + (uint32_t)j * box_bytes, tmap, full, ks * kRowsStageK + j * kBoxK, wrow, pol_stream);
+                    issued += 1;
+                    fl[1] = (int)issued;
+                    if (++s == S) {
+                      s = 0;
+                      empty_parity ^= 1u;
+                    }
+                  }
+                }
+              }
+            continue;
+          }
           const MoeWalk wk = moe_walk(rop, T * topk);
           if (!wk.any || wk.row0 >= wk.row1) continue;
           const int p_first = wk.row0 / wk.n, p_last = (wk.row1 - 1) / wk.n;

@@ -93,6 +93,7 @@ struct PlanOp {
 };
 
 bool starts_with(const std::string& s, const char* p) { return s.rfind(p, 0) == 0; }
+bool canonical_name_is_w2(const std::string& s) { return starts_with(s, "moe_w2_linear") || s == "gang_moe_w2"; }
 
 }  // namespace
 
@@ -808,6 +809,18 @@ int plan_graph(mk_handle* h) {
       if (in.ndim != 3 || out.ndim != 2 || in.dims[2] != out.dims[1] || out.dims[1] % 8)
         return h->fail(MK_E_INVALID, "moe_mul_sum_add: input [T, k, n], output [T, n]");
       if (int e = check_2d_bf16(h, op.t[2], nm.c_str())) return e;
+      // right behind the down projection of the experts, and its only reader: that op adds the slots up itself
+      if (fuse && rows_mode && !h->plan.empty() && in.dims[1] <= 8) {
+        PlanOp& prev = h->plan.back();
+        if (prev.type == mk::OP_MOE_LINEAR && (prev.flags & mk::F_MOE_PAIR_IN) && prev.out == op.t[0] && h->tensors[op.t[0]].owned &&
+            only_next_reads(i - 1, op.t[0]) && canonical_name_is_w2(h->nops[i - 1].name)) {
+          prev.flags |= mk::F_MOE_COMBINE;
+          prev.res = op.t[2];
+          prev.out = op.t[3];
+          prev.note += prev.note.empty() ? "weighted sum folded in" : ", weighted sum folded in";
+          continue;
+        }
+      }
       po.type = mk::OP_MOE_COMBINE;
       po.in = op.t[0]; po.res = op.t[2]; po.out = op.t[3];
       po.n = (int)out.dims[1];
@@ -1251,7 +1264,8 @@ static int compile_program(mk_handle* h, bool first) {
       const int64_t units = pairs * (p.n / mk::kUnitRows);
       const int g = (int)std::min<int64_t>(h->num_sms, units);
       const int64_t rows_per_cta = ((units + g - 1) / g) * mk::kUnitRows;
-      const int spans = (int)((rows_per_cta + p.n - 1) / p.n + 1);
+      int spans = (int)((rows_per_cta + p.n - 1) / p.n + 1);
+      if (p.flags & mk::F_MOE_COMBINE) spans = std::max(spans, p.aux0);  // (the token's top-k input rows)
       if (spans > 8) return h->fail(MK_E_UNSUPPORTED, "moe linear: %d rows per expert are too few for the row-owner split", p.n);
       if (spans * (kp + 8) * 2 + 16 > x_budget) return h->fail(MK_E_UNSUPPORTED, "moe linear: K=%d is too wide", p.k);
       x_bytes = std::max(x_bytes, spans * (kp + 8) * 2 + 16);

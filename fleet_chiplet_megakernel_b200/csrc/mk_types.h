@@ -72,6 +72,8 @@ enum OpFlags : int {
   F_LL_OUT = 1 << 18,       // linear / attention: the outputs are also stored as tagged words (ll_out)
   F_LL_IN = 1 << 19,        // linear / attention: the input rows are read from tagged words (ll_in, producer op ll_in_op); no barrier
   F_LL_RES = 1 << 20,       // linear: the residual is read from tagged words (ll_res, producer op ll_res_op)
+  F_MOE_COMBINE = 1 << 23,  // MoE down linear: a CTA owns output rows for ALL expert slots of a token and adds the slots up itself
+                            // (weights amax_val, + res), out: [T, n]; no per-slot output, no separate weighted-sum op
   F_MOE_ROUTE = 1 << 22,    // MoE gate/up linear: the op first routes the tokens itself (res: router logits [T, experts]); every CTA
                             // keeps the expert ids in shared memory for its producer, CTA 0 also stores the runtime's tables
   F_XRED = 1 << 21,         // linear with F_LL_IN under tensor parallelism: the op first adds up its slice of the latest exchange
