@@ -865,7 +865,7 @@ __device__ __noinline__ void stage_x_rows(Ctx& c, const void* in, int ld_in, int
   constexpr int kMaxV = 6;  // 24 stages / 4 per round
   uint4* xs = reinterpret_cast<uint4*>(c.smem + c.p.x_off);
   const int pitch = (kp >> 3) + 1;  // uint4 per row
-  const int v0 = ((c.lane >> 3) * kRowsStageK + c.warp * 64 + (c.lane & 7) * 8) >> 3;  // vector of round 0
+  const int v0 = ((c.lane >> 3) * kRowsStageK + c.warp * 64 + (c.lane & 7) * 8) >> 3;  // vector of the first round
   constexpr int vstep = 4 * kRowsStageK / 8;                                           // vectors per round
   const int kvec = K >> 3, nvec = kp >> 3;
   if (c.lane == 0) xs[rows * pitch] = make_uint4(0, 0, 0, 0);  // the chunk absent tokens point at (every warp writes the same zeros)
