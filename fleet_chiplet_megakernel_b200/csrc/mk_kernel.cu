@@ -1815,7 +1815,7 @@ __device__ __noinline__ void linear_pass_rows(Ctx& c, const OpDesc& op, int tok0
         best = arg_better(best, b);
       }
     }
-    consumer_sync();  // the sums block is free again
+    if (ci + 1 < nch) consumer_sync();  // the sums block is free again (after the last chunk, the sync that opens the next op or pass does it)
   }
   if ((op.flags & F_ARGMAX) && lane == 0 && e_tok < ntok) {
     op.amax_val[(size_t)(tok0 + e_tok) * op.amax_n + blockIdx.x] = best.v;
@@ -1856,7 +1856,10 @@ __device__ void op_linear(Ctx& c, const OpDesc& op, int T) {
   if (c.tid == 0) c.flags()[4] = (int)c.lin_seq;  // the activation producer may now read this op's input
   const int passes = linear_passes(op, T);
   if constexpr (PATH == PATH_ROWS) {
-    for (int g = 0; g < passes; ++g) linear_pass_rows(c, op, g * op.aux3, T, (pre && g == 0) ? pre_w : nullptr);
+    for (int g = 0; g < passes; ++g) {
+      linear_pass_rows(c, op, g * op.aux3, T, (pre && g == 0) ? pre_w : nullptr);
+      if (g + 1 < passes) consumer_sync();  // (a pass leaves its last chunk's sums block without a sync of its own)
+    }
   } else if constexpr (PATH == PATH_UMMA) {
     for (int g = 0; g < passes; ++g) linear_pass_umma(c, op, g * op.aux3, T, g);
   } else {
